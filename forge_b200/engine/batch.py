@@ -1,0 +1,97 @@
+"""The batch of one step: for each request its next tokens (a portion of its prompt, cut anywhere, or one
+decoded token), flattened into one list of tokens that every kernel runs over once.
+
+The reference's InferenceBatch (include/forge/inference_batch.h:10-76) carries the same information per
+item; its engine then loops over sequences (transformer_engine.cpp:201-254).  Here the arrays are flat and
+on the device: attention is the only kernel that looks at request boundaries.
+"""
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step.  ``want``: indices into ``tokens`` whose logits are asked for."""
+    req_id: object
+    tokens: List[int]
+    want: List[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupBatch:
+    block_table: torch.Tensor          # int32 [S, max_pages]; -1 where a page was released
+    slot_mapping: torch.Tensor         # int32 [T]: page * page_size + offset of each new token
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_requests: int
+    num_logits: int
+    token_ids: torch.Tensor            # int32 [T]
+    positions: torch.Tensor            # int32 [T]   position of each token in its request
+    tok_req: torch.Tensor              # int32 [T]   row (0..S-1) of each token's request in this step
+    q_start: torch.Tensor              # int32 [S+1] first token of each request in the flat list
+    context_before: torch.Tensor       # int32 [S]   tokens the request already had in the cache
+    slots: torch.Tensor                # int32 [S]   request slot (row of fixed-size state tensors)
+    logits_rows: Optional[torch.Tensor]  # int32 [R] flat token indices whose logits are wanted
+    groups: Dict[str, GroupBatch]
+    status: Optional[torch.Tensor] = None    # int32 [1] device error flags raised by kernels
+    # host copies for parts and kernels that plan their work on the host
+    host_q_start: List[int] = field(default_factory=list)
+    host_context_before: List[int] = field(default_factory=list)
+    host_slots: List[int] = field(default_factory=list)
+    attention_plan: dict = field(default_factory=dict)
+
+
+def build_step_batch(entries, manager, device, max_pages, status=None):
+    """Appends every entry's tokens to its request in the cache manager (allocating pages) and lays the
+    step out as device arrays.  Raises OutOfPages before touching anything if a request cannot grow."""
+    reserve = {g: 0 for g in manager.groups}
+    for e in entries:
+        need = manager.pages_needed(e.req_id, len(e.tokens))
+        for g, n in need.items():
+            reserve[g] += n
+    for g, n in reserve.items():
+        if n > manager.num_free_pages(g):
+            from ..cache import OutOfPages
+            raise OutOfPages(f"step needs {n} pages of group {g!r}, {manager.num_free_pages(g)} free")
+
+    token_ids, positions, tok_req, q_start, ctx_before, slots, rows = [], [], [], [0], [], [], []
+    slot_maps = {g: [] for g in manager.groups}
+    for s, e in enumerate(entries):
+        n0 = manager.num_tokens(e.req_id)
+        new_slots = manager.append(e.req_id, len(e.tokens))
+        for g in slot_maps:
+            slot_maps[g].extend(new_slots[g])
+        base = len(token_ids)
+        token_ids.extend(e.tokens)
+        positions.extend(range(n0, n0 + len(e.tokens)))
+        tok_req.extend([s] * len(e.tokens))
+        q_start.append(base + len(e.tokens))
+        ctx_before.append(n0)
+        slots.append(manager.slot(e.req_id))
+        for w in e.want:
+            if not 0 <= w < len(e.tokens):
+                raise ValueError(f"request {e.req_id!r}: wanted index {w} outside its {len(e.tokens)} tokens")
+            rows.append(base + w)
+
+    def dev(lst):
+        return torch.tensor(lst, dtype=torch.int32, device=device)
+
+    groups = {}
+    for g in manager.groups:
+        table = torch.full((len(entries), max_pages), -1, dtype=torch.int32)
+        for s, e in enumerate(entries):
+            t = manager.block_table(e.req_id, g)
+            if len(t) > max_pages:
+                raise ValueError(f"request {e.req_id!r} holds {len(t)} pages, tables have room for {max_pages}")
+            table[s, :len(t)] = torch.tensor(t, dtype=torch.int32)
+        groups[g] = GroupBatch(table.to(device), dev(slot_maps[g]))
+    return StepBatch(
+        num_tokens=len(token_ids), num_requests=len(entries), num_logits=len(rows),
+        token_ids=dev(token_ids), positions=dev(positions), tok_req=dev(tok_req), q_start=dev(q_start),
+        context_before=dev(ctx_before), slots=dev(slots), logits_rows=dev(rows) if rows else None, groups=groups,
+        status=status, host_q_start=q_start, host_context_before=ctx_before, host_slots=slots)

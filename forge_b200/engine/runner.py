@@ -1,0 +1,129 @@
+"""The step function: one call runs one batch of (request, its next tokens) through the model, from the
+cache that earlier steps left, and returns the logits at the wanted places.
+
+``ModelRunner`` owns the model, the cache storage and the cache manager.  Callers (the scheduler, the
+replay tool, tests) admit a request, feed it tokens over any number of steps, cut anywhere, and release
+it; the runner makes no scheduling decision of its own.  (Reference counterparts:
+InferenceEngine::forward / forward_batch, include/forge/engine.h:65-90.)
+"""
+import torch
+
+from ..cache import CacheStorage, OutOfPages, bytes_per_page
+from ..config import load_config
+from ..parts import Runtime
+from ..weights.loader import load_tensors
+from .batch import StepEntry, build_step_batch
+from .model import Model
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    """The step was refused before anything ran (bad token id, position limit, unknown request)."""
+
+
+def resolve_dtype(dtype):
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(DTYPES)}, got {dtype!r}") from None
+
+
+class ModelRunner:
+    def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
+                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6):
+        """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
+        ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the
+        free device memory holds, capped by max_requests * max positions)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("forge_b200 runs on a CUDA device (B200, sm_100a) only; no device is visible")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = resolve_dtype(dtype)
+        self.rt = Runtime(self.device, self.dtype)
+        if config is None:
+            if model_dir is None:
+                raise ValueError("give a model folder, or a config and tensors")
+            config = load_config(model_dir)
+        self.config = config
+        self.plan = config.plan()
+        self.model = Model(self.plan, self.rt)
+        if tensors is None:
+            tensors = load_tensors(model_dir, self.model.tensor_specs())
+        else:
+            from ..weights.loader import check_tensors
+            check_tensors("tensors", self.model.tensor_specs(), {n: (tuple(t.shape), t.dtype) for n, t in tensors.items()})
+        self.model.load(tensors, where=str(model_dir or "tensors"))
+        del tensors
+
+        self.page_size, self.max_requests = int(page_size), int(max_requests)
+        specs, cfrom = self.model.cache_specs(), self.model.cache_from()
+        if cache_tokens is None:
+            per_page = max(bytes_per_page(specs, cfrom, self.page_size, self.dtype).values(), default=0)
+            free, _ = torch.cuda.mem_get_info(self.device)
+            cap = self.max_requests * self.plan.max_positions
+            cache_tokens = cap if per_page == 0 else min(cap, int(free * memory_fraction) // per_page * self.page_size)
+        self.num_pages = max(1, -(-int(cache_tokens) // self.page_size))
+        self.storage = CacheStorage(specs, cfrom, self.page_size, self.num_pages, self.max_requests, self.dtype,
+                                    self.device)
+        self.manager = self.storage.manager
+        self.max_pages_per_request = min(self.num_pages, -(-self.plan.max_positions // self.page_size))
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ---------------------------------------------------------------------------------- requests
+    def admit(self, req_id):
+        return self.manager.admit(req_id)
+
+    def release(self, req_id):
+        self.manager.free(req_id)
+
+    def is_live(self, req_id):
+        return req_id in self.manager.live_requests()
+
+    # ---------------------------------------------------------------------------------- the step
+    def validate(self, entries):
+        V, limit = self.plan.vocab_size, self.plan.max_positions
+        live = set(self.manager.live_requests())
+        seen = set()
+        for e in entries:
+            if e.req_id not in live:
+                raise StepError(f"request {e.req_id!r} was not admitted")
+            if e.req_id in seen:
+                raise StepError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if not e.tokens:
+                raise StepError(f"request {e.req_id!r} brings no tokens")
+            for t in e.tokens:
+                if not isinstance(t, int) or not 0 <= t < V:
+                    raise StepError(f"request {e.req_id!r}: token id {t!r} is outside [0, {V})")
+            if self.manager.num_tokens(e.req_id) + len(e.tokens) > limit:
+                raise StepError(f"request {e.req_id!r} would exceed the model's {limit} positions")
+
+    def step(self, entries):
+        """entries: list of StepEntry.  Runs exactly the tokens given, as one batch; returns fp32 logits
+        [number of wanted places, vocab] on the device in the order of the entries and of their ``want``
+        (None if nothing is wanted).  Raises StepError / OutOfPages before anything has run."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self.validate(entries)
+        batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
+        self.storage.zero_state_slots(self.manager.take_fresh_slots())
+        logits = self.model.forward(batch, self.storage.layers)
+        for e in entries:
+            self.manager.release_out_of_window(e.req_id)
+        return logits
+
+    def check_status(self):
+        """Reads the device error word (synchronises); raises if a kernel flagged a problem."""
+        s = int(self.status.item())
+        if s:
+            self.status.zero_()
+            raise RuntimeError(f"a kernel reported an error (status word {s:#x}): "
+                               + ("token id outside the vocabulary; " if s & 1 else "")
+                               + ("a bounded wait ran out; " if s & 2 else ""))
+
+
+__all__ = ["ModelRunner", "StepEntry", "StepError", "OutOfPages", "resolve_dtype"]

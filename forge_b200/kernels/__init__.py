@@ -1,0 +1,256 @@
+"""Python face of the hand-written CUDA kernels (sm_100a).
+
+Each function checks its tensors (device, dtype, contiguity, shapes), passes raw pointers and the
+current CUDA stream to an ``extern "C"`` entry point through ctypes, and raises ``KernelError`` with the
+library's message on a non-zero return.  There is no CPU or PyTorch fallback: if a library cannot be
+compiled or loaded the first call that needs it raises.
+"""
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .build import BuildError, build_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt):
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dt}")
+
+
+_P, _I, _F = c_void_p, c_int, c_float
+
+_SIGNATURES = {
+    "core": {
+        "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+        "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _P],
+        "forge_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "forge_paged_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+        "forge_argmax": [_P, _P, _I, _I, _P],
+        "forge_repeat_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
+        "forge_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    },
+    "gemm_sm100": {
+        "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    },
+    "attention_mma": {
+        "forge_paged_attention_mma": [_P] * 9 + [_I] * 10 + [_F, _P],
+    },
+}
+
+_libs = {}
+
+
+def library(name):
+    """Loads (building first if needed) kernel library ``name`` and returns its ctypes handle."""
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    if not torch.cuda.is_available():
+        raise KernelError("forge_b200 runs on a CUDA device (B200, sm_100a) only; no device is visible")
+    try:
+        path = build_library(name)
+    except BuildError as e:
+        raise KernelError(f"kernel library '{name}' is not available: {e}") from e
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        raise KernelError(f"cannot load {path}: {e}") from e
+    for fn, argtypes in _SIGNATURES[name].items():
+        f = getattr(lib, fn)
+        f.argtypes = argtypes
+        f.restype = c_int
+    lib.forge_last_error.restype = ctypes.c_char_p
+    _libs[name] = lib
+    return lib
+
+
+def _check(lib, rc, what):
+    if rc != 0:
+        raise KernelError(f"{what}: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t, name, dtype=None, ndim=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dims, got shape {tuple(t.shape)}")
+    return t.data_ptr()
+
+
+def _opt(t, name, dtype=None):
+    return None if t is None else _need(t, name, dtype)
+
+
+# ---------------------------------------------------------------------------------------------- core
+
+def embedding(ids, table, out=None, status=None):
+    """out[t,:] = table[ids[t],:] as float32 [T,H]; ids int32 [T]; table [V,H] float32 or bfloat16."""
+    lib = library("core")
+    T, (V, H) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(lib, lib.forge_embedding(_need(ids, "ids", torch.int32), _need(table, "table", ndim=2),
+                                    dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V,
+                                    _opt(status, "status", torch.int32), _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
+    """y = x * rsqrt(mean(x^2)+eps) * w over the last dim of float32 x [T,H]; ``rows`` (int32) picks rows."""
+    lib = library("core")
+    H = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    if weight.numel() != H:
+        raise KernelError(f"rmsnorm: weight has {weight.numel()} elements, rows have {H}")
+    if out is None:
+        out = torch.empty((R, H), dtype=out_dtype, device=x.device)
+    _check(lib, lib.forge_rmsnorm(_need(x, "x", torch.float32, 2), _need(weight, "weight", torch.float32),
+                                  _need(out, "out", out_dtype), dtype_code(out_dtype),
+                                  _opt(rows, "rows", torch.int32), R, H, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def rope_kv_write(qkv, positions, slot_mapping, kv_cache, n_heads, n_kv_heads, head_dim, page_size, theta,
+                  act_dtype, rotary=True, q_out=None):
+    """Rotates q and k of float32 qkv [T,(NH+2NKV)*HD], returns q [T,NH*HD] in ``act_dtype`` and writes
+    k, v into ``kv_cache`` [pages,2,NKV,page,HD] at ``slot_mapping`` (int32 [T]; None or negative: no write)."""
+    lib = library("core")
+    T = qkv.shape[0]
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    if qkv.shape[1] != width:
+        raise KernelError(f"rope_kv_write: qkv has width {qkv.shape[1]}, expected {width}")
+    if q_out is None:
+        q_out = torch.empty((T, n_heads * head_dim), dtype=act_dtype, device=qkv.device)
+    if kv_cache is not None and kv_cache.dtype != act_dtype:
+        raise KernelError("rope_kv_write: cache and activation dtypes differ")
+    if kv_cache is None:
+        slot_mapping = None
+    _check(lib, lib.forge_rope_kv_write(_need(qkv, "qkv", torch.float32, 2), _need(positions, "positions", torch.int32),
+                                        _opt(slot_mapping, "slot_mapping", torch.int32), _need(q_out, "q_out", act_dtype),
+                                        _opt(kv_cache, "kv_cache"), dtype_code(act_dtype), T, n_heads, n_kv_heads,
+                                        head_dim, page_size, float(theta), 1 if rotary else 0, _stream()),
+           "rope_kv_write")
+    return q_out
+
+
+def silu_mul_interleaved(gu, out_dtype, out=None):
+    """out[t,j] = silu(gu[t,2j]) * gu[t,2j+1]; gu float32 [T,2I]."""
+    lib = library("core")
+    T, two_i = gu.shape
+    if out is None:
+        out = torch.empty((T, two_i // 2), dtype=out_dtype, device=gu.device)
+    _check(lib, lib.forge_silu_mul_interleaved(_need(gu, "gu", torch.float32, 2), _need(out, "out", out_dtype),
+                                               dtype_code(out_dtype), T, two_i // 2, _stream()), "silu_mul_interleaved")
+    return out
+
+
+def gemm_simt(a, w, bias=None, out=None, accumulate=False):
+    """float32 C[M,N] = a[M,K] . w[N,K]^T (+bias) (+C when ``accumulate``), true fp32 FMA; a, w same dtype."""
+    lib = library("core")
+    (M, K), (N, K2) = a.shape, w.shape
+    if K != K2 or a.dtype != w.dtype:
+        raise KernelError(f"gemm_simt: a {tuple(a.shape)} {a.dtype} does not match w {tuple(w.shape)} {w.dtype}")
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm_simt: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    elif tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_simt: out has shape {tuple(out.shape)}, expected {(M, N)}")
+    _check(lib, lib.forge_gemm_simt(_need(a, "a", ndim=2), _need(w, "w", ndim=2), _opt(bias, "bias", torch.float32),
+                                    _need(out, "out", torch.float32), dtype_code(a.dtype), M, N, K,
+                                    1 if accumulate else 0, _stream()), "gemm_simt")
+    return out
+
+
+def paged_attention_simt(q, kv_cache, block_table, tok_req, positions, n_heads, n_kv_heads, head_dim, page_size,
+                         window=0, scale=None, out=None):
+    """Causal GQA over the paged cache, fp32 arithmetic; q [T,NH*HD]; block_table int32 [S,max_pages];
+    tok_req / positions int32 [T] give each token's row of the table and its position."""
+    lib = library("core")
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    if kv_cache.dtype != q.dtype:
+        raise KernelError("paged_attention_simt: q and cache dtypes differ")
+    scale = head_dim ** -0.5 if scale is None else scale
+    _check(lib, lib.forge_paged_attention_simt(
+        _need(q, "q", ndim=2), _need(kv_cache, "kv_cache"), _need(block_table, "block_table", torch.int32, 2),
+        _need(tok_req, "tok_req", torch.int32), _need(positions, "positions", torch.int32), _need(out, "out", q.dtype),
+        dtype_code(q.dtype), T, n_heads, n_kv_heads, head_dim, page_size, block_table.shape[1], int(window or 0),
+        float(scale), _stream()), "paged_attention_simt")
+    return out
+
+
+def argmax(logits, out=None):
+    """int32 [R]: index of the largest of each row of float32 logits [R,V]; lowest index wins a tie."""
+    lib = library("core")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(lib, lib.forge_argmax(_need(logits, "logits", torch.float32, 2), _need(out, "out", torch.int32), R, V,
+                                 _stream()), "argmax")
+    return out
+
+
+def repeat_penalty(logits, tokens, counts, offsets, penalty):
+    """In place: for row r and each (token, count) in [offsets[r], offsets[r+1]): logit>0 ? /pen : *pen, count times."""
+    lib = library("core")
+    R, V = logits.shape
+    _check(lib, lib.forge_repeat_penalty(_need(logits, "logits", torch.float32, 2), _need(tokens, "tokens", torch.int32),
+                                         _need(counts, "counts", torch.int32), _need(offsets, "offsets", torch.int32),
+                                         _need(penalty, "penalty", torch.float32), R, V, _stream()), "repeat_penalty")
+    return logits
+
+
+def sample(logits, temperature, top_k, top_p, u, out=None):
+    """int32 [R]: temperature / top-k / top-p sampling of each row with the caller's uniform numbers u [R]."""
+    lib = library("core")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(lib, lib.forge_sample(_need(logits, "logits", torch.float32, 2), _need(temperature, "temperature", torch.float32),
+                                 _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32),
+                                 _need(u, "u", torch.float32), _need(out, "out", torch.int32), R, V, _stream()), "sample")
+    return out
+
+
+# ------------------------------------------------------------------------------- tensor-core kernels
+
+def gemm_sm100_supports(n, k):
+    """The tcgen05 kernel reads rows by TMA: a row of K bfloat16 must be a multiple of 16 bytes."""
+    return _TENSOR_CORE_GEMM and k % 8 == 0 and n >= 1
+
+
+def attention_mma_supports(head_dim, group, page_size):
+    return _TENSOR_CORE_ATTENTION and head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size % 16 == 0
+
+
+def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=None,
+                    scale=None):
+    """Attention of every token of the step over its request's pages; picks the kernel by dtype and shape."""
+    return paged_attention_simt(q, kv_cache, group_batch.block_table, batch.tok_req, batch.positions, n_heads,
+                                n_kv_heads, head_dim, page_size, window=window or 0, scale=scale)
+
+
+_TENSOR_CORE_GEMM = False
+_TENSOR_CORE_ATTENTION = False

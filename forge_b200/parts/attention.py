@@ -1,0 +1,65 @@
+"""Grouped-query causal self-attention over the paged cache.
+
+  qkv = x . [Wq;Wk;Wv]^T (+b);  q, k <- position(q, k);  cache <- k, v;  o = softmax(q k^T / sqrt(HD)) v;
+  residual += o . Wo^T
+(reference: src/inference/engines/generic_engine.cpp:940-1002; kv head of q head h is h // (NH/NKV)).
+The three projections are one matrix product (rows of Wq, Wk, Wv concatenated at load time).
+"""
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import KVCacheSpec, Part, build_part, register_part
+from .linear import Linear
+
+DEFAULT_NAMES = {"q": "self_attn.q_proj", "k": "self_attn.k_proj", "v": "self_attn.v_proj", "o": "self_attn.o_proj"}
+
+
+class GQAAttention(Part):
+    def __init__(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, position, qkv_bias=False, out_bias=False,
+                 window=None, names=None):
+        self.rt = rt
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), window
+        self.names = {**DEFAULT_NAMES, **(names or {})}
+        self.position = build_part("position", position, rt)
+        self.scale = head_dim ** -0.5
+        self.qkv = self.o = None
+
+    def tensor_specs(self):
+        n, H = self.names, self.hidden_size
+        q_out, kv_out = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        specs = {n["q"] + ".weight": TensorSpec((q_out, H)), n["k"] + ".weight": TensorSpec((kv_out, H)),
+                 n["v"] + ".weight": TensorSpec((kv_out, H)), n["o"] + ".weight": TensorSpec((H, q_out))}
+        if self.qkv_bias:
+            specs.update({n["q"] + ".bias": TensorSpec((q_out,), role="bias"),
+                          n["k"] + ".bias": TensorSpec((kv_out,), role="bias"),
+                          n["v"] + ".bias": TensorSpec((kv_out,), role="bias")})
+        if self.out_bias:
+            specs[n["o"] + ".bias"] = TensorSpec((H,), role="bias")
+        return specs
+
+    def bind(self, tensors):
+        n = self.names
+        w = torch.cat([tensors[n[k] + ".weight"] for k in "qkv"], dim=0)
+        b = torch.cat([tensors[n[k] + ".bias"] for k in "qkv"], dim=0) if self.qkv_bias else None
+        self.qkv = Linear(self._matrix(w), None if b is None else self._vector_f32(b), self.rt)
+        ob = self._vector_f32(tensors[n["o"] + ".bias"]) if self.out_bias else None
+        self.o = Linear(self._matrix(tensors[n["o"] + ".weight"]), ob, self.rt)
+
+    def cache_spec(self):
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, x, batch, cache, residual):
+        """x [T,H] normed input; cache: the layer's KV cache view; adds the output projection into residual."""
+        g = batch.groups[cache.group]
+        qkv = self.qkv.forward(x)                                           # fp32 [T,(NH+2NKV)*HD]
+        slots = g.slot_mapping if cache.writable else None
+        q = self.position.encode_and_store(qkv, batch.positions, slots, cache.kv if cache.writable else None,
+                                           self.num_heads, self.num_kv_heads, cache.page_size)
+        o = kernels.paged_attention(q, cache.kv, g, batch, self.num_heads, self.num_kv_heads, self.head_dim,
+                                    cache.page_size, window=self.window, scale=self.scale)
+        self.o.forward(o, accumulate_into=residual)
+
+
+register_part("mixer", "attention", GQAAttention, replace=True)

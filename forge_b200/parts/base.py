@@ -1,0 +1,98 @@
+"""What a part is, and the registry that builds parts from ``PartSpec``s.
+
+A part owns its sizes and constants (constructor parameters), the names and shapes of its tensors
+(``tensor_specs``), their device layout (``bind``) and its computation (``forward``).  It never looks at
+the model configuration or at other layers.  Categories and the interface of each:
+
+  norm          forward(x_f32[T,H], out_dtype, rows=None) -> [R,H]
+  position      encode_and_store(qkv_f32, positions, slot_mapping, kv_cache, num_heads, num_kv_heads,
+                                 page_size, act_dtype) -> q[T,NH*HD]
+  mixer         cache_spec() -> KVCacheSpec | StateSpec | None
+                forward(x[T,H], batch, cache, residual_f32[T,H])      (adds its output into residual)
+  feed_forward  forward(x[T,H], residual_f32[T,H])                     (adds its output into residual)
+  block         built from a LayerSpec; forward(residual, batch, cache)
+  embedding     forward(token_ids) -> residual_f32[T,H]
+  lm_head       forward(x[R,H]) -> logits_f32[R,V]
+"""
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..config.base import ConfigError, PartSpec
+from ..weights.loader import TensorSpec
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "lm_head")
+_REGISTRY = {c: {} for c in CATEGORIES}
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision parts compute.  ``dtype`` is the type of activations, matrices and
+    cache: torch.bfloat16 (tensor-core kernels) or torch.float32 (true 32-bit kernels everywhere)."""
+    device: torch.device
+    dtype: torch.dtype
+
+    @property
+    def full_precision(self):
+        return self.dtype == torch.float32
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """A mixer that keeps keys and values: pages of [2, num_kv_heads, page_size, head_dim].
+    ``window``: only the last ``window`` positions are ever read (None: all of them)."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A mixer that keeps per-request state of fixed size: one row of ``shape`` per request slot."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+def register_part(category, kind, cls, replace=False):
+    if category not in _REGISTRY:
+        raise ConfigError(f"unknown part category {category!r}; known: {CATEGORIES}")
+    if kind in _REGISTRY[category] and not replace:
+        raise ConfigError(f"{category} part {kind!r} is already registered")
+    _REGISTRY[category][kind] = cls
+
+
+def unregister_part(category, kind):
+    _REGISTRY[category].pop(kind, None)
+
+
+def registered_parts(category):
+    return sorted(_REGISTRY[category])
+
+
+def build_part(category, spec: PartSpec, rt: Runtime):
+    try:
+        cls = _REGISTRY[category][spec.kind]
+    except KeyError:
+        raise ConfigError(f"no {category} part named {spec.kind!r}; known: {registered_parts(category)}") from None
+    return cls(rt=rt, **spec.params)
+
+
+class Part:
+    """Base of all parts.  Subclasses define ``tensor_specs`` and ``bind``."""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]):
+        """Takes the part's tensors (CPU or device, as stored in the file) and keeps device copies in the
+        layout its kernels want."""
+
+    # helpers -------------------------------------------------------------------------------------
+    def _matrix(self, t):
+        """Matrices compute in the runtime's dtype."""
+        return t.to(device=self.rt.device, dtype=self.rt.dtype).contiguous()
+
+    def _vector_f32(self, t):
+        """Norm weights and biases are read in 32-bit by every kernel."""
+        return t.to(device=self.rt.device, dtype=torch.float32).contiguous()

@@ -1,0 +1,53 @@
+"""Arrangements of a layer's parts around the fp32 residual stream.
+
+"pre_norm":  r += mixer(norm_in(r));  r += feed_forward(norm_post(r))
+(reference: src/inference/engines/generic_engine.cpp:931-938, 1045-1052, 1080).  The additions happen in
+the epilogue of each part's last matrix product, in fp32.
+"""
+from ..weights.loader import TensorSpec  # noqa: F401  (re-exported for part authors)
+from .base import Part, build_part, register_part
+
+
+class PreNormBlock(Part):
+    NORM_NAMES = {"input": "input_layernorm.", "post_mixer": "post_attention_layernorm."}
+
+    def __init__(self, rt, layer_spec):
+        self.rt = rt
+        self.mixer = build_part("mixer", layer_spec.mixer, rt)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt)
+        self.norm_in = build_part("norm", layer_spec.norms["input"], rt)
+        self.norm_post = build_part("norm", layer_spec.norms["post_mixer"], rt)
+
+    def _children(self):
+        return [("", self.mixer), ("", self.feed_forward), (self.NORM_NAMES["input"], self.norm_in),
+                (self.NORM_NAMES["post_mixer"], self.norm_post)]
+
+    def tensor_specs(self):
+        specs = {}
+        for prefix, part in self._children():
+            for name, s in part.tensor_specs().items():
+                specs[prefix + name] = s
+        return specs
+
+    def bind(self, tensors):
+        for prefix, part in self._children():
+            part.bind({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
+
+    def forward(self, residual, batch, cache):
+        x = self.norm_in.forward(residual)
+        self.mixer.forward(x, batch, cache, residual)
+        x = self.norm_post.forward(residual)
+        self.feed_forward.forward(x, residual)
+
+
+def build_block(layer_spec, rt):
+    from .base import _REGISTRY
+    from ..config.base import ConfigError
+    try:
+        cls = _REGISTRY["block"][layer_spec.block]
+    except KeyError:
+        raise ConfigError(f"no block arrangement named {layer_spec.block!r}") from None
+    return cls(rt, layer_spec)
+
+
+register_part("block", "pre_norm", PreNormBlock, replace=True)

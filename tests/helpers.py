@@ -1,0 +1,49 @@
+"""Shared pieces of the tests: the two tiny configurations, model folders made in temporary
+directories, schedules, and the tolerances (fixed here once, for every test)."""
+import os
+
+import torch
+
+from forge_b200.config import config_from_dict
+from forge_b200.weights import write_random_model
+
+# Two tiny LLaMA configurations that differ in every size and option: layers, width, heads and groups
+# (GQA 4:2 vs MQA 3:1, the latter a group of 3), head size, a feed-forward width and a vocabulary that are
+# no powers of two, rotary base, norm eps, q/k/v bias, tied or untied head, position limit.
+TINY = {
+    "A": dict(architectures=["LlamaForCausalLM"], vocab_size=250, hidden_size=64, intermediate_size=176,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16, rope_theta=10000.0,
+              rms_norm_eps=1e-5, attention_bias=False, tie_word_embeddings=False, max_position_embeddings=768),
+    "B": dict(architectures=["LlamaForCausalLM"], vocab_size=387, hidden_size=96, intermediate_size=264,
+              num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=32, rope_theta=500000.0,
+              rms_norm_eps=1e-6, attention_bias=True, tie_word_embeddings=True, max_position_embeddings=1024),
+}
+SEEDS = {"A": 0, "B": 1}
+
+# max |engine - plain| allowed, as a fraction of max |plain logits| of the compared rows.
+# float32: the engine rounds every product and sum to fp32 (the oracle is float64) and takes rotary
+# angles in fp32.  bfloat16: activations, cache and matrices are rounded to 8 bits of mantissa.
+TOL = {"float32": 2e-4, "bfloat16": 4e-2}
+
+
+def tiny_config(name):
+    return config_from_dict(TINY[name])
+
+
+def make_model_dir(tmp_path_factory, name):
+    """A model folder with weights large enough that attention is far from uniform and every norm
+    weight and bias matters."""
+    d = str(tmp_path_factory.mktemp(f"tiny{name}"))
+    write_random_model(tiny_config(name), d, seed=SEEDS[name], std=0.12, embed_std=0.6, norm_std=0.15, bias_std=0.2)
+    return d
+
+
+def random_tokens(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def max_rel_err(got, want):
+    want = want.to(torch.float32).cpu()
+    got = got.to(torch.float32).cpu()
+    return float((got - want).abs().max() / want.abs().max())
