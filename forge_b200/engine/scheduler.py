@@ -1,0 +1,295 @@
+"""Continuous batching above the step function: admits requests, cuts prompts into portions under a token
+budget, decodes one token per running request per step, finishes and frees.
+
+Names and meanings follow the reference's RequestScheduler (include/forge/request_scheduler.h:17-53,
+src/inference/request_scheduler.cpp:157-416): submit / step / get_finished / has_pending / abort / reset,
+requests Waiting -> Prefilling -> Decoding -> Finished | Failed with finish_reason "eos" | "stop" | "length"
+| "aborted" | "error:...".  What differs, on purpose:
+  * a prompt is cut into portions so that no step exceeds ``max_tokens_per_step`` (the reference hands the
+    whole prompt to one step, :238-244); portions of prompts run beside single decoded tokens;
+  * admission needs a free request slot AND free pages for the portion (the reference looks only at how
+    full layer 0 is, :386-416);
+  * when pages run out, the most recently admitted running request is PREEMPTED: its pages go back, its
+    prompt plus the tokens it has generated become the prompt to recompute, and it returns to the front of
+    the queue; a request that cannot make progress even alone fails with "error:out_of_pages" (the
+    reference logs "cache overflow" and carries on, src/inference/kv_cache.cpp:629-633);
+  * every request has its own sampler state.
+"""
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Callable, List, Optional
+
+from ..cache import OutOfPages
+from ..sampling import RequestSampler, SamplerConfig
+from .batch import StepEntry
+
+
+class RequestStatus(Enum):
+    Waiting = 0
+    Prefilling = 1
+    Decoding = 2
+    Finished = 3
+    Failed = 4
+
+
+@dataclass
+class GenerateRequest:
+    request_id: int
+    prompt_tokens: List[int]
+    max_new_tokens: int = 256
+    eos_token_id: int = -1
+    sampler_config: SamplerConfig = field(default_factory=SamplerConfig)
+    stop_token_ids: List[int] = field(default_factory=list)
+    status: RequestStatus = RequestStatus.Waiting
+    output_tokens: List[int] = field(default_factory=list)
+    num_generated: int = 0
+    current_pos: int = 0                 # tokens of this request that are in the cache
+    finish_reason: str = ""
+    num_preemptions: int = 0
+    callback: Optional[Callable] = None  # callback(request_id, token_id, step, status)
+    sampler: Optional[RequestSampler] = None
+
+    def tokens_to_compute(self):
+        """Everything that must be in the cache before the next token can be sampled: the prompt and all
+        generated tokens (after a preemption those are recomputed like a prompt)."""
+        return self.prompt_tokens + self.output_tokens
+
+
+class RequestScheduler:
+    def __init__(self, runner, max_num_seqs=4, max_tokens_per_step=2048, sample_fn=None):
+        """runner: a ModelRunner (or anything with .manager, .plan, .admit, .release, .step).
+        sample_fn(logits, samplers) -> token list; defaults to the device sampler."""
+        self.runner = runner
+        self.manager = runner.manager
+        self.max_num_seqs = min(int(max_num_seqs), self.manager.max_requests)
+        self.max_tokens_per_step = int(max_tokens_per_step)
+        if self.max_num_seqs <= 0 or self.max_tokens_per_step <= 0:
+            raise ValueError("max_num_seqs and max_tokens_per_step must be positive")
+        if sample_fn is None:
+            from ..sampling import sample_batch
+            sample_fn = sample_batch
+        self.sample_fn = sample_fn
+        self.requests = {}
+        self.waiting = deque()
+        self.active = []                 # admission order
+        self.finished = []
+        self.next_request_id = 0
+        self.num_steps = 0
+        self.num_preemptions = 0
+        self.last_step = None            # what the last step ran, for tests and logs
+
+    # ------------------------------------------------------------------------------- public API
+    def submit(self, prompt_tokens, max_new_tokens=256, eos_token_id=-1, sampler_config=None, callback=None,
+               stop_token_ids=()):
+        prompt = [int(t) for t in prompt_tokens]
+        V, limit = self.runner.plan.vocab_size, self.runner.plan.max_positions
+        if not prompt:
+            raise ValueError("empty prompt")
+        if max_new_tokens <= 0:
+            raise ValueError("max_new_tokens must be positive")
+        bad = [t for t in prompt if not 0 <= t < V]
+        if bad:
+            raise ValueError(f"prompt token id {bad[0]} is outside [0, {V})")
+        if len(prompt) + max_new_tokens - 1 > limit:
+            raise ValueError(f"prompt of {len(prompt)} tokens plus {max_new_tokens} new ones exceeds the model's "
+                             f"{limit} positions")
+        total_pages = min(p.num_pages for p in self.manager.pools.values()) if self.manager.pools else None
+        if total_pages is not None and -(-len(prompt) // self.manager.page_size) > total_pages:
+            raise ValueError(f"prompt of {len(prompt)} tokens can never fit the cache "
+                             f"({total_pages} pages of {self.manager.page_size})")
+        cfg = sampler_config or SamplerConfig()
+        rid = self.next_request_id
+        self.next_request_id += 1
+        self.requests[rid] = GenerateRequest(rid, prompt, int(max_new_tokens), int(eos_token_id), cfg,
+                                             [int(t) for t in stop_token_ids], callback=callback,
+                                             sampler=RequestSampler(cfg))
+        self.waiting.append(rid)
+        return rid
+
+    def has_pending(self):
+        return bool(self.waiting or self.active)
+
+    def num_active(self):
+        return len(self.active)
+
+    def num_waiting(self):
+        return len(self.waiting)
+
+    def get_finished(self):
+        out, self.finished = self.finished, []
+        for r in out:
+            self.requests.pop(r.request_id, None)
+        return out
+
+    def get_all_requests(self):
+        return list(self.requests.values())
+
+    def abort(self, request_id):
+        r = self.requests.get(request_id)
+        if r is None or r.status in (RequestStatus.Finished, RequestStatus.Failed):
+            return
+        self._finish(r, RequestStatus.Failed, "aborted")
+
+    def reset(self):
+        for rid in list(self.active):
+            self.runner.release(rid)
+        self.requests.clear()
+        self.waiting.clear()
+        self.active.clear()
+        self.finished.clear()
+
+    # ------------------------------------------------------------------------------- one step
+    def plan_step(self):
+        """Decides what the next step runs.  Returns a list of (request, first token index, n tokens,
+        wants_logits).  Frees and re-queues requests when pages run out; admits waiting requests."""
+        mgr, budget = self.manager, self.max_tokens_per_step
+        plan, reserve = [], {g: 0 for g in mgr.groups}
+
+        def reserve_for(rid, n):
+            need = mgr.pages_needed(rid, n)
+            for g, k in need.items():
+                reserve[g] += k
+
+        # 1. one token for every decoding request, oldest first; preempt the youngest when pages run out
+        for rid in list(self.active):
+            if rid not in self.active:
+                continue                                     # preempted below while serving an older one
+            r = self.requests[rid]
+            if r.status != RequestStatus.Decoding or budget <= 0:
+                continue
+            while not mgr.can_append(rid, 1, reserve):
+                victim = self._youngest_other_than(rid, {p[0].request_id for p in plan})
+                if victim is None:
+                    break
+                self._preempt(victim)
+            if not mgr.can_append(rid, 1, reserve):
+                if len(self.active) == 1 and not plan:
+                    self._finish(r, RequestStatus.Failed, "error:out_of_pages")
+                else:
+                    self._preempt(rid)
+                continue
+            reserve_for(rid, 1)
+            plan.append((r, r.current_pos, 1, True))
+            budget -= 1
+
+        # 2. portions of prompts: requests already admitted first, then the queue, in order
+        def portion(r):
+            nonlocal budget
+            todo = r.tokens_to_compute()
+            left = len(todo) - r.current_pos
+            n = min(left, budget)
+            # shrink to what the free pages hold
+            while n > 0 and not mgr.can_append(r.request_id, n, reserve):
+                room = min(mgr.num_free_pages(g) - reserve[g] for g in mgr.groups) if mgr.groups else n
+                fit = max(0, room) * mgr.page_size + (-mgr.num_tokens(r.request_id)) % mgr.page_size
+                n = min(n - 1, fit)
+            if n <= 0:
+                return False
+            reserve_for(r.request_id, n)
+            plan.append((r, r.current_pos, n, r.current_pos + n == len(todo)))
+            budget -= n
+            return True
+
+        for rid in self.active:
+            r = self.requests[rid]
+            if r.status == RequestStatus.Prefilling and budget > 0:
+                portion(r)
+        while self.waiting and budget > 0 and len(self.active) < self.max_num_seqs and mgr.has_free_slot():
+            rid = self.waiting[0]
+            r = self.requests[rid]
+            self.runner.admit(rid)
+            r.status, r.current_pos = RequestStatus.Prefilling, 0
+            if not portion(r):
+                self.runner.release(rid)            # no page for even one token: stays waiting
+                r.status = RequestStatus.Waiting
+                break
+            self.waiting.popleft()
+            self.active.append(rid)
+
+        if not plan and self.active:
+            # nobody can move: every page is held by requests that all need more.  Give the youngest's back.
+            victim = self.active[-1]
+            if len(self.active) == 1:
+                self._finish(self.requests[victim], RequestStatus.Failed, "error:out_of_pages")
+            else:
+                self._preempt(victim)
+                return self.plan_step()
+        return plan
+
+    def step(self):
+        """Runs one step.  Returns False when there was nothing to do."""
+        plan = self.plan_step()
+        if not plan:
+            return False
+        entries, rows = [], []
+        for r, start, n, wants in plan:
+            toks = r.tokens_to_compute()[start:start + n]
+            entries.append(StepEntry(r.request_id, toks, [n - 1] if wants else []))
+            if wants:
+                rows.append(r)
+        self.last_step = [(r.request_id, start, n, wants) for r, start, n, wants in plan]
+        try:
+            logits = self.runner.step(entries)
+        except OutOfPages:
+            raise                                         # plan_step reserved pages; this is a bug
+        except Exception as e:                            # a failed step fails the requests that were in it
+            for r, _, _, _ in plan:
+                self._finish(r, RequestStatus.Failed, f"error:{type(e).__name__}")
+            raise
+        self.num_steps += 1
+        for r, start, n, wants in plan:
+            r.current_pos = start + n
+        if rows:
+            tokens = self.sample_fn(logits, [r.sampler for r in rows])
+            for r, tok in zip(rows, tokens):
+                self._accept(r, int(tok))
+        return True
+
+    def run(self):
+        """Steps until no request is pending; returns the finished requests."""
+        while self.has_pending():
+            if not self.step():
+                break
+        return self.get_finished()
+
+    # ------------------------------------------------------------------------------- internals
+    def _accept(self, r, tok):
+        r.output_tokens.append(tok)
+        r.num_generated += 1
+        r.status = RequestStatus.Decoding
+        if r.callback:
+            r.callback(r.request_id, tok, r.num_generated - 1, r.status)
+        if r.eos_token_id >= 0 and tok == r.eos_token_id:
+            self._finish(r, RequestStatus.Finished, "eos")
+        elif tok in r.stop_token_ids:
+            self._finish(r, RequestStatus.Finished, "stop")
+        elif r.num_generated >= r.max_new_tokens:
+            self._finish(r, RequestStatus.Finished, "length")
+
+    def _finish(self, r, status, reason):
+        rid = r.request_id
+        if rid in self.active:
+            self.active.remove(rid)
+            self.runner.release(rid)
+        elif rid in self.waiting:
+            self.waiting.remove(rid)
+        r.status, r.finish_reason = status, reason
+        self.finished.append(r)
+        if r.callback and status == RequestStatus.Failed:
+            r.callback(rid, -1, r.num_generated, status)
+
+    def _youngest_other_than(self, rid, planned):
+        for cand in reversed(self.active):
+            if cand != rid and cand not in planned:
+                return cand
+        return None
+
+    def _preempt(self, rid):
+        r = self.requests[rid]
+        self.active.remove(rid)
+        self.runner.release(rid)
+        r.status, r.current_pos = RequestStatus.Waiting, 0
+        r.num_preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(rid)

@@ -1,0 +1,137 @@
+"""Generation through the Python entry point, the scheduler on the real engine, and the command line."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import TINY, TOL, make_model_dir, max_rel_err, random_tokens
+from plain.llama import PlainLlama
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request, tmp_path_factory):
+    d = make_model_dir(tmp_path_factory, request.param)
+    return request.param, d, PlainLlama(d)
+
+
+def _greedy_with_margins(plain, prompt, n):
+    """Plain greedy tokens and, for each, the gap between the best and second-best logit relative to the
+    logit scale: where the gap is wide, any correct engine must pick the same token."""
+    ids, toks, gaps = list(prompt), [], []
+    for _ in range(n):
+        lg = plain.logits(ids)[-1]
+        top = torch.topk(lg, 2).values
+        toks.append(int(torch.argmax(lg)))
+        gaps.append(float((top[0] - top[1]) / lg.abs().max()))
+        ids.append(toks[-1])
+    return toks, gaps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_equals_plain(tiny, dtype):
+    import forge_b200 as forge
+    name, d, plain = tiny
+    prompt = random_tokens(9, TINY[name]["vocab_size"], seed=5)
+    want, gaps = _greedy_with_margins(plain, prompt, 24)
+    model = forge.Model(d, dtype=dtype, max_num_seqs=2, cache_tokens=256)
+    out = model.generate(prompt, max_new_tokens=24, do_sample=False)
+    assert out["num_prompt_tokens"] == 9 and out["num_generated_tokens"] == 24
+    assert out["finished"] and out["finish_reason"] == "length"
+    got = out["token_ids"]
+    for i, (g, w, gap) in enumerate(zip(got, want, gaps)):
+        if gap < 4 * TOL[dtype]:
+            break                      # a near-tie: later tokens may legitimately differ
+        assert g == w, f"token {i}: engine {g}, plain {w} (gap {gap:.3g})"
+    assert i >= 6, "the test model has too many near-ties to say anything"
+    # deterministic, and eos / stop end it early with the token included
+    assert model.generate(prompt, max_new_tokens=24, do_sample=False)["token_ids"] == got
+    e = model.generate(prompt, max_new_tokens=24, do_sample=False, eos_token_id=got[3])
+    k = got.index(got[3])
+    assert e["finish_reason"] == "eos" and e["token_ids"] == got[:k + 1]
+    s = model.generate(prompt, max_new_tokens=24, do_sample=False, stop_token_ids=[got[2]])
+    assert s["finish_reason"] == "stop" and s["token_ids"][-1] == got[2]
+
+
+def test_temperature_sampling_follows_the_seed(tiny):
+    import forge_b200 as forge
+    name, d, plain = tiny
+    prompt = random_tokens(7, TINY[name]["vocab_size"], seed=6)
+    model = forge.Model(d, dtype="float32", max_num_seqs=2, cache_tokens=256)
+    a = model.generate(prompt, max_new_tokens=16, temperature=0.8, seed=11)["token_ids"]
+    b = model.generate(prompt, max_new_tokens=16, temperature=0.8, seed=11)["token_ids"]
+    c = model.generate(prompt, max_new_tokens=16, temperature=0.8, seed=12)["token_ids"]
+    assert a == b and a != c
+    # every drawn token is the one whose interval of the plain distribution holds the generator's number
+    from forge_b200.sampling import XorShift64
+    rng, ids = XorShift64(11), list(prompt)
+    for tok in a:
+        p = torch.softmax(plain.logits(ids)[-1] / 0.8, dim=0)
+        cdf = torch.cumsum(p, 0)
+        u = rng.uniform()
+        lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+        assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4
+        ids.append(tok)
+    for kw in (dict(top_k=5), dict(top_p=0.8), dict(repeat_penalty=1.3), dict(top_k=40, top_p=0.9, repeat_penalty=1.1)):
+        out = model.generate(prompt, max_new_tokens=8, temperature=0.7, seed=3, **kw)
+        assert out["num_generated_tokens"] == 8
+
+
+def test_context_forward_is_incremental(tiny):
+    import forge_b200 as forge
+    name, d, plain = tiny
+    ids = random_tokens(11, TINY[name]["vocab_size"], seed=8)
+    want = plain.logits(ids).float()
+    ctx = forge.Model(d, dtype="float32", max_num_seqs=2, cache_tokens=256).create_context()
+    full = torch.from_numpy(ctx.forward(ids, 0))
+    assert full.shape == want.shape and max_rel_err(full, want) <= TOL["float32"]
+    ctx.reset_kv()
+    parts = [torch.from_numpy(ctx.forward(ids[:5], 0))] + [torch.from_numpy(ctx.forward([t], 5 + i)) for i, t in enumerate(ids[5:])]
+    assert max_rel_err(torch.cat(parts), want) <= TOL["float32"]
+    with pytest.raises(ValueError, match="start_pos"):
+        ctx.forward([1], 3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scheduler_many_requests_few_pages(tiny, dtype):
+    """Eight requests through four slots and a cache so small that requests are preempted: every request
+    still generates exactly what it generates alone."""
+    import forge_b200 as forge
+    name, d, plain = tiny
+    V = TINY[name]["vocab_size"]
+    prompts = [random_tokens(n, V, seed=20 + i) for i, n in enumerate([5, 17, 33, 9, 40, 3, 26, 12])]
+    model = forge.Model(d, dtype=dtype, max_num_seqs=4, cache_tokens=160, max_tokens_per_step=24)
+    alone = [model.generate(p, max_new_tokens=20, do_sample=False)["token_ids"] for p in prompts]
+    sched = forge.RequestScheduler(model, max_num_seqs=4)
+    ids = [sched.submit(p, max_new_tokens=20, sampler_config=forge.SamplerConfig(do_sample=False)) for p in prompts]
+    done = {r.request_id: r for r in sched.run()}
+    assert sched.num_preemptions >= 1, "the cache was meant to be too small"
+    for rid, want in zip(ids, alone):
+        got = done[rid].output_tokens
+        if dtype == "float32":
+            assert got == want
+        else:   # a bf16 near-tie may flip when the batch around a request changes; most requests agree wholly
+            assert got[:3] == want[:3]
+        assert done[rid].finish_reason == "length"
+    model.runner.manager.check()
+    assert model.runner.manager.live_requests() == []
+
+
+def test_command_line(tiny):
+    name, d, plain = tiny
+    prompt = random_tokens(6, TINY[name]["vocab_size"], seed=9)
+    want = plain.generate_greedy(prompt, 5)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p",
+                           " ".join(map(str, prompt)), "-n", "5", "--temp", "0", "--no-stream", "--dtype", "float32"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    first = proc.stdout.strip().splitlines()[0]
+    assert [int(t) for t in first.split()] == want
+    assert "6 prompt" in proc.stdout and "5 generated" in proc.stdout
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p", "1", "-ngl", "0"],
+                         capture_output=True, text=True, timeout=60)
+    assert bad.returncode != 0 and "does not have" in bad.stderr

@@ -1,0 +1,174 @@
+"""The scheduler's decisions with a fake step function: a real CacheManager, no model, no GPU."""
+from types import SimpleNamespace
+
+import pytest
+
+from forge_b200.cache import CacheManager, GroupSpec
+from forge_b200.engine.scheduler import RequestScheduler, RequestStatus
+from forge_b200.sampling import SamplerConfig, XorShift64
+
+
+class FakeRunner:
+    """Stands in for ModelRunner: appends tokens to the real cache manager and returns 'logits' that are
+    just the (request, position) of each wanted row."""
+
+    def __init__(self, pages=8, page_size=4, max_requests=4, vocab=100, max_positions=64):
+        self.manager = CacheManager([GroupSpec("g", pages)], page_size, max_requests)
+        self.plan = SimpleNamespace(vocab_size=vocab, max_positions=max_positions)
+        self.steps = []
+
+    def admit(self, rid):
+        return self.manager.admit(rid)
+
+    def release(self, rid):
+        self.manager.free(rid)
+
+    def step(self, entries):
+        self.steps.append([(e.req_id, len(e.tokens), list(e.want)) for e in entries])
+        rows = []
+        for e in entries:
+            start = self.manager.num_tokens(e.req_id)
+            self.manager.append(e.req_id, len(e.tokens))
+            rows += [(e.req_id, start + w, e.tokens[w]) for w in e.want]
+        self.manager.check()
+        return rows
+
+
+def next_token(rows, samplers):
+    """'Samples' token = (last input token + 1) % 100: generation is a counter, easy to check."""
+    return [(tok + 1) % 100 for _, _, tok in rows]
+
+
+def make(pages=8, max_num_seqs=4, budget=16, **kw):
+    r = FakeRunner(pages=pages, **kw)
+    return r, RequestScheduler(r, max_num_seqs=max_num_seqs, max_tokens_per_step=budget, sample_fn=next_token)
+
+
+def test_prompt_is_cut_under_the_token_budget_and_decodes_follow():
+    r, s = make(pages=16, budget=5)
+    rid = s.submit(list(range(10, 22)), max_new_tokens=3)          # 12 prompt tokens
+    assert s.step() and r.steps[-1] == [(rid, 5, [])]
+    assert s.step() and r.steps[-1] == [(rid, 5, [])]
+    assert s.step() and r.steps[-1] == [(rid, 2, [1])]              # last portion: logits wanted at its end
+    assert s.requests[rid].status == RequestStatus.Decoding and s.requests[rid].output_tokens == [22]
+    assert s.step() and r.steps[-1] == [(rid, 1, [0])]
+    assert s.step()
+    (done,) = s.get_finished()
+    assert done.output_tokens == [22, 23, 24] and done.finish_reason == "length" and done.num_generated == 3
+    assert not s.has_pending() and not s.step()
+    assert r.manager.num_free_pages("g") == 16
+
+
+def test_decodes_go_first_and_prompts_fill_the_rest():
+    r, s = make(pages=32, budget=8)
+    a = s.submit([1, 2, 3], max_new_tokens=10)
+    s.step()                                                        # a prefilled, now decoding
+    b = s.submit(list(range(20)), max_new_tokens=2)
+    s.step()
+    assert r.steps[-1] == [(a, 1, [0]), (b, 7, [])]                 # 1 decode + 7 of b's prompt = budget 8
+    s.step()
+    assert r.steps[-1] == [(a, 1, [0]), (b, 7, [])]
+    s.step()
+    assert r.steps[-1] == [(a, 1, [0]), (b, 6, [5])]
+
+
+def test_admission_is_fifo_and_bounded_by_max_num_seqs():
+    r, s = make(pages=32, max_num_seqs=2, budget=64)
+    ids = [s.submit([5, 6, 7], max_new_tokens=2) for _ in range(4)]
+    s.step()
+    assert [e[0] for e in r.steps[-1]] == ids[:2] and s.num_waiting() == 2 and s.num_active() == 2
+    s.step()                                                        # both finish (2 tokens each)
+    assert sorted(x.request_id for x in s.get_finished()) == ids[:2]
+    s.step()
+    assert [e[0] for e in r.steps[-1]] == ids[2:]
+    s.run()
+    assert r.manager.num_free_pages("g") == 32
+
+
+def test_finish_reasons():
+    r, s = make(pages=16)
+    a = s.submit([10], max_new_tokens=50, eos_token_id=13)
+    b = s.submit([20], max_new_tokens=50, stop_token_ids=[24])
+    c = s.submit([30], max_new_tokens=2)
+    done = {x.request_id: x for x in s.run()}
+    assert (done[a].finish_reason, done[a].output_tokens) == ("eos", [11, 12, 13])
+    assert (done[b].finish_reason, done[b].output_tokens) == ("stop", [21, 22, 23, 24])
+    assert (done[c].finish_reason, done[c].output_tokens) == ("length", [31, 32])
+    assert all(x.status == RequestStatus.Finished for x in done.values())
+
+
+def test_abort_frees_pages():
+    r, s = make(pages=8)
+    a = s.submit([1] * 9, max_new_tokens=20)
+    s.step()
+    assert r.manager.num_free_pages("g") == 5
+    s.abort(a)
+    (x,) = s.get_finished()
+    assert x.status == RequestStatus.Failed and x.finish_reason == "aborted"
+    assert r.manager.num_free_pages("g") == 8 and not s.has_pending()
+
+
+def test_pages_run_out_youngest_is_preempted_and_recomputed():
+    # 6 pages of 4 tokens.  a and b each take 2 pages for their 8-token prompts, then decode: each needs a
+    # 3rd page after 1 token (fine: 6 pages), and a 4th after 5 tokens: not both.
+    r, s = make(pages=6, budget=64)
+    a = s.submit(list(range(8)), max_new_tokens=12)
+    b = s.submit(list(range(50, 58)), max_new_tokens=12)
+    done = {x.request_id: x for x in s.run()}
+    assert s.num_preemptions >= 1 and done[b].num_preemptions >= 1 and done[a].num_preemptions == 0
+    # preemption does not change what is generated
+    assert done[a].output_tokens == list(range(8, 20)) and done[b].output_tokens == list(range(58, 70))
+    assert done[a].finish_reason == done[b].finish_reason == "length"
+    # b's recompute step fed prompt + generated tokens as one prompt
+    assert any(e[0] == b and e[1] > 8 for step in r.steps for e in step)
+    assert r.manager.num_free_pages("g") == 6
+    r.manager.check()
+
+
+def test_a_request_that_cannot_fit_alone_fails_cleanly():
+    r, s = make(pages=3, budget=64, max_positions=64)
+    a = s.submit(list(range(10)), max_new_tokens=20)               # needs 8 pages in the end, pool has 3
+    (x,) = s.run()
+    assert x.status == RequestStatus.Failed and x.finish_reason == "error:out_of_pages"
+    assert x.output_tokens == [10, 11, 12]                          # what fit was generated
+    assert r.manager.num_free_pages("g") == 3
+    with pytest.raises(ValueError, match="never fit"):
+        s.submit(list(range(13)), max_new_tokens=1)
+
+
+def test_submit_refuses_bad_requests():
+    r, s = make()
+    with pytest.raises(ValueError, match="empty"):
+        s.submit([])
+    with pytest.raises(ValueError, match="outside"):
+        s.submit([100])
+    with pytest.raises(ValueError, match="positions"):
+        s.submit([1] * 10, max_new_tokens=56)
+    with pytest.raises(ValueError, match="positive"):
+        s.submit([1], max_new_tokens=0)
+
+
+def test_prompt_portion_shrinks_to_the_free_pages():
+    r, s = make(pages=4, budget=64)
+    a = s.submit(list(range(8)), max_new_tokens=4)                  # 2 pages, then a 3rd while decoding
+    s.step()
+    b = s.submit(list(range(20, 31)), max_new_tokens=1)             # 11 tokens = 3 pages; only 2 free after a's decode
+    s.step()
+    assert r.steps[-1] == [(a, 1, [0]), (b, 4, [])]                  # a's decode took a page; one page for b
+    r.manager.check()
+    done = {x.request_id: x for x in s.run()}
+    assert done[a].output_tokens == [8, 9, 10, 11] and done[b].output_tokens == [31]
+
+
+def test_xorshift_matches_the_reference_recurrence():
+    g = XorShift64(0)
+    assert g.state == 12345
+    x = 12345
+    for _ in range(5):
+        x ^= (x << 13) & (2**64 - 1)
+        x ^= x >> 7
+        x ^= (x << 17) & (2**64 - 1)
+        assert g.uniform() == float(x & 0x7FFFFFFF) / float(0x7FFFFFFF)
+    assert XorShift64(7).state == 7
+    assert SamplerConfig(temperature=0.0).greedy and SamplerConfig(do_sample=False).greedy
+    assert not SamplerConfig(temperature=0.8).greedy
