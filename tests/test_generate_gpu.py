@@ -43,11 +43,14 @@ def test_greedy_generation_equals_plain(tiny, dtype):
     assert out["num_prompt_tokens"] == 9 and out["num_generated_tokens"] == 24
     assert out["finished"] and out["finish_reason"] == "length"
     got = out["token_ids"]
+    agree = 0
     for i, (g, w, gap) in enumerate(zip(got, want, gaps)):
-        if gap < 4 * TOL[dtype]:
-            break                      # a near-tie: later tokens may legitimately differ
-        assert g == w, f"token {i}: engine {g}, plain {w} (gap {gap:.3g})"
-    assert i >= 6, "the test model has too many near-ties to say anything"
+        if g != w:
+            # only a near-tie of the plain logits may be decided differently; after it the texts diverge
+            assert gap < 2 * TOL[dtype], f"token {i}: engine {g}, plain {w} (gap {gap:.3g})"
+            break
+        agree += 1
+    assert agree >= 6, "the texts part too early to say anything"
     # deterministic, and eos / stop end it early with the token included
     assert model.generate(prompt, max_new_tokens=24, do_sample=False)["token_ids"] == got
     e = model.generate(prompt, max_new_tokens=24, do_sample=False, eos_token_id=got[3])
@@ -126,7 +129,7 @@ def test_command_line(tiny):
     prompt = random_tokens(6, TINY[name]["vocab_size"], seed=9)
     want = plain.generate_greedy(prompt, 5)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p",
-                           " ".join(map(str, prompt)), "-n", "5", "--temp", "0", "--no-stream", "--dtype", "float32"],
+                           " ".join(map(str, prompt)), "-n", "5", "--temp", "0", "--repeat-penalty", "1.0", "--no-stream", "--dtype", "float32"],
                           capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stderr[-2000:]
     first = proc.stdout.strip().splitlines()[0]
