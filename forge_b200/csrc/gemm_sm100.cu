@@ -1,0 +1,323 @@
+// bf16 matrix product on the 5th-generation tensor cores:  C[M,N] = A[M,K] . W[N,K]^T, fp32 accumulation
+// in tensor memory, operands brought to shared memory by TMA, epilogue fused.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0     TMA producer: for each (tile, k-block) waits for a free stage, arms the stage's barrier with
+//              the byte count and issues two tile loads (A box 128 x 64, W box BN x 64, 128-byte swizzle).
+//   warp 1     MMA issuer: owns the TMEM allocation (two accumulators of BN columns), waits for a full
+//              stage, issues four tcgen05.mma (K = 16 each) per k-block and commits the stage's "empty"
+//              barrier; after the last k-block commits the accumulator's "full" barrier.
+//   warps 2-5  epilogue: each warp reads its quarter of the 128 TMEM lanes (one output row per thread),
+//              32 columns at a time, applies the epilogue and stores to global memory, then releases the
+//              accumulator.  Two accumulators let the epilogue of tile i overlap the MMAs of tile i+1.
+// Tiles are walked with the row-tile index fastest, so CTAs that run together share a W tile in L2.
+// Edges: TMA fills out-of-range rows and the K tail with zeros; the epilogue masks rows >= M, cols >= N.
+//
+// Epilogues (all arithmetic fp32):
+//   0  C fp32  = acc + bias
+//   1  C fp32 += acc + bias                      (the residual stream)
+//   2  C bf16  = acc + bias
+//   3  C bf16[M, N/2]: out[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]     (gate/up rows interleaved in W)
+// Replaces the reference's cuBLAS GemmEx / tiled GEMM / GEMV trio and its separate bias-add, residual-add
+// and silu-multiply launches (src/operators/cuda/cuda_quant.cu:582-599, cuda_gemm.cu:7-55,
+// cuda_elementwise.cu:8-48).
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kSmemLimit = 227 * 1024;
+
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACCUM_F32 = 1, EPI_STORE_BF16 = 2, EPI_SWIGLU_BF16 = 3 };
+
+struct GemmParams {
+    void* C;
+    const float* bias;
+    int M, N, K;
+    int epilogue;
+    int* status;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int kStageBytes = (BM + BN) * BK * 2;
+    static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes > 12 ? 12 : (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers*/;
+};
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                  const GemmParams p) {
+    using C = Cfg<BN>;
+    constexpr int kStages = C::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern to line up with the descriptors
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes);
+    uint64_t* full = bars;                       // [kStages]  TMA -> MMA
+    uint64_t* empty = bars + kStages;            // [kStages]  MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kStages;     // [2]        MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2]      epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        mbar_fence_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;       // k-blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort, p.status))) break;
+                    mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                    uint8_t* a_dst = tiles + s * C::kStageBytes;
+                    tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, m0);
+                    tma_load_2d(a_dst + BM * BK * 2, &tmap_w, &full[s], kb * BK, n0);
+                }
+            }
+            if (!ok) {
+                // drain: wait (bounded) for the copies already issued so none lands after the CTA is gone
+                const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0;
+                for (uint32_t j = first; j < it; ++j) {
+                    const unsigned long long t0 = global_ns();
+                    while (!mbar_try_wait(&full[j % kStages], (j / kStages) & 1) && global_ns() - t0 < 100000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+            uint32_t it = 0;
+            bool ok = true;
+            int local = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                const int a = local & 1;
+                const uint32_t aph = (local >> 1) & 1;
+                if (!(ok = mbar_wait(&acc_empty[a], aph ^ 1, abort, p.status))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + a * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(&full[s], ph, abort, p.status))) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
+                    const uint32_t w_addr = a_addr + BM * BK * 2;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        umma_bf16(d_tmem, umma_desc_k_sw128(a_addr + k * UMMA_K * 2),
+                                  umma_desc_k_sw128(w_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[s]);       // stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter .. +31
+        const int row_in_tile = quarter * 32 + lane;
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int a = local & 1;
+            const uint32_t aph = (local >> 1) & 1;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            if (!(ok = mbar_wait(&acc_full[a], aph, abort, p.status))) break;
+            tc_fence_after_sync();
+            const int m = m0 + row_in_tile;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                if constexpr (BN >= 32) {
+                    tmem_ld_32x32b_x32(t_row + c, r);
+                } else {
+                    uint32_t h[16];
+                    tmem_ld_32x32b_x16(t_row + c, h);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { r[i] = h[i]; r[i + 16] = 0; }
+                }
+                tmem_ld_wait();
+                const int n = n0 + c;
+                if (m < p.M && n < p.N) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    const int width = min(min(32, BN), p.N - n);
+                    if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) if (i < width) v[i] += p.bias[n + i];
+                    }
+                    if (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) {
+                        float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                        const bool acc = p.epilogue == EPI_ACCUM_F32;
+                        if (width == 32 && (p.N & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                if (acc) {
+                                    const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + i) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) if (i < width) dst[i] = acc ? dst[i] + v[i] : v[i];
+                        }
+                    } else if (p.epilogue == EPI_STORE_BF16) {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
+                        if (width == 32 && (p.N & 7) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                                uint4 o;
+                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                *reinterpret_cast<uint4*>(dst + i) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    } else {   // EPI_SWIGLU_BF16: N is even, pairs never straddle a 32-column chunk
+                        const int half_n = p.N >> 1;
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * half_n + (n >> 1);
+                        if (width == 32 && (half_n & 7) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 8) {
+                                uint32_t w4[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const int q = 2 * (i + 2 * j);
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(silu(v[q]) * v[q + 1], silu(v[q + 2]) * v[q + 3]);
+                                    w4[j] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                *reinterpret_cast<uint4*>(dst + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(silu(v[2 * i]) * v[2 * i + 1]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[a]);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+int g_num_sms = 0;
+
+template <int BN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
+                                                 C::kSmemBytes, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+    gemm_sm100_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tw, p);
+    return forge::check_launch("gemm_sm100");
+}
+
+}  // namespace
+
+// A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
+// epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
+// tile_n: 0 = choose, else one of 16, 32, 64, 128, 256.  status: device int, bit 1 raised if a wait ran out.
+extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
+                                int K, int epilogue, int tile_n, void* reserved, cudaStream_t stream) {
+    (void)reserved;
+    if (M < 0 || N <= 0 || K <= 0) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return FORGE_OK;
+    if (K % 8 != 0) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: K=%d is not a multiple of 8 (TMA row stride)", K);
+    if (epilogue < 0 || epilogue > 3) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: unknown epilogue %d", epilogue);
+    if (epilogue == EPI_SWIGLU_BF16 && (N & 1)) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: swiglu epilogue needs even N, got %d", N);
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    int bn = tile_n;
+    if (bn == 0) {
+        // few rows (decode): narrow tiles so that many SMs stream W; many rows: the widest tile whose tile
+        // count wastes the least of the last wave
+        if (M <= BM) {
+            bn = N >= 64 * g_num_sms ? 64 : (N >= 32 * g_num_sms ? 32 : 16);
+        } else {
+            const long tm = (M + BM - 1) / BM;
+            long best = -1;
+            for (int cand : {256, 128}) {
+                const long tiles = tm * ((N + cand - 1) / cand);
+                const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * cand;
+                if (best < 0 || cost < best) { best = cost; bn = cand; }
+            }
+        }
+    }
+    const char* err = nullptr;
+    CUtensorMap ta, tw;
+    if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+    if (!bf16_tile_map(W, N, K, bn, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+    GemmParams p{C, bias, M, N, K, epilogue, status};
+    switch (bn) {
+        case 256: return launch<256>(ta, tw, p, stream);
+        case 128: return launch<128>(ta, tw, p, stream);
+        case 64: return launch<64>(ta, tw, p, stream);
+        case 32: return launch<32>(ta, tw, p, stream);
+        case 16: return launch<16>(ta, tw, p, stream);
+        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128 or 256, got %d", bn);
+    }
+}
+
+extern "C" const char* forge_last_error() { return forge::error_buffer(); }

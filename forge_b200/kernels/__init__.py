@@ -252,5 +252,63 @@ def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_d
                                 n_kv_heads, head_dim, page_size, window=window or 0, scale=scale)
 
 
-_TENSOR_CORE_GEMM = False
+EPILOGUES = {"none": 0, "accumulate": 1, "cast": 2, "swiglu": 3}
+
+
+def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0, status=None, out=None):
+    """bf16 x [M,K] . w [N,K]^T on the tcgen05 tensor cores, fp32 accumulation.
+    epilogue "none": fp32 [M,N] (added into ``accumulate_into`` when given); "cast": bf16 [M,N];
+    "swiglu": bf16 [M,N/2] = silu(y[:,2j]) * y[:,2j+1]."""
+    lib = library("gemm_sm100")
+    (M, K), (N, K2) = x.shape, w.shape
+    if K != K2:
+        raise KernelError(f"gemm_sm100: x {tuple(x.shape)} does not match w {tuple(w.shape)}")
+    if epilogue == "none":
+        if accumulate_into is not None:
+            out, code = accumulate_into, EPILOGUES["accumulate"]
+        else:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device) if out is None else out
+            code = EPILOGUES["none"]
+        want_shape, want_dtype = (M, N), torch.float32
+    elif epilogue == "cast":
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if out is None else out
+        code, want_shape, want_dtype = EPILOGUES["cast"], (M, N), torch.bfloat16
+    elif epilogue == "swiglu":
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device) if out is None else out
+        code, want_shape, want_dtype = EPILOGUES["swiglu"], (M, N // 2), torch.bfloat16
+    else:
+        raise KernelError(f"gemm_sm100: unknown epilogue {epilogue!r}")
+    if tuple(out.shape) != want_shape:
+        raise KernelError(f"gemm_sm100: output has shape {tuple(out.shape)}, expected {want_shape}")
+    if status is None:
+        status = _gemm_status(x.device)
+    _check(lib, lib.forge_gemm_sm100(_need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2),
+                                     _opt(bias, "bias", torch.float32), _need(out, "out", want_dtype),
+                                     _need(status, "status", torch.int32), M, N, K, code, int(tile_n), None, _stream()),
+           "gemm_sm100")
+    return out
+
+
+_status_words = {}
+
+
+def _gemm_status(device):
+    """One int32 per device on which tensor-core kernels raise bit 1 when a bounded wait runs out."""
+    key = str(device)
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_kernel_status(device="cuda:0"):
+    """Synchronises and raises if a tensor-core kernel gave up on a wait since the last check."""
+    w = _status_words.get(str(torch.device(device)))
+    if w is not None:
+        v = int(w.item())
+        if v:
+            w.zero_()
+            raise KernelError(f"a tensor-core kernel reported status {v:#x} (a bounded wait ran out)")
+
+
+_TENSOR_CORE_GEMM = True
 _TENSOR_CORE_ATTENTION = False

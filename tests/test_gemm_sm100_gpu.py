@@ -1,0 +1,73 @@
+"""The tcgen05/TMA matrix product against a plain fp64 product, at sizes that are not the engine's:
+row, column and reduction tails, every tile width, every epilogue."""
+import pytest
+import torch
+
+from plain import kernels_ref as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+def _k():
+    from forge_b200 import kernels
+    return kernels
+
+
+SHAPES = [(128, 256, 64), (1, 48, 8), (7, 100, 72), (130, 257, 200), (300, 515, 1032), (64, 2560, 2048),
+          (1000, 384, 96), (257, 130, 4104)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("tile_n", [0, 16, 32, 64, 128, 256])
+def test_plain_product_every_tile_width(M, N, K, tile_n):
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    ref = R.gemm_ref(a, w, bias)
+    got = k.gemm_sm100(a, w, bias=bias, tile_n=tile_n)
+    k.check_kernel_status()
+    # fp32 accumulation of exact bf16 products: the error is a few fp32 roundings of the row's magnitude
+    assert (got - ref).abs().max() <= 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 64, 64), (200, 330, 264), (129, 2048, 520)])
+def test_epilogues(M, N, K):
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.2)
+    ref = R.gemm_ref(a, w)
+    tol = 1e-5 * ref.abs().max() * 3
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    got = k.gemm_sm100(a, w, accumulate_into=res.clone())
+    assert (got - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max()
+    got = k.gemm_sm100(a, w, epilogue="cast")
+    assert got.dtype == torch.bfloat16 and (got.float() - ref).abs().max() <= 8e-3 * ref.abs().max()
+    got = k.gemm_sm100(a, w, epilogue="swiglu")
+    want = R.silu_mul_interleaved_ref(ref)
+    assert got.shape == (M, N // 2) and (got.float() - want).abs().max() <= 8e-3 * want.abs().max() + 1e-6
+    k.check_kernel_status()
+
+
+def test_many_tiles_per_cta_and_both_accumulators():
+    """More tiles than SMs, so every CTA walks several tiles and alternates its two accumulators."""
+    k = _k()
+    a, w = _rand(1536, 256), _rand(4096, 256, seed=1)
+    ref = R.gemm_ref(a, w)
+    for tile_n in (128, 256):
+        got = k.gemm_sm100(a, w, tile_n=tile_n)
+        assert (got - ref).abs().max() <= 2e-5 * ref.abs().max()
+    k.check_kernel_status()
+
+
+def test_refuses_what_it_cannot_do():
+    k = _k()
+    with pytest.raises(k.KernelError, match="multiple of 8"):
+        k.gemm_sm100(_rand(4, 12), _rand(8, 12))
+    with pytest.raises(k.KernelError, match="even"):
+        k.gemm_sm100(_rand(4, 16), _rand(7, 16), epilogue="swiglu")
+    assert not k.gemm_sm100_supports(64, 12) and k.gemm_sm100_supports(64, 16)
