@@ -46,37 +46,55 @@ class StepBatch:
     attention_plan: dict = field(default_factory=dict)
 
 
-def build_step_batch(entries, manager, device, max_pages, status=None):
+@dataclass
+class HostStep:
+    """A step laid out on the host, before it is copied to the device."""
+    token_ids: List[int]
+    positions: List[int]
+    tok_req: List[int]
+    q_start: List[int]
+    context_before: List[int]
+    slots: List[int]
+    rows: List[int]
+    slot_maps: Dict[str, List[int]]
+    tables: Dict[str, List[List[int]]]
+
+
+def layout_step(entries, manager):
     """Appends every entry's tokens to its request in the cache manager (allocating pages) and lays the
-    step out as device arrays.  Raises OutOfPages before touching anything if a request cannot grow."""
+    step out as flat host lists.  Raises OutOfPages before touching anything if the step cannot grow."""
     reserve = {g: 0 for g in manager.groups}
     for e in entries:
-        need = manager.pages_needed(e.req_id, len(e.tokens))
-        for g, n in need.items():
+        for g, n in manager.pages_needed(e.req_id, len(e.tokens)).items():
             reserve[g] += n
     for g, n in reserve.items():
         if n > manager.num_free_pages(g):
             from ..cache import OutOfPages
             raise OutOfPages(f"step needs {n} pages of group {g!r}, {manager.num_free_pages(g)} free")
-
-    token_ids, positions, tok_req, q_start, ctx_before, slots, rows = [], [], [], [0], [], [], []
-    slot_maps = {g: [] for g in manager.groups}
+    hs = HostStep([], [], [], [0], [], [], [], {g: [] for g in manager.groups}, {g: [] for g in manager.groups})
     for s, e in enumerate(entries):
-        n0 = manager.num_tokens(e.req_id)
-        new_slots = manager.append(e.req_id, len(e.tokens))
-        for g in slot_maps:
-            slot_maps[g].extend(new_slots[g])
-        base = len(token_ids)
-        token_ids.extend(e.tokens)
-        positions.extend(range(n0, n0 + len(e.tokens)))
-        tok_req.extend([s] * len(e.tokens))
-        q_start.append(base + len(e.tokens))
-        ctx_before.append(n0)
-        slots.append(manager.slot(e.req_id))
+        n0, n = manager.num_tokens(e.req_id), len(e.tokens)
+        new_slots = manager.append(e.req_id, n)
+        for g in hs.slot_maps:
+            hs.slot_maps[g].extend(new_slots[g])
+            hs.tables[g].append(manager.block_table(e.req_id, g))
+        base = len(hs.token_ids)
+        hs.token_ids.extend(e.tokens)
+        hs.positions.extend(range(n0, n0 + n))
+        hs.tok_req.extend([s] * n)
+        hs.q_start.append(base + n)
+        hs.context_before.append(n0)
+        hs.slots.append(manager.slot(e.req_id))
         for w in e.want:
-            if not 0 <= w < len(e.tokens):
-                raise ValueError(f"request {e.req_id!r}: wanted index {w} outside its {len(e.tokens)} tokens")
-            rows.append(base + w)
+            if not 0 <= w < n:
+                raise ValueError(f"request {e.req_id!r}: wanted index {w} outside its {n} tokens")
+            hs.rows.append(base + w)
+    return hs
+
+
+def build_step_batch(entries, manager, device, max_pages, status=None):
+    """Lays the step out (see ``layout_step``) and copies it to the device as one StepBatch."""
+    hs = layout_step(entries, manager)
 
     def dev(lst):
         return torch.tensor(lst, dtype=torch.int32, device=device)
@@ -84,14 +102,14 @@ def build_step_batch(entries, manager, device, max_pages, status=None):
     groups = {}
     for g in manager.groups:
         table = torch.full((len(entries), max_pages), -1, dtype=torch.int32)
-        for s, e in enumerate(entries):
-            t = manager.block_table(e.req_id, g)
+        for s, t in enumerate(hs.tables[g]):
             if len(t) > max_pages:
-                raise ValueError(f"request {e.req_id!r} holds {len(t)} pages, tables have room for {max_pages}")
+                raise ValueError(f"request {entries[s].req_id!r} holds {len(t)} pages, tables have room for {max_pages}")
             table[s, :len(t)] = torch.tensor(t, dtype=torch.int32)
-        groups[g] = GroupBatch(table.to(device), dev(slot_maps[g]))
+        groups[g] = GroupBatch(table.to(device), dev(hs.slot_maps[g]))
     return StepBatch(
-        num_tokens=len(token_ids), num_requests=len(entries), num_logits=len(rows),
-        token_ids=dev(token_ids), positions=dev(positions), tok_req=dev(tok_req), q_start=dev(q_start),
-        context_before=dev(ctx_before), slots=dev(slots), logits_rows=dev(rows) if rows else None, groups=groups,
-        status=status, host_q_start=q_start, host_context_before=ctx_before, host_slots=slots)
+        num_tokens=len(hs.token_ids), num_requests=len(entries), num_logits=len(hs.rows),
+        token_ids=dev(hs.token_ids), positions=dev(hs.positions), tok_req=dev(hs.tok_req), q_start=dev(hs.q_start),
+        context_before=dev(hs.context_before), slots=dev(hs.slots), logits_rows=dev(hs.rows) if hs.rows else None,
+        groups=groups, status=status, host_q_start=hs.q_start, host_context_before=hs.context_before,
+        host_slots=hs.slots)

@@ -12,7 +12,8 @@ from ..cache import CacheStorage, OutOfPages, bytes_per_page
 from ..config import load_config
 from ..parts import Runtime
 from ..weights.loader import load_tensors
-from .batch import StepEntry, build_step_batch
+from .batch import StepEntry, build_step_batch, layout_step
+from .decode_graph import DecodeGraph
 from .model import Model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -35,7 +36,7 @@ def resolve_dtype(dtype):
 
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
-                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6):
+                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
         ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the
         free device memory holds, capped by max_requests * max positions)."""
@@ -73,6 +74,8 @@ class ModelRunner:
         self.manager = self.storage.manager
         self.max_pages_per_request = min(self.num_pages, -(-self.plan.max_positions // self.page_size))
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.cuda_graphs = bool(cuda_graphs)
+        self._decode_graphs = {}
 
     # ---------------------------------------------------------------------------------- requests
     def admit(self, req_id):
@@ -109,12 +112,31 @@ class ModelRunner:
         (None if nothing is wanted).  Raises StepError / OutOfPages before anything has run."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self.validate(entries)
+        if self.cuda_graphs and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            return self.decode_step(entries)[0]
         batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
         self.storage.zero_state_slots(self.manager.take_fresh_slots())
         logits = self.model.forward(batch, self.storage.layers)
         for e in entries:
             self.manager.release_out_of_window(e.req_id)
         return logits
+
+    def decode_step(self, entries, tokens_on_device=False):
+        """One token for each entry, logits wanted for all: replays the CUDA graph captured for this number
+        of requests.  Returns (logits [S,V], greedy tokens int32 [S]); both are overwritten by the next
+        decode step of the same size.  Entries must have been validated.  ``tokens_on_device``: the
+        entries' token ids are placeholders; the step consumes the previous decode step's greedy tokens
+        straight from device memory."""
+        S = len(entries)
+        g = self._decode_graphs.get(S)
+        if g is None:
+            g = self._decode_graphs[S] = DecodeGraph(self, S)
+        hs = layout_step(entries, self.manager)
+        self.storage.zero_state_slots(self.manager.take_fresh_slots())
+        out = g.run(hs, tokens_on_device=tokens_on_device)
+        for e in entries:
+            self.manager.release_out_of_window(e.req_id)
+        return out
 
     def check_status(self):
         """Reads the device error word (synchronises); raises if a kernel flagged a problem."""

@@ -229,8 +229,14 @@ class RequestScheduler:
             if wants:
                 rows.append(r)
         self.last_step = [(r.request_id, start, n, wants) for r, start, n, wants in plan]
+        decode_only = all(n == 1 and wants for _, _, n, wants in plan) and getattr(self.runner, "cuda_graphs", False)
+        greedy = None
         try:
-            logits = self.runner.step(entries)
+            if decode_only:
+                self.runner.validate(entries)
+                logits, greedy = self.runner.decode_step(entries)
+            else:
+                logits = self.runner.step(entries)
         except OutOfPages:
             raise                                         # plan_step reserved pages; this is a bug
         except Exception as e:                            # a failed step fails the requests that were in it
@@ -241,7 +247,13 @@ class RequestScheduler:
         for r, start, n, wants in plan:
             r.current_pos = start + n
         if rows:
-            tokens = self.sample_fn(logits, [r.sampler for r in rows])
+            if greedy is not None and all(r.sampler.config.greedy and r.sampler.config.repeat_penalty == 1.0
+                                          for r in rows):
+                tokens = greedy.tolist()                  # argmax ran inside the decode graph
+                for r, tok in zip(rows, tokens):
+                    r.sampler.record(tok)
+            else:
+                tokens = self.sample_fn(logits, [r.sampler for r in rows])
             for r, tok in zip(rows, tokens):
                 self._accept(r, int(tok))
         return True

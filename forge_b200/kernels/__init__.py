@@ -76,7 +76,20 @@ def library(name):
     return lib
 
 
+_launches = [0]
+
+
+def launch_count():
+    """How many kernels of these libraries have been launched (graph replays add their kernels)."""
+    return _launches[0]
+
+
+def count_launches(n):
+    _launches[0] += n
+
+
 def _check(lib, rc, what):
+    _launches[0] += 1
     if rc != 0:
         raise KernelError(f"{what}: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
 
