@@ -1,0 +1,344 @@
+// Paged causal grouped-query attention on the tensor cores (bf16 operands, fp32 softmax and accumulation),
+// for portions of prompts and for decode tokens alike.
+//
+// A CTA works on one (request, kv head, tile of up to 64 query rows, slice of the keys).  A query row is a
+// (token of the step, query head of this kv head's group) pair: row r <-> token r / G, head r % G with
+// G = NH / NKV, so the G heads that share a kv head also share every K/V tile that is loaded.  Each warp
+// owns 16 rows; a decode token (G <= 16 rows) is one warp.  Keys and values are fetched page by page
+// through the request's block table with cp.async into double-buffered shared memory (rows padded by 16
+// bytes: conflict-free ldmatrix for every head size that is a multiple of 16), scores and outputs come
+// from mma.sync.m16n8k16, the softmax runs online in fp32 in the exp2 domain.
+//   s_j = (q . k_j) / sqrt(HD) for keys max(0, p - window + 1) <= j <= p of the row's position p;
+//   o = sum_j softmax(s)_j v_j          (formulas of src/operators/cuda/cuda_flash_attn.cu:154-248, 297-439)
+// With num_splits > 1 the key range of a tile is cut into slices handled by different CTAs that write
+// unnormalised partial results (o, running max, running sum) to scratch memory; a second kernel merges
+// them.  That is how a single decode token with a long context fills the GPU.
+#include <mma.h>
+
+#include "common.cuh"
+
+#ifndef FORGE_ATT_HD
+#define FORGE_ATT_HD 64
+#endif
+
+namespace {
+
+constexpr int HD = FORGE_ATT_HD;
+constexpr int BQ = 64, BKV = 64;
+constexpr int LD = HD + 8;                    // padded row length in shared memory (bf16 elements)
+constexpr int CPR = HD / 8;                   // 16-byte chunks per row
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+
+struct AttnParams {
+    const __nv_bfloat16* q;       // [T, NH*HD]
+    const __nv_bfloat16* kv;      // [pages, 2, NKV, page_size, HD]
+    __nv_bfloat16* out;           // [T, NH*HD]
+    float* part_o;                // [tiles, NKV, splits, part_rows, HD]   (num_splits > 1)
+    float* part_ml;               // [tiles, NKV, splits, part_rows, 2]
+    const int32_t* block_table;   // [S, max_pages]
+    const int32_t* tile_req;      // [tiles] request row of each query tile
+    const int32_t* tile_row0;     // [tiles] first query row (token * G + head) of the tile within its request
+    const int32_t* q_start;       // [S+1]
+    const int32_t* ctx_before;    // [S]
+    int NH, NKV, page_size, max_pages, window, num_splits, part_rows;
+    float scale_log2;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Loads keys/values of token indices [t0, t0+BKV) of the request into one shared-memory buffer; rows
+// outside [lo, hi) are zero-filled (their scores are masked and their values must not be NaN).
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const AttnParams& p,
+                                             const int32_t* table, int kvh, int t0, int lo, int hi) {
+    const size_t head_stride = (size_t)p.page_size * HD;
+    const size_t page_stride = 2 * (size_t)p.NKV * head_stride;
+    for (int c = threadIdx.x; c < BKV * CPR; c += blockDim.x) {
+        const int row = c / CPR, ch = c % CPR;
+        const int t = t0 + row;
+        __nv_bfloat16* kd = ks + row * LD + ch * 8;
+        __nv_bfloat16* vd = vs + row * LD + ch * 8;
+        if (t >= lo && t < hi) {
+            const int page = table[t / p.page_size];
+            const __nv_bfloat16* kp = p.kv + (size_t)page * page_stride + (size_t)kvh * head_stride +
+                                      (size_t)(t % p.page_size) * HD + ch * 8;
+            cp_async16(kd, kp);
+            cp_async16(vd, kp + (size_t)p.NKV * head_stride);
+        } else {
+            *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+paged_attention_mma_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BQ][LD]
+    __nv_bfloat16* ks = qs + BQ * LD;                                    // [2][BKV][LD]
+    __nv_bfloat16* vs = ks + 2 * BKV * LD;                               // [2][BKV][LD]
+
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.NH / p.NKV;
+    const int s = p.tile_req[tile], row0 = p.tile_row0[tile];
+    const int qs0 = p.q_start[s], qlen = p.q_start[s + 1] - qs0, ctx = p.ctx_before[s];
+    const int rows_here = min(BQ, qlen * G - row0);
+    const int32_t* table = p.block_table + (size_t)s * p.max_pages;
+
+    // key range of this tile and of this CTA's slice of it
+    const int pos_lo = ctx + row0 / G, pos_hi = ctx + (row0 + rows_here - 1) / G;
+    const int kv_hi = pos_hi + 1;
+    const int kv_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
+    const int t_begin = kv_lo / BKV, t_end = (kv_hi + BKV - 1) / BKV;
+    const int per_split = (t_end - t_begin + p.num_splits - 1) / p.num_splits;
+    const int my_begin = t_begin + split * per_split, my_end = min(my_begin + per_split, t_end);
+
+    // this thread's two rows (of the warp's 16): r_a = lane/4, r_b = r_a + 8
+    const int wrow = warp * 16;
+    const bool warp_active = wrow < rows_here;
+    const int ra = row0 + wrow + (lane >> 2), rb = ra + 8;
+    const int pos_a = ctx + ra / G, pos_b = ctx + rb / G;
+    const bool valid_a = wrow + (lane >> 2) < rows_here, valid_b = wrow + (lane >> 2) + 8 < rows_here;
+
+    float o_acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    if (my_begin < my_end) {
+        // stage the query tile: row r -> token r / G, head kvh * G + r % G
+        for (int c = threadIdx.x; c < BQ * CPR; c += blockDim.x) {
+            const int row = c / CPR, ch = c % CPR;
+            __nv_bfloat16* dst = qs + row * LD + ch * 8;
+            if (row < rows_here) {
+                const int r = row0 + row;
+                cp_async16(dst, p.q + (size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD + ch * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        load_kv_tile(ks, vs, p, table, kvh, my_begin * BKV, kv_lo, kv_hi);
+        cp_async_commit();
+
+        for (int t = my_begin; t < my_end; ++t) {
+            const int buf = (t - my_begin) & 1;
+            if (t + 1 < my_end) {
+                load_kv_tile(ks + (buf ^ 1) * BKV * LD, vs + (buf ^ 1) * BKV * LD, p, table, kvh, (t + 1) * BKV, kv_lo, kv_hi);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (warp_active) {
+                const __nv_bfloat16* kb = ks + buf * BKV * LD;
+                const __nv_bfloat16* vb = vs + buf * BKV * LD;
+                float sc[BKV / 8][4];
+#pragma unroll
+                for (int i = 0; i < BKV / 8; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, qs + (wrow + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int nb = 0; nb < BKV / 16; ++nb) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, kb + (nb * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                        mma_bf16(sc[2 * nb], a, b[0], b[1]);
+                        mma_bf16(sc[2 * nb + 1], a, b[2], b[3]);
+                    }
+                }
+                // scale, mask, online softmax (exp2 domain)
+                const int j0 = t * BKV + 2 * (lane & 3);
+                float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+                for (int i = 0; i < BKV / 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = j0 + i * 8 + e;
+                        const bool va = valid_a && j <= pos_a && (p.window <= 0 || j > pos_a - p.window);
+                        const bool vb2 = valid_b && j <= pos_b && (p.window <= 0 || j > pos_b - p.window);
+                        sc[i][e] = va ? sc[i][e] * p.scale_log2 : -INFINITY;
+                        sc[i][2 + e] = vb2 ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
+                        mx_a = fmaxf(mx_a, sc[i][e]);
+                        mx_b = fmaxf(mx_b, sc[i][2 + e]);
+                    }
+                }
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+                // a row that has seen no visible key yet keeps max -inf: use 0 as the reference so exp2 gives 0
+                const float ref_a = mx_a == -INFINITY ? 0.f : mx_a, ref_b = mx_b == -INFINITY ? 0.f : mx_b;
+                const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+                m_a = mx_a;
+                m_b = mx_b;
+                float sum_a = 0.f, sum_b = 0.f;
+                uint32_t pfrag[BKV / 16][4];
+#pragma unroll
+                for (int i = 0; i < BKV / 8; ++i) {
+                    const float p0 = exp2f(sc[i][0] - ref_a), p1 = exp2f(sc[i][1] - ref_a);
+                    const float p2 = exp2f(sc[i][2] - ref_b), p3 = exp2f(sc[i][3] - ref_b);
+                    sum_a += p0 + p1;
+                    sum_b += p2 + p3;
+                    pfrag[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+                    pfrag[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+                }
+                l_a = l_a * alpha_a + sum_a;
+                l_b = l_b * alpha_b + sum_b;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) {
+                    o_acc[i][0] *= alpha_a; o_acc[i][1] *= alpha_a;
+                    o_acc[i][2] *= alpha_b; o_acc[i][3] *= alpha_b;
+                }
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+#pragma unroll
+                    for (int db = 0; db < HD / 16; ++db) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, vb + (kk * 16 + (lane & 15)) * LD + db * 16 + (lane >> 4) * 8);
+                        mma_bf16(o_acc[2 * db], pfrag[kk], b[0], b[1]);
+                        mma_bf16(o_acc[2 * db + 1], pfrag[kk], b[2], b[3]);
+                    }
+                }
+            }
+            __syncthreads();     // the buffer just read is the target of the next iteration's loads
+        }
+    }
+
+    if (!warp_active) return;
+    // row sums live spread over the 4 lanes of a row
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const int d0 = 2 * (lane & 3);
+    if (p.num_splits == 1) {
+        const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            if (valid_a)
+                *reinterpret_cast<uint32_t*>(p.out + (size_t)(qs0 + ra / G) * p.NH * HD + (size_t)(kvh * G + ra % G) * HD + i * 8 + d0) =
+                    pack_bf16(o_acc[i][0] * inv_a, o_acc[i][1] * inv_a);
+            if (valid_b)
+                *reinterpret_cast<uint32_t*>(p.out + (size_t)(qs0 + rb / G) * p.NH * HD + (size_t)(kvh * G + rb % G) * HD + i * 8 + d0) =
+                    pack_bf16(o_acc[i][2] * inv_b, o_acc[i][3] * inv_b);
+        }
+    } else {
+        const size_t slot = ((size_t)tile * p.NKV + kvh) * p.num_splits + split;
+        float* po = p.part_o + slot * p.part_rows * HD;
+        float* pml = p.part_ml + slot * p.part_rows * 2;
+        const int la = wrow + (lane >> 2), lb = la + 8;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            if (valid_a) *reinterpret_cast<float2*>(po + la * HD + i * 8 + d0) = make_float2(o_acc[i][0], o_acc[i][1]);
+            if (valid_b) *reinterpret_cast<float2*>(po + lb * HD + i * 8 + d0) = make_float2(o_acc[i][2], o_acc[i][3]);
+        }
+        if ((lane & 3) == 0) {
+            if (valid_a) { pml[la * 2] = m_a; pml[la * 2 + 1] = l_a; }
+            if (valid_b) { pml[lb * 2] = m_b; pml[lb * 2 + 1] = l_b; }
+        }
+    }
+}
+
+// One warp per (tile, kv head, row): combines the slices' partial results in a fixed order.
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const AttnParams p, int num_tiles) {
+    const int G = p.NH / p.NKV;
+    const int gw = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int PR = p.part_rows;
+    if (gw >= num_tiles * p.NKV * PR) return;
+    const int row = gw % PR, kvh = (gw / PR) % p.NKV, tile = gw / (PR * p.NKV);
+    const int s = p.tile_req[tile], row0 = p.tile_row0[tile];
+    const int qs0 = p.q_start[s], qlen = p.q_start[s + 1] - qs0;
+    if (row0 + row >= qlen * G) return;
+    const size_t slot0 = ((size_t)tile * p.NKV + kvh) * p.num_splits;
+    float M = -INFINITY;
+    for (int z = 0; z < p.num_splits; ++z) M = fmaxf(M, p.part_ml[((slot0 + z) * PR + row) * 2]);
+    float L = 0.f;
+    float acc[(HD + 31) / 32];
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+    for (int z = 0; z < p.num_splits; ++z) {
+        const float m = p.part_ml[((slot0 + z) * PR + row) * 2];
+        if (m == -INFINITY) continue;           // a slice that had no visible key
+        const float w = exp2f(m - M);
+        L += w * p.part_ml[((slot0 + z) * PR + row) * 2 + 1];
+        const float* po = p.part_o + ((slot0 + z) * PR + row) * HD;
+#pragma unroll
+        for (int i = 0; i < (HD + 31) / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < HD) acc[i] += w * po[d];
+        }
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    const int r = row0 + row;
+    __nv_bfloat16* o = p.out + (size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD;
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < HD) o[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+}
+
+}  // namespace
+
+// Scratch floats needed for num_splits > 1, with R = 16 if max_rows <= 16 else 64:
+//   part_o = tiles*NKV*splits*R*HD, part_ml = tiles*NKV*splits*R*2.
+// max_rows: the largest number of query rows (tokens * G) of any tile, which sets the CTA size (1..4 warps).
+extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* out, float* part_o, float* part_ml,
+                                         const int32_t* block_table, const int32_t* tile_req, const int32_t* tile_row0,
+                                         const int32_t* q_start, const int32_t* ctx_before, int num_tiles, int max_rows,
+                                         int NH, int NKV, int head_dim, int page_size, int max_pages, int window,
+                                         int num_splits, float scale, cudaStream_t stream) {
+    if (head_dim != HD) return forge::fail(FORGE_ERR_UNSUPPORTED, "this attention library was built for head_dim %d, got %d", HD, head_dim);
+    if (num_tiles < 0 || NH <= 0 || NKV <= 0 || NH % NKV != 0 || page_size <= 0 || max_pages <= 0 || num_splits < 1 ||
+        max_rows < 1 || max_rows > BQ)
+        return forge::fail(FORGE_ERR_ARG, "paged_attention_mma: bad sizes tiles=%d NH=%d NKV=%d page=%d splits=%d rows=%d",
+                           num_tiles, NH, NKV, page_size, num_splits, max_rows);
+    if (num_tiles == 0) return FORGE_OK;
+    if (num_splits > 1 && (!part_o || !part_ml)) return forge::fail(FORGE_ERR_ARG, "paged_attention_mma: splits need scratch");
+    if (NKV > 65535 || num_splits > 65535) return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_mma: grid too large");
+    AttnParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (__nv_bfloat16*)out, part_o, part_ml, block_table,
+                 tile_req, tile_row0, q_start, ctx_before, NH, NKV, page_size, max_pages, window, num_splits,
+                 max_rows <= 16 ? 16 : BQ, scale * 1.4426950408889634f};
+    constexpr int smem = (BQ + 4 * BKV) * LD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_mma: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    const int threads = 32 * ((max_rows + 15) / 16);
+    paged_attention_mma_kernel<<<dim3(num_tiles, NKV, num_splits), threads, smem, stream>>>(p);
+    int rc = forge::check_launch("paged_attention_mma");
+    if (rc != FORGE_OK || num_splits == 1) return rc;
+    const long warps = (long)num_tiles * NKV * p.part_rows;
+    attention_merge_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(p, num_tiles);
+    return forge::check_launch("attention_merge");
+}
+
+extern "C" int forge_attention_head_dim() { return HD; }
+extern "C" const char* forge_last_error() { return forge::error_buffer(); }

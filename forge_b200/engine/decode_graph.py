@@ -42,6 +42,7 @@ class DecodeGraph:
             logits_rows=ar[:S].contiguous(), groups=groups, status=runner.status,
             host_q_start=list(range(S + 1)), host_context_before=[0] * S, host_slots=[0] * S)
         self.batch.decode_only = True
+        self.batch.max_context = runner.plan.max_positions     # the graph must fit any context length
         self.graph = None
         self.logits = self.tokens = None
         self.kernels_per_replay = 0

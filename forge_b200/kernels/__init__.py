@@ -45,22 +45,24 @@ _SIGNATURES = {
         "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
-        "forge_paged_attention_mma": [_P] * 9 + [_I] * 10 + [_F, _P],
+        "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
     },
 }
 
 _libs = {}
 
 
-def library(name):
-    """Loads (building first if needed) kernel library ``name`` and returns its ctypes handle."""
-    lib = _libs.get(name)
+def library(name, defines=None):
+    """Loads (building first if needed) kernel library ``name`` (variant ``defines``) and returns its
+    ctypes handle."""
+    key = (name, tuple(sorted((defines or {}).items())))
+    lib = _libs.get(key)
     if lib is not None:
         return lib
     if not torch.cuda.is_available():
         raise KernelError("forge_b200 runs on a CUDA device (B200, sm_100a) only; no device is visible")
     try:
-        path = build_library(name)
+        path = build_library(name, defines=defines)
     except BuildError as e:
         raise KernelError(f"kernel library '{name}' is not available: {e}") from e
     try:
@@ -72,7 +74,7 @@ def library(name):
         f.argtypes = argtypes
         f.restype = c_int
     lib.forge_last_error.restype = ctypes.c_char_p
-    _libs[name] = lib
+    _libs[key] = lib
     return lib
 
 
@@ -255,12 +257,89 @@ def gemm_sm100_supports(n, k):
 
 
 def attention_mma_supports(head_dim, group, page_size):
-    return _TENSOR_CORE_ATTENTION and head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size % 16 == 0
+    """Head sizes in steps of 16 up to 256, any group size, any page size; other shapes use the fp32 kernel."""
+    return _TENSOR_CORE_ATTENTION and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+BQ_ROWS = 64        # query rows (token, head-of-group pairs) per attention tile
+KV_TILE = 64        # keys per inner iteration
+_NUM_SMS = {}
+
+
+def _sm_count(device):
+    key = str(device)
+    if key not in _NUM_SMS:
+        _NUM_SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _NUM_SMS[key]
+
+
+def attention_plan(batch, group, device):
+    """How the step's query rows are cut into tiles for the tensor-core attention kernel, and into how
+    many slices each tile's keys are cut.  Computed once per step and group size (all layers share it).
+    A request with q_len tokens has q_len * group rows; tiles never span requests."""
+    key = ("mma", group)
+    plan = batch.attention_plan.get(key)
+    if plan is not None:
+        return plan
+    tile_req, tile_row0, max_rows = [], [], 1
+    qs = batch.host_q_start
+    for s in range(batch.num_requests):
+        rows = (qs[s + 1] - qs[s]) * group
+        for r0 in range(0, rows, BQ_ROWS):
+            tile_req.append(s)
+            tile_row0.append(r0)
+            max_rows = max(max_rows, min(BQ_ROWS, rows - r0))
+    max_ctx = getattr(batch, "max_context", None)
+    if max_ctx is None:
+        max_ctx = max(c + qs[s + 1] - qs[s] for s, c in enumerate(batch.host_context_before))
+    plan = {"tile_req": torch.tensor(tile_req, dtype=torch.int32, device=device),
+            "tile_row0": torch.tensor(tile_row0, dtype=torch.int32, device=device),
+            "num_tiles": len(tile_req), "max_rows": max_rows, "max_kv_tiles": -(-max_ctx // KV_TILE), "scratch": {}}
+    batch.attention_plan[key] = plan
+    return plan
+
+
+def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=0,
+                        scale=None, out=None, num_splits=None):
+    """bf16 tensor-core attention over the paged cache for every token of the step."""
+    lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
+    plan = attention_plan(batch, n_heads // n_kv_heads, q.device)
+    if num_splits is None:
+        # decode-like steps (every tile one warp): slice the keys until about two CTAs per SM exist
+        base = plan["num_tiles"] * n_kv_heads
+        num_splits = 1
+        if plan["max_rows"] <= 16:
+            num_splits = max(1, min(plan["max_kv_tiles"], -(-2 * _sm_count(q.device) // base)))
+    part_o = part_ml = None
+    if num_splits > 1:
+        pr = 16 if plan["max_rows"] <= 16 else BQ_ROWS
+        sk = (num_splits, head_dim, pr)
+        if sk not in plan["scratch"]:
+            n = plan["num_tiles"] * n_kv_heads * num_splits * pr
+            plan["scratch"][sk] = (torch.empty(n * head_dim, dtype=torch.float32, device=q.device),
+                                   torch.empty(n * 2, dtype=torch.float32, device=q.device))
+        part_o, part_ml = plan["scratch"][sk]
+    if out is None:
+        out = torch.empty_like(q)
+    scale = head_dim ** -0.5 if scale is None else scale
+    _check(lib, lib.forge_paged_attention_mma(
+        _need(q, "q", torch.bfloat16, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
+        _opt(part_o, "part_o"), _opt(part_ml, "part_ml"), _need(group_batch.block_table, "block_table", torch.int32, 2),
+        _need(plan["tile_req"], "tile_req"), _need(plan["tile_row0"], "tile_row0"),
+        _need(batch.q_start, "q_start", torch.int32), _need(batch.context_before, "context_before", torch.int32),
+        plan["num_tiles"], plan["max_rows"], n_heads, n_kv_heads, head_dim, page_size, group_batch.block_table.shape[1],
+        int(window or 0), int(num_splits), float(scale), _stream()), "paged_attention_mma")
+    if num_splits > 1:
+        count_launches(1)      # the merge kernel
+    return out
 
 
 def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=None,
                     scale=None):
     """Attention of every token of the step over its request's pages; picks the kernel by dtype and shape."""
+    if q.dtype == torch.bfloat16 and attention_mma_supports(head_dim, n_heads // n_kv_heads, page_size):
+        return paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size,
+                                   window=window or 0, scale=scale)
     return paged_attention_simt(q, kv_cache, group_batch.block_table, batch.tok_req, batch.positions, n_heads,
                                 n_kv_heads, head_dim, page_size, window=window or 0, scale=scale)
 
@@ -324,4 +403,4 @@ def check_kernel_status(device="cuda:0"):
 
 
 _TENSOR_CORE_GEMM = True
-_TENSOR_CORE_ATTENTION = False
+_TENSOR_CORE_ATTENTION = True

@@ -89,11 +89,16 @@ def _run_with_heartbeat(cmds, what):
             raise BuildError(f"nvcc failed ({' '.join(c)}):\n{o}")
 
 
-def build_library(name, force=False):
-    """Returns the path of lib ``name``, compiling it first if it is missing or stale."""
+def build_library(name, force=False, defines=None):
+    """Returns the path of lib ``name``, compiling it first if it is missing or stale.  ``defines``
+    ({macro: value}) selects a variant of the library, built and cached under its own file name (the
+    attention library is compiled per head size)."""
     if name not in LIBRARIES:
         raise BuildError(f"unknown kernel library {name!r}; known: {sorted(LIBRARIES)}")
     srcs = [os.path.join(CSRC, s) for s in LIBRARIES[name]]
+    dflags = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    lib_sources = LIBRARIES[name]
+    name = name + "".join(f"_{k.lower().replace('forge_', '')}{v}" for k, v in sorted((defines or {}).items()))
     headers = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
     for s in srcs:
         if not os.path.exists(s):
@@ -101,16 +106,16 @@ def build_library(name, force=False):
     out_dir = _build_dir()
     so = os.path.join(out_dir, f"libforge_{name}.so")
     stamp = so + ".sha256"
-    want = _digest(srcs + headers)
+    want = _digest(srcs + headers) + "".join(dflags)
     with open(os.path.join(out_dir, f".{name}.lock"), "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         if not force and os.path.exists(so) and os.path.exists(stamp) and open(stamp).read() == want:
             return so
         nvcc = _nvcc()
-        _say(f"compiling kernel library '{name}' for sm_100a ({len(srcs)} files) ...")
+        _say(f"compiling kernel library '{name}' for sm_100a ({len(lib_sources)} files) ...")
         t0 = time.time()
         objs = [os.path.join(out_dir, f"{name}_{os.path.basename(s)[:-3]}.o") for s in srcs]
-        _run_with_heartbeat([[nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", s, "-o", o] for s, o in zip(srcs, objs)],
+        _run_with_heartbeat([[nvcc, *NVCC_FLAGS, *dflags, "-I", CSRC, "-c", s, "-o", o] for s, o in zip(srcs, objs)],
                             f"'{name}'")
         tmp = so + f".tmp{os.getpid()}"
         _run_with_heartbeat([[nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]],
@@ -122,6 +127,16 @@ def build_library(name, force=False):
     return so
 
 
+# head sizes whose attention library build_all compiles ahead of time; others compile on first use
+COMMON_HEAD_DIMS = (64, 128)
+
+
 def build_all(force=False):
-    return {name: build_library(name, force=force) for name in LIBRARIES
-            if all(os.path.exists(os.path.join(CSRC, s)) for s in LIBRARIES[name])}
+    out = {}
+    for name in LIBRARIES:
+        if name == "attention_mma":
+            for hd in COMMON_HEAD_DIMS:
+                out[f"{name}_hd{hd}"] = build_library(name, force=force, defines={"FORGE_ATT_HD": hd})
+        else:
+            out[name] = build_library(name, force=force)
+    return out

@@ -1,0 +1,85 @@
+"""The tensor-core paged attention kernel alone, against a plain fp64 restatement: head sizes in steps of
+16, groups that are no power of two, page sizes, windows, steps that mix prompt portions with decode
+tokens, and key ranges cut into slices."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from plain import kernels_ref as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_case(nh, nkv, hd, ps, reqs, seed=0):
+    """reqs: list of (context_before, q_len).  Pages are scattered; returns everything the kernel needs
+    plus flat per-token (request, position) for the reference."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-(c + q) // ps) for c, q in reqs) + 2
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    max_pages = max(-(-(c + q) // ps) for c, q in reqs)
+    table = torch.full((len(reqs), max_pages), -1, dtype=torch.int32)
+    cache = torch.randn(total_pages, 2, nkv, ps, hd, generator=g).to(torch.bfloat16)
+    q_start, tok_req, positions = [0], [], []
+    for s, (c, q) in enumerate(reqs):
+        for i in range(-(-(c + q) // ps)):
+            table[s, i] = perm.pop()
+        tok_req += [s] * q
+        positions += list(range(c, c + q))
+        q_start.append(q_start[-1] + q)
+    T = q_start[-1]
+    q = torch.randn(T, nh * hd, generator=g).to(torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(num_requests=len(reqs), host_q_start=q_start, host_context_before=[c for c, _ in reqs],
+                            q_start=i32(q_start), context_before=i32([c for c, _ in reqs]), attention_plan={})
+    group = SimpleNamespace(block_table=table.to(DEV))
+    return q.to(DEV), cache.to(DEV), group, batch, i32(tok_req), i32(positions)
+
+
+SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (32, 4, 64, 16), (8, 1, 128, 32), (6, 2, 80, 16), (7, 1, 48, 16),
+          (2, 1, 256, 64), (40, 2, 64, 16)]
+MIXED = [(0, 1), (0, 77), (130, 1), (63, 2), (200, 40), (5, 1), (64, 64), (511, 1)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", SHAPES)
+@pytest.mark.parametrize("window", [0, 50])
+def test_mixed_step(nh, nkv, hd, ps, window):
+    from forge_b200 import kernels as k
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, MIXED)
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
+    got = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, window=window).float()
+    err = (got - ref).abs().amax(dim=1)
+    bad = torch.nonzero(err > 1e-2 * ref.abs().max())
+    assert len(bad) == 0, f"first wrong token {int(bad[0])} (request {int(tok_req[bad[0]])}, position {int(positions[bad[0]])})"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 4, 64, 16), (3, 1, 32, 8), (16, 2, 128, 16)])
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_decode_tokens_with_sliced_keys(nh, nkv, hd, ps, splits):
+    from forge_b200 import kernels as k
+    reqs = [(0, 1), (63, 1), (64, 1), (65, 1), (300, 1), (1000, 1)]
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=1)
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps)
+    got = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, num_splits=splits).float()
+    assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
+    auto = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps).float()      # the heuristic's choice
+    assert (auto - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
+def test_far_key_and_page_edges():
+    """One early key gets nearly all the weight of the last query; contexts end exactly on, one before and
+    one after a page's edge and a key tile's edge."""
+    from forge_b200 import kernels as k
+    nh, nkv, hd, ps = 8, 2, 64, 16
+    reqs = [(c, 1) for c in (15, 16, 17, 63, 64, 65, 127, 128, 129)] + [(700, 3)]
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=2)
+    far = 21
+    page = int(group.block_table[len(reqs) - 1, far // ps])
+    cache[page, 0, 0, far % ps, :] = (q[-1, :hd].float() * 4.0).to(torch.bfloat16)
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps)
+    v_far = cache[page, 1, 0, far % ps, :].float()
+    assert (ref[-1, :hd] - v_far).abs().max() < 5e-2
+    for splits in (1, 4):
+        got = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, num_splits=splits).float()
+        assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
