@@ -252,6 +252,189 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Few rows (decode): the weight matrix is the MMA's M operand.
+//
+// With M <= 64 tokens the product is a stream of weights through the SMs: what matters is that every SM
+// has many bytes of W in flight and that no byte is loaded twice.  So here a CTA takes 128 rows of W
+// (all 16 KB of each 128 x 64 tile are useful bytes; the tokens are the narrow N side, padded to 16/32/64
+// by TMA's zero fill) and only a slice of K; the `kSplit` CTAs of a thread-block cluster share one row
+// tile and cut K between them, which gives enough CTAs to cover the GPU even when N is small.  Their
+// partial sums meet in distributed shared memory: every CTA parks its [tokens x 128] fp32 partial in its
+// own shared memory, the cluster synchronises, and each CTA then adds up, in rank order (so the result
+// does not depend on timing), the slice of rows it owns, applies the epilogue and writes C.  No scratch
+// in global memory, no atomics.
+template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
+    static constexpr int kStageBytes = BM * BK * 2 + NT * BK * 2;
+    static constexpr int kPartialBytes = NT * BM * 4;
+    static constexpr int kStages = (kSmemLimit - 2048 - kPartialBytes) / kStageBytes > 12
+                                       ? 12 : (kSmemLimit - 2048 - kPartialBytes) / kStageBytes;
+    static constexpr int kTmemCols = NT < 32 ? 32 : NT;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                         const GemmParams p, const int ksplit) {
+    using C = SkinnyCfg<NT>;
+    constexpr int kStages = C::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    float* partial = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);          // [NT][BM]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kPartialBytes);
+    uint64_t* full = bars;
+    uint64_t* acc_full = bars + kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kStages + 1);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // A stage is used once per CTA when the CTA has at most kStages k-blocks; beyond that the producer
+    // reuses stage s for k-block s + kStages once the MMA warp has committed it (signalled through `reuse`).
+    uint64_t* reuse = bars + kStages + 2;         // [kStages] MMA -> TMA
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int n0 = (blockIdx.x / ksplit) * BM;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int kb_per = (num_kb + ksplit - 1) / ksplit;
+    const int kb_begin = rank * kb_per, kb_end = min(kb_begin + kb_per, num_kb);
+    const int my_kb = max(kb_end - kb_begin, 0);
+
+    if (threadIdx.x == 0) {
+        *abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&reuse[s], 1); }
+        mbar_init(acc_full, 1);
+        mbar_fence_init();
+        prefetch_tensormap(&tmap_w);
+        prefetch_tensormap(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < my_kb && ok; ++i) {
+                const int s = i % kStages;
+                if (i >= kStages) ok = mbar_wait(&reuse[s], ((i / kStages) - 1) & 1, abort, p.status);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                uint8_t* w_dst = tiles + s * C::kStageBytes;
+                tma_load_2d(w_dst, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
+                tma_load_2d(w_dst + BM * BK * 2, &tmap_x, &full[s], (kb_begin + i) * BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, NT);
+            bool ok = true;
+            for (int i = 0; i < my_kb && ok; ++i) {
+                const int s = i % kStages;
+                if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
+                tc_fence_after_sync();
+                const uint32_t w_addr = smem_u32(tiles + s * C::kStageBytes);
+                const uint32_t x_addr = w_addr + BM * BK * 2;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
+                              umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (i | k) != 0);
+                umma_commit(&reuse[s]);
+            }
+            if (ok && my_kb > 0) umma_commit(acc_full);
+        }
+    } else {
+        // epilogue warps: park this CTA's partial [token][row] in shared memory
+        const int quarter = warp & 3;
+        const int n_local = quarter * 32 + lane;
+        bool ok = true;
+        if (my_kb > 0) ok = mbar_wait(acc_full, 0, abort, p.status);
+        tc_fence_after_sync();
+        if (my_kb > 0 && ok) {
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < NT; c += 16) {
+                uint32_t r[16];
+                tmem_ld_32x32b_x16(t_row + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) partial[(c + i) * BM + n_local] = __uint_as_float(r[i]);
+            }
+        } else {
+            for (int m = 0; m < NT; ++m) partial[m * BM + n_local] = 0.f;
+        }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();                       // every CTA's partial is in place and visible
+
+    if (warp >= 2) {
+        // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order
+        const int rows_per = BM / ksplit;                  // ksplit divides 128
+        const int t = threadIdx.x - 64;                    // 0..127
+        const uint32_t partial_addr = smem_u32(partial);
+        const bool swiglu = p.epilogue == EPI_SWIGLU_BF16;
+        const int cols = swiglu ? rows_per / 2 : rows_per;  // output columns this CTA produces per token
+        for (int idx = t; idx < p.M * cols; idx += 128) {
+            const int m = idx / cols, j = idx % cols;
+            if (swiglu) {
+                const int nl = rank * rows_per + 2 * j;
+                float g = 0.f, u = 0.f;
+                for (int q = 0; q < ksplit; ++q) {
+                    g += ld_dsmem_f32(partial_addr + (m * BM + nl) * 4, q);
+                    u += ld_dsmem_f32(partial_addr + (m * BM + nl + 1) * 4, q);
+                }
+                const int n = n0 + nl;
+                if (n + 1 < p.N) {
+                    if (p.bias) { g += p.bias[n]; u += p.bias[n + 1]; }
+                    reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] = __float2bfloat16_rn(silu(g) * u);
+                }
+            } else {
+                const int nl = rank * rows_per + j;
+                float v = 0.f;
+                for (int q = 0; q < ksplit; ++q) v += ld_dsmem_f32(partial_addr + (m * BM + nl) * 4, q);
+                const int n = n0 + nl;
+                if (n < p.N) {
+                    if (p.bias) v += p.bias[n];
+                    if (p.epilogue == EPI_STORE_BF16) {
+                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                    } else {
+                        float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                        *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_all();                       // nobody leaves while a peer may still read its partial
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 int g_num_sms = 0;
 
 template <int BN>
@@ -270,11 +453,40 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cu
     return forge::check_launch("gemm_sm100");
 }
 
+template <int NT>
+int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int ksplit, cudaStream_t stream) {
+    using C = SkinnyCfg<NT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
+                                                 C::kSmemBytes, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tiles_n = (p.N + BM - 1) / BM;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles_n * ksplit, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_skinny_kernel<NT>, tw, tx, p, ksplit);
+    if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100 (few rows): %s", cudaGetErrorString(e));
+    return forge::check_launch("gemm_sm100 (few rows)");
+}
+
 }  // namespace
 
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
-// tile_n: 0 = choose, else one of 16, 32, 64, 128, 256.  status: device int, bit 1 raised if a wait ran out.
+// tile_n: 0 = choose; 16, 32, 64, 128, 256 = token-major tiles of that width; -1, -2, -4, -8 (M <= 64 only) =
+// the few-rows kernel with K cut across a cluster of that many CTAs.  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
                                 int K, int epilogue, int tile_n, void* reserved, cudaStream_t stream) {
     (void)reserved;
@@ -288,6 +500,29 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
         if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    const char* err = nullptr;
+    if (M <= 64 && tile_n <= 0) {
+        // few rows: weights are the MMA's M operand, K is cut across a cluster (tile_n < 0: -tile_n CTAs)
+        const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        const int tiles_n = (N + BM - 1) / BM, num_kb = (K + BK - 1) / BK;
+        int ksplit = 1;
+        if (tile_n < 0) {
+            ksplit = -tile_n;
+            if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
+                return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1, 2, 4 or 8, got %d", ksplit);
+        } else {
+            while (ksplit < 8 && tiles_n * ksplit * 2 <= g_num_sms && num_kb / (ksplit * 2) >= 2) ksplit *= 2;
+        }
+        CUtensorMap tw, tx;
+        if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_tile_map(A, M, K, nt, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+        GemmParams p{C, bias, M, N, K, epilogue, status};
+        switch (nt) {
+            case 16: return launch_skinny<16>(tw, tx, p, ksplit, stream);
+            case 32: return launch_skinny<32>(tw, tx, p, ksplit, stream);
+            default: return launch_skinny<64>(tw, tx, p, ksplit, stream);
+        }
     }
     int bn = tile_n;
     if (bn == 0) {
@@ -305,7 +540,6 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             }
         }
     }
-    const char* err = nullptr;
     CUtensorMap ta, tw;
     if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     if (!bf16_tile_map(W, N, K, bn, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);

@@ -64,6 +64,39 @@ def test_many_tiles_per_cta_and_both_accumulators():
     k.check_kernel_status()
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
+@pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8])
+def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
+    """The decode-shaped kernel (weights as the MMA's M operand, K cut over a cluster, partial sums added
+    through distributed shared memory) for every cluster size and every epilogue."""
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    ref = R.gemm_ref(a, w, bias)
+    tol = 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
+    got = k.gemm_sm100(a, w, bias=bias, tile_n=cluster)
+    assert (got - ref).abs().max() <= tol
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    got = k.gemm_sm100(a, w, bias=bias, accumulate_into=res.clone(), tile_n=cluster)
+    assert (got - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max()
+    got = k.gemm_sm100(a, w, bias=bias, epilogue="cast", tile_n=cluster)
+    assert (got.float() - ref).abs().max() <= 8e-3 * ref.abs().max()
+    if N % 2 == 0:
+        got = k.gemm_sm100(a, w, bias=bias, epilogue="swiglu", tile_n=cluster)
+        want = R.silu_mul_interleaved_ref(ref)
+        assert got.shape == (M, N // 2) and (got.float() - want).abs().max() <= 8e-3 * want.abs().max() + 1e-6
+    k.check_kernel_status()
+
+
+def test_few_rows_kernel_is_deterministic():
+    k = _k()
+    a, w = _rand(8, 2048), _rand(2048, 2048, seed=1)
+    first = k.gemm_sm100(a, w)
+    for _ in range(5):
+        assert torch.equal(k.gemm_sm100(a, w), first)
+
+
 def test_refuses_what_it_cannot_do():
     k = _k()
     with pytest.raises(k.KernelError, match="multiple of 8"):
