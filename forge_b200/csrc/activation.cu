@@ -7,6 +7,8 @@ namespace {
 
 template <typename TOut>
 __global__ void silu_mul_interleaved_kernel(const float* __restrict__ gu, TOut* __restrict__ out, size_t n) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float2 p = reinterpret_cast<const float2*>(gu)[i];
@@ -21,7 +23,8 @@ extern "C" int forge_silu_mul_interleaved(const float* gu, void* out, int out_dt
     const size_t n = (size_t)T * I;
     if (n == 0) return FORGE_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(out_dtype, TO,
-        silu_mul_interleaved_kernel<TO><<<blocks, 256, 0, stream>>>(gu, (TO*)out, n));
-    return forge::check_launch("silu_mul_interleaved");
+        e = forge::launch(silu_mul_interleaved_kernel<TO>, dim3(blocks), dim3(256), 0, stream, 1, gu, (TO*)out, n));
+    return forge::check_launch("silu_mul_interleaved", e);
 }

@@ -99,6 +99,8 @@ paged_attention_mma_kernel(const AttnParams p) {
     __nv_bfloat16* ks = qs + BQ * LD;                                    // [2][BKV][LD]
     __nv_bfloat16* vs = ks + 2 * BKV * LD;                               // [2][BKV][LD]
 
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.NH / p.NKV;
@@ -266,6 +268,8 @@ paged_attention_mma_kernel(const AttnParams p) {
 // One warp per (tile, kv head, row): combines the slices' partial results in a fixed order.
 __global__ void __launch_bounds__(128)
 attention_merge_kernel(const AttnParams p, int num_tiles) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int G = p.NH / p.NKV;
     const int gw = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int PR = p.part_rows;
@@ -275,22 +279,34 @@ attention_merge_kernel(const AttnParams p, int num_tiles) {
     const int qs0 = p.q_start[s], qlen = p.q_start[s + 1] - qs0;
     if (row0 + row >= qlen * G) return;
     const size_t slot0 = ((size_t)tile * p.NKV + kvh) * p.num_splits;
+    // pass 1: the slices' running maxima and sums, 32 slices at a time across the lanes
     float M = -INFINITY;
-    for (int z = 0; z < p.num_splits; ++z) M = fmaxf(M, p.part_ml[((slot0 + z) * PR + row) * 2]);
+    for (int z = lane; z < p.num_splits; z += 32) M = fmaxf(M, p.part_ml[((slot0 + z) * PR + row) * 2]);
+    M = forge::warp_max(M);
     float L = 0.f;
     float acc[(HD + 31) / 32];
 #pragma unroll
     for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
-    for (int z = 0; z < p.num_splits; ++z) {
-        const float m = p.part_ml[((slot0 + z) * PR + row) * 2];
-        if (m == -INFINITY) continue;           // a slice that had no visible key
-        const float w = exp2f(m - M);
-        L += w * p.part_ml[((slot0 + z) * PR + row) * 2 + 1];
-        const float* po = p.part_o + ((slot0 + z) * PR + row) * HD;
+    // pass 2: slices in index order (a fixed order of additions); the loads of different slices are independent
+    for (int z0 = 0; z0 < p.num_splits; z0 += 32) {
+        const int zl = z0 + lane;
+        float m_l = -INFINITY, l_l = 0.f;
+        if (zl < p.num_splits) {
+            m_l = p.part_ml[((slot0 + zl) * PR + row) * 2];
+            l_l = p.part_ml[((slot0 + zl) * PR + row) * 2 + 1];
+        }
+        const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);      // a slice without a visible key weighs 0
+        const int nz = min(32, p.num_splits - z0);
+        for (int zz = 0; zz < nz; ++zz) {
+            const float w = __shfl_sync(0xffffffffu, w_l, zz);
+            L += w * __shfl_sync(0xffffffffu, l_l, zz);
+            if (w == 0.f) continue;
+            const float* po = p.part_o + ((slot0 + z0 + zz) * PR + row) * HD;
 #pragma unroll
-        for (int i = 0; i < (HD + 31) / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < HD) acc[i] += w * po[d];
+            for (int i = 0; i < (HD + 31) / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < HD) acc[i] += w * po[d];
+            }
         }
     }
     const float inv = L > 0.f ? 1.0f / L : 0.f;
@@ -332,12 +348,10 @@ extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* ou
         configured = true;
     }
     const int threads = 32 * ((max_rows + 15) / 16);
-    paged_attention_mma_kernel<<<dim3(num_tiles, NKV, num_splits), threads, smem, stream>>>(p);
-    int rc = forge::check_launch("paged_attention_mma");
+    int rc = forge::check_launch("paged_attention_mma", forge::launch(paged_attention_mma_kernel, dim3(num_tiles, NKV, num_splits), dim3(threads), smem, stream, 1, p));
     if (rc != FORGE_OK || num_splits == 1) return rc;
     const long warps = (long)num_tiles * NKV * p.part_rows;
-    attention_merge_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(p, num_tiles);
-    return forge::check_launch("attention_merge");
+    return forge::check_launch("attention_merge", forge::launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, 1, p, num_tiles));
 }
 
 extern "C" int forge_attention_head_dim() { return HD; }

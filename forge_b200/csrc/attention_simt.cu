@@ -17,6 +17,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ kv_ca
                             const int32_t* __restrict__ block_table, const int32_t* __restrict__ tok_req,
                             const int32_t* __restrict__ positions, T* __restrict__ out, int T_tokens, int NH,
                             int NKV, int HD, int page_size, int max_pages, int window, float scale) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (warp_global >= T_tokens * NH) return;
@@ -77,9 +79,10 @@ int launch(const void* q, const void* kv, const int32_t* bt, const int32_t* tok_
     const int warps = T_tokens * NH;
     const unsigned blocks = (unsigned)((warps + 3) / 4);
     const int dpl = (HD + 31) / 32;
+    cudaError_t e = cudaSuccess;
 #define FORGE_ATT_CASE(D)                                                                                  \
     case D:                                                                                                \
-        paged_attention_simt_kernel<D, T><<<blocks, 128, 0, stream>>>(                                     \
+        e = forge::launch(paged_attention_simt_kernel<D, T>, dim3(blocks), dim3(128), 0, stream, 1,        \
             (const T*)q, (const T*)kv, bt, tok_req, positions, (T*)out, T_tokens, NH, NKV, HD, page_size,  \
             max_pages, window, scale);                                                                     \
         break;
@@ -89,7 +92,7 @@ int launch(const void* q, const void* kv, const int32_t* bt, const int32_t* tok_
         default: return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_simt: head_dim %d > 256", HD);
     }
 #undef FORGE_ATT_CASE
-    return forge::check_launch("paged_attention_simt");
+    return forge::check_launch("paged_attention_simt", e);
 }
 
 }  // namespace

@@ -11,6 +11,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #define FORGE_OK 0
 #define FORGE_ERR_ARG (-1)
@@ -34,10 +35,54 @@ inline int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-inline int check_launch(const char* what) {
-    cudaError_t e = cudaGetLastError();
+inline int check_launch(const char* what, cudaError_t launch_result = cudaSuccess) {
+    cudaError_t e = launch_result != cudaSuccess ? launch_result : cudaGetLastError();
     if (e != cudaSuccess) return fail(FORGE_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
     return FORGE_OK;
+}
+
+// Programmatic dependent launch.  Every kernel of these libraries is launched with the attribute that lets
+// it start while its predecessor in the stream is still draining; it tells the scheduler at once that its
+// own successor may be set up (launch_dependents), does whatever does not depend on earlier kernels
+// (barrier set-up, weight prefetch), and executes pdl_wait() before it touches memory that an earlier
+// kernel wrote or still reads.  Because every kernel waits, completion is transitive along the stream.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("FORGE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+// Launches `kernel` with programmatic stream serialization (and an optional cluster size).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          int cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -8,6 +8,8 @@ namespace {
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* status) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -27,7 +29,8 @@ extern "C" int forge_embedding(const int32_t* ids, const void* table, int table_
     if (T < 0 || H <= 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);
     if (T == 0) return FORGE_OK;
     const int threads = H >= 1024 ? 256 : 128;
+    cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(table_dtype, TT,
-        embedding_kernel<TT><<<T, threads, 0, stream>>>(ids, (const TT*)table, out, H, V, status));
-    return forge::check_launch("embedding");
+        e = forge::launch(embedding_kernel<TT>, dim3(T), dim3(threads), 0, stream, 1, ids, (const TT*)table, out, H, V, status));
+    return forge::check_launch("embedding", e);
 }

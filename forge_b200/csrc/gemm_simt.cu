@@ -18,6 +18,8 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
                  float* __restrict__ C, int M, int N, int K, int accumulate) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     float acc[TM][TN] = {};
@@ -72,7 +74,8 @@ extern "C" int forge_gemm_simt(const void* A, const void* W, const float* bias, 
     if (M == 0) return FORGE_OK;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_simt: M=%d too large", M);
+    cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        gemm_simt_kernel<TT, TT><<<grid, 256, 0, stream>>>((const TT*)A, (const TT*)W, bias, C, M, N, K, accumulate));
-    return forge::check_launch("gemm_simt");
+        e = forge::launch(gemm_simt_kernel<TT, TT>, grid, dim3(256), 0, stream, 1, (const TT*)A, (const TT*)W, bias, C, M, N, K, accumulate));
+    return forge::check_launch("gemm_simt", e);
 }

@@ -90,6 +90,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();                 // A, bias and C may come from (or still be read by) earlier kernels
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -267,10 +269,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
     static constexpr int kStageBytes = BM * BK * 2 + NT * BK * 2;
     static constexpr int kPartialBytes = NT * BM * 4;
-    static constexpr int kStages = (kSmemLimit - 2048 - kPartialBytes) / kStageBytes > 12
-                                       ? 12 : (kSmemLimit - 2048 - kPartialBytes) / kStageBytes;
+    static constexpr int kMaxStages = (kSmemLimit - 2048 - kPartialBytes) / kStageBytes > 12
+                                          ? 12 : (kSmemLimit - 2048 - kPartialBytes) / kStageBytes;
     static constexpr int kTmemCols = NT < 32 ? 32 : NT;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 1024;
+    // a CTA takes only as many stages as it has k-blocks, so that CTAs of the next kernel fit beside it
+    static constexpr int smem_bytes(int stages) { return stages * kStageBytes + kPartialBytes + 1024 + 1024; }
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -281,32 +284,32 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
-    float v;
+    float4 v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
     return v;
 }
 
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                         const GemmParams p, const int ksplit) {
+                         const GemmParams p, const int ksplit, const int kStages) {
     using C = SkinnyCfg<NT>;
-    constexpr int kStages = C::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
     float* partial = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);          // [NT][BM]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kPartialBytes);
     uint64_t* full = bars;
-    uint64_t* acc_full = bars + kStages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kStages + 1);
+    uint64_t* acc_full = bars + C::kMaxStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kMaxStages + 1);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // A stage is used once per CTA when the CTA has at most kStages k-blocks; beyond that the producer
     // reuses stage s for k-block s + kStages once the MMA warp has committed it (signalled through `reuse`).
-    uint64_t* reuse = bars + kStages + 2;         // [kStages] MMA -> TMA
+    uint64_t* reuse = bars + C::kMaxStages + 2;   // [kStages] MMA -> TMA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -332,14 +335,23 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    forge::pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
+            // the weights do not depend on earlier kernels: their first stages are requested before the wait
+            const int first = min(my_kb, kStages);
+            for (int i = 0; i < first; ++i) {
+                mbar_arrive_expect_tx(&full[i], C::kStageBytes);
+                tma_load_2d(tiles + i * C::kStageBytes, &tmap_w, &full[i], (kb_begin + i) * BK, n0);
+            }
+            forge::pdl_wait();                    // the activations come from the previous kernel
+            for (int i = 0; i < first; ++i)
+                tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_x, &full[i], (kb_begin + i) * BK, 0);
             bool ok = true;
-            for (int i = 0; i < my_kb && ok; ++i) {
+            for (int i = first; i < my_kb && ok; ++i) {
                 const int s = i % kStages;
-                if (i >= kStages) ok = mbar_wait(&reuse[s], ((i / kStages) - 1) & 1, abort, p.status);
-                if (!ok) break;
+                if (!(ok = mbar_wait(&reuse[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
                 mbar_arrive_expect_tx(&full[s], C::kStageBytes);
                 uint8_t* w_dst = tiles + s * C::kStageBytes;
                 tma_load_2d(w_dst, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
@@ -365,14 +377,47 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (ok && my_kb > 0) umma_commit(acc_full);
         }
     } else {
-        // epilogue warps: park this CTA's partial [token][row] in shared memory
         const int quarter = warp & 3;
         const int n_local = quarter * 32 + lane;
+        forge::pdl_wait();                        // C and bias: written or still read by earlier kernels
         bool ok = true;
         if (my_kb > 0) ok = mbar_wait(acc_full, 0, abort, p.status);
         tc_fence_after_sync();
-        if (my_kb > 0 && ok) {
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        if (ksplit == 1) {
+            // the whole reduction happened in this CTA: straight from tensor memory to C.  A thread holds
+            // one weight row n for all tokens, so for each token a warp writes 32 consecutive columns.
+            const int n = n0 + n_local;
+            const float b = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            if (ok) {
+#pragma unroll
+                for (int c = 0; c < NT; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(t_row + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = c + i;
+                        if (m >= p.M) break;                       // uniform over the warp
+                        const float v = __uint_as_float(r[i]) + b;
+                        if (p.epilogue == EPI_SWIGLU_BF16) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                            if ((lane & 1) == 0 && n + 1 < p.N)
+                                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] =
+                                    __float2bfloat16_rn(silu(v) * other);
+                        } else if (n < p.N) {
+                            if (p.epilogue == EPI_STORE_BF16) {
+                                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                            } else {
+                                float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                                *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (my_kb > 0 && ok) {
+            // park this CTA's partial [token][row] in shared memory for the cluster-wide sum
 #pragma unroll
             for (int c = 0; c < NT; c += 16) {
                 uint32_t r[16];
@@ -389,40 +434,47 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncwarp();
     cluster_sync_all();                       // every CTA's partial is in place and visible
 
-    if (warp >= 2) {
-        // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order
-        const int rows_per = BM / ksplit;                  // ksplit divides 128
+    if (warp >= 2 && ksplit > 1) {
+        // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order, four
+        // adjacent rows (16 bytes of each peer's shared memory) per thread
+        const int rows_per = BM / ksplit;                  // 16, 32 or 64
+        const int groups = rows_per / 4;
         const int t = threadIdx.x - 64;                    // 0..127
         const uint32_t partial_addr = smem_u32(partial);
-        const bool swiglu = p.epilogue == EPI_SWIGLU_BF16;
-        const int cols = swiglu ? rows_per / 2 : rows_per;  // output columns this CTA produces per token
-        for (int idx = t; idx < p.M * cols; idx += 128) {
-            const int m = idx / cols, j = idx % cols;
-            if (swiglu) {
-                const int nl = rank * rows_per + 2 * j;
-                float g = 0.f, u = 0.f;
-                for (int q = 0; q < ksplit; ++q) {
-                    g += ld_dsmem_f32(partial_addr + (m * BM + nl) * 4, q);
-                    u += ld_dsmem_f32(partial_addr + (m * BM + nl + 1) * 4, q);
-                }
-                const int n = n0 + nl;
-                if (n + 1 < p.N) {
-                    if (p.bias) { g += p.bias[n]; u += p.bias[n + 1]; }
-                    reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] = __float2bfloat16_rn(silu(g) * u);
-                }
+        for (int idx = t; idx < p.M * groups; idx += 128) {
+            const int m = idx / groups, nl = rank * rows_per + 4 * (idx % groups);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < ksplit; ++q) {
+                const float4 v = ld_dsmem_f32x4(partial_addr + (m * BM + nl) * 4, q);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            const int n = n0 + nl;
+            float v[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (n + i < p.N) v[i] += p.bias[n + i];
+            }
+            if (p.epilogue == EPI_SWIGLU_BF16) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * (p.N >> 1) + (n >> 1);
+                if (n + 1 < p.N) dst[0] = __float2bfloat16_rn(silu(v[0]) * v[1]);
+                if (n + 3 < p.N) dst[1] = __float2bfloat16_rn(silu(v[2]) * v[3]);
+            } else if (p.epilogue == EPI_STORE_BF16) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (n + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
             } else {
-                const int nl = rank * rows_per + j;
-                float v = 0.f;
-                for (int q = 0; q < ksplit; ++q) v += ld_dsmem_f32(partial_addr + (m * BM + nl) * 4, q);
-                const int n = n0 + nl;
-                if (n < p.N) {
-                    if (p.bias) v += p.bias[n];
-                    if (p.epilogue == EPI_STORE_BF16) {
-                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
-                    } else {
-                        float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
-                        *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;
+                float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                const bool accum = p.epilogue == EPI_ACCUM_F32;
+                if (n + 3 < p.N && (p.N & 3) == 0) {
+                    float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                    if (accum) {
+                        const float4 old = *reinterpret_cast<const float4*>(dst);
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                     }
+                    *reinterpret_cast<float4*>(dst) = o;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) if (n + i < p.N) dst[i] = accum ? dst[i] + v[i] : v[i];
                 }
             }
         }
@@ -449,8 +501,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cu
     }
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid = tiles < g_num_sms ? tiles : g_num_sms;
-    gemm_sm100_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tw, p);
-    return forge::check_launch("gemm_sm100");
+    return forge::check_launch("gemm_sm100", forge::launch(gemm_sm100_kernel<BN>, dim3(grid), dim3(kThreads),
+                                                             C::kSmemBytes, stream, 1, ta, tw, p));
 }
 
 template <int NT>
@@ -458,27 +510,18 @@ int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams
     using C = SkinnyCfg<NT>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::smem_bytes(C::kMaxStages));
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
-                                                 C::kSmemBytes, cudaGetErrorString(e));
+                                                 C::smem_bytes(C::kMaxStages), cudaGetErrorString(e));
         configured = true;
     }
     const int tiles_n = (p.N + BM - 1) / BM;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles_n * ksplit, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ksplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sm100_skinny_kernel<NT>, tw, tx, p, ksplit);
-    if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100 (few rows): %s", cudaGetErrorString(e));
-    return forge::check_launch("gemm_sm100 (few rows)");
+    const int num_kb = (p.K + BK - 1) / BK, kb_per = (num_kb + ksplit - 1) / ksplit;
+    const int stages = kb_per < C::kMaxStages ? kb_per : C::kMaxStages;
+    return forge::check_launch("gemm_sm100 (few rows)",
+                               forge::launch(gemm_sm100_skinny_kernel<NT>, dim3(tiles_n * ksplit), dim3(kThreads),
+                                             C::smem_bytes(stages), stream, ksplit, tw, tx, p, ksplit, stages));
 }
 
 }  // namespace
@@ -512,7 +555,11 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
                 return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1, 2, 4 or 8, got %d", ksplit);
         } else {
-            while (ksplit < 8 && tiles_n * ksplit * 2 <= g_num_sms && num_kb / (ksplit * 2) >= 2) ksplit *= 2;
+            // as many CTAs as fit the GPU at once; a cluster of 8 only when each CTA then still has a short
+            // pipeline of its own (measured: with K = 5632, 4 CTAs of 22 k-blocks beat 8 of 11)
+            while (ksplit < 8 && tiles_n * ksplit * 2 <= g_num_sms + g_num_sms / 8 && num_kb / (ksplit * 2) >= 2 &&
+                   (ksplit < 4 || num_kb <= 32))
+                ksplit *= 2;
         }
         CUtensorMap tw, tx;
         if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);

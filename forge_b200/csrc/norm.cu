@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
                const int32_t* __restrict__ rows, int H, float eps) {
     __shared__ float red[32];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
     float ss = 0.f;
@@ -34,7 +36,8 @@ extern "C" int forge_rmsnorm(const float* x, const float* w, void* out, int out_
                              int R, int H, float eps, cudaStream_t stream) {
     if (R < 0 || H <= 0) return forge::fail(FORGE_ERR_ARG, "rmsnorm: bad sizes R=%d H=%d", R, H);
     if (R == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(out_dtype, TO,
-        rmsnorm_kernel<TO><<<R, kNormThreads, 0, stream>>>(x, w, (TO*)out, rows, H, eps));
-    return forge::check_launch("rmsnorm");
+        e = forge::launch(rmsnorm_kernel<TO>, dim3(R), dim3(kNormThreads), 0, stream, 1, x, w, (TO*)out, rows, H, eps));
+    return forge::check_launch("rmsnorm", e);
 }

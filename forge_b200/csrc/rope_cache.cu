@@ -12,50 +12,43 @@
 
 namespace {
 
+// One thread per pair (d, d + HD/2) of one head of one token: q and k heads are rotated, v heads copied.
 template <typename TAct, typename TCache>
-__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
-                                     const int32_t* __restrict__ slot_mapping, TAct* __restrict__ q_out,
-                                     TCache* __restrict__ kv_cache, int NH, int NKV, int HD, int page_size,
-                                     float theta, int rotary) {
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
+                     const int32_t* __restrict__ slot_mapping, TAct* __restrict__ q_out,
+                     TCache* __restrict__ kv_cache, int NH, int NKV, int HD, int page_size,
+                     float theta, int rotary) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int t = blockIdx.x;
     const int half = HD >> 1;
-    const int n_rot_heads = NH + NKV;
-    const int width = (NH + 2 * NKV) * HD;
-    const float* row = qkv + (size_t)t * width;
-    const float pos = (float)positions[t];
+    const int w = blockIdx.y * blockDim.x + threadIdx.x;
+    if (w >= (NH + 2 * NKV) * half) return;
+    const int h = w / half, d = w % half;
+    const float* row = qkv + (size_t)t * (NH + 2 * NKV) * HD;
+    float x0 = row[h * HD + d], x1 = row[h * HD + d + half];
+    if (rotary && h < NH + NKV) {
+        const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
+        float s, c;
+        sincosf((float)positions[t] * freq, &s, &c);
+        const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
+        x0 = y0;
+        x1 = y1;
+    }
+    if (h < NH) {
+        TAct* q = q_out + (size_t)t * NH * HD + h * HD;
+        q[d] = forge::from_float<TAct>(x0);
+        q[d + half] = forge::from_float<TAct>(x1);
+        return;
+    }
     const int slot = slot_mapping ? slot_mapping[t] : -1;
-    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    TCache* kbase = kv_cache + ((size_t)page * 2 + 0) * NKV * page_size * HD + (size_t)off * HD;
-    TCache* vbase = kv_cache + ((size_t)page * 2 + 1) * NKV * page_size * HD + (size_t)off * HD;
-
-    // q and k heads: one thread per rotated pair
-    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
-        const int h = i / half, d = i % half;
-        float x0 = row[h * HD + d], x1 = row[h * HD + d + half];
-        if (rotary) {
-            const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
-            float s, c;
-            sincosf(pos * freq, &s, &c);
-            const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
-            x0 = y0;
-            x1 = y1;
-        }
-        if (h < NH) {
-            q_out[(size_t)t * NH * HD + h * HD + d] = forge::from_float<TAct>(x0);
-            q_out[(size_t)t * NH * HD + h * HD + d + half] = forge::from_float<TAct>(x1);
-        } else if (slot >= 0) {
-            TCache* k = kbase + (size_t)(h - NH) * page_size * HD;
-            k[d] = forge::from_float<TCache>(x0);
-            k[d + half] = forge::from_float<TCache>(x1);
-        }
-    }
-    if (slot >= 0) {
-        const float* vrow = row + (NH + NKV) * HD;
-        for (int i = threadIdx.x; i < NKV * HD; i += blockDim.x) {
-            const int h = i / HD, d = i % HD;
-            vbase[(size_t)h * page_size * HD + d] = forge::from_float<TCache>(vrow[i]);
-        }
-    }
+    if (slot < 0) return;
+    const int page = slot / page_size, off = slot % page_size;
+    const int is_v = h >= NH + NKV, kvh = h - NH - (is_v ? NKV : 0);
+    TCache* dst = kv_cache + (((size_t)page * 2 + is_v) * NKV + kvh) * page_size * HD + (size_t)off * HD;
+    dst[d] = forge::from_float<TCache>(x0);
+    dst[d + half] = forge::from_float<TCache>(x1);
 }
 
 }  // namespace
@@ -63,12 +56,15 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
 extern "C" int forge_rope_kv_write(const float* qkv, const int32_t* positions, const int32_t* slot_mapping,
                                    void* q_out, void* kv_cache, int dtype, int T, int NH, int NKV, int HD,
                                    int page_size, float theta, int rotary, cudaStream_t stream) {
+    if (T > 2147483647 / 2 || ((NH + 2 * NKV) * (HD / 2) + 127) / 128 > 65535)
+        return forge::fail(FORGE_ERR_UNSUPPORTED, "rope_kv_write: too many heads for one launch");
     if (T < 0 || NH <= 0 || NKV <= 0 || HD <= 0 || (HD & 1) || page_size <= 0)
         return forge::fail(FORGE_ERR_ARG, "rope_kv_write: bad sizes T=%d NH=%d NKV=%d HD=%d page=%d (HD must be even)",
                            T, NH, NKV, HD, page_size);
     if (T == 0) return FORGE_OK;
+    cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
-        rope_kv_write_kernel<TT, TT><<<T, 128, 0, stream>>>(qkv, positions, slot_mapping, (TT*)q_out,
-                                                              (TT*)kv_cache, NH, NKV, HD, page_size, theta, rotary));
-    return forge::check_launch("rope_kv_write");
+        e = forge::launch(rope_kv_write_kernel<TT, TT>, dim3(T, ((NH + 2 * NKV) * (HD / 2) + 127) / 128), dim3(128), 0, stream, 1,
+                          qkv, positions, slot_mapping, (TT*)q_out, (TT*)kv_cache, NH, NKV, HD, page_size, theta, rotary));
+    return forge::check_launch("rope_kv_write", e);
 }

@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -78,6 +80,8 @@ argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int32_t* __restrict__ tokens,
                                       const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                                       const float* __restrict__ penalty, int V) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int r = blockIdx.x;
     const float pen = penalty[r];
     if (pen == 1.0f) return;
@@ -99,6 +103,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ int ired[32];
     __shared__ float wsum[kThreads / 32];
     __shared__ int s_first, s_last;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     const float inv_t = 1.0f / temperature[r];
@@ -200,8 +206,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 extern "C" int forge_argmax(const float* logits, int32_t* out, int R, int V, cudaStream_t stream) {
     if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "argmax: bad sizes R=%d V=%d", R, V);
     if (R == 0) return FORGE_OK;
-    argmax_kernel<<<R, kThreads, 0, stream>>>(logits, out, V);
-    return forge::check_launch("argmax");
+    return forge::check_launch("argmax", forge::launch(argmax_kernel, dim3(R), dim3(kThreads), 0, stream, 1, logits, out, V));
 }
 
 extern "C" int forge_repeat_penalty(float* logits, const int32_t* tokens, const int32_t* counts,
@@ -209,8 +214,7 @@ extern "C" int forge_repeat_penalty(float* logits, const int32_t* tokens, const 
                                     cudaStream_t stream) {
     if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "repeat_penalty: bad sizes R=%d V=%d", R, V);
     if (R == 0) return FORGE_OK;
-    repeat_penalty_kernel<<<R, 256, 0, stream>>>(logits, tokens, counts, offsets, penalty, V);
-    return forge::check_launch("repeat_penalty");
+    return forge::check_launch("repeat_penalty", forge::launch(repeat_penalty_kernel, dim3(R), dim3(256), 0, stream, 1, logits, tokens, counts, offsets, penalty, V));
 }
 
 // temperature[r] must be > 0 (the caller routes temperature <= 0 to forge_argmax).
@@ -219,8 +223,7 @@ extern "C" int forge_sample(const float* logits, const float* temperature, const
                             cudaStream_t stream) {
     if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "sample: bad sizes R=%d V=%d", R, V);
     if (R == 0) return FORGE_OK;
-    sample_kernel<<<R, kThreads, 0, stream>>>(logits, temperature, top_k, top_p, u, out, V);
-    return forge::check_launch("sample");
+    return forge::check_launch("sample", forge::launch(sample_kernel, dim3(R), dim3(kThreads), 0, stream, 1, logits, temperature, top_k, top_p, u, out, V));
 }
 
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }
