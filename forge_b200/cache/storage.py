@@ -1,10 +1,11 @@
-"""Device storage behind the cache manager, laid out from the model's layers.
+"""Device storage behind the cache manager, laid out from the model's schedule of layer runs.
 
-Every layer's mixer states what it needs (``cache_spec``): keys/values in pages, fixed-size state, or
-nothing.  Layers with equal key/value needs share a group (one page pool, one block table per request);
-each such layer owns a tensor [num_pages, 2, kv_heads, page_size, head_dim] with a page's keys and values
-adjacent.  A state-keeping layer owns a tensor [max_requests, *shape] addressed by request slot.  A layer
-whose plan says ``cache_from`` gets a read-only view of another layer's storage and allocates nothing.
+Every run of a layer's mixer states what it needs (``cache_spec``): keys/values in pages, fixed-size
+state, or nothing.  Runs with equal key/value needs share a group (one page pool, one block table per
+request); each such run owns a tensor [num_pages, 2, kv_heads, page_size, head_dim] with a page's keys
+and values adjacent.  A state-keeping run owns a tensor [max_requests, *shape] addressed by request slot.
+A run whose layer says ``cache_from`` gets a read-only view of an earlier run's storage and allocates
+nothing.  ("Layer" below means one position of the schedule.)
 """
 from dataclasses import dataclass
 from typing import Optional

@@ -62,19 +62,35 @@ class Model:
         self.loaded = True
 
     # ---------------------------------------------------------------------------------- cache needs
+    # Caches belong to positions of the schedule, not to layers: a layer that runs twice shares its weights
+    # between the two runs but each run keeps keys/values (or state) of its own.
     def cache_specs(self):
-        return [blk.mixer.cache_spec() for blk in self.blocks]
+        """Per schedule position: what that run of its layer's mixer keeps."""
+        return [self.blocks[i].mixer.cache_spec() for i in self.plan.schedule]
 
     def cache_from(self):
-        return [spec.cache_from for spec in self.plan.layers]
+        """Per schedule position: the earlier position whose cache it reads instead of keeping one (None:
+        its own).  A LayerSpec names a LAYER in ``cache_from``; that resolves to the latest earlier run of
+        that layer."""
+        out = []
+        for pos, i in enumerate(self.plan.schedule):
+            src_layer = self.plan.layers[i].cache_from
+            if src_layer is None:
+                out.append(None)
+                continue
+            earlier = [q for q in range(pos) if self.plan.schedule[q] == src_layer]
+            if not earlier:
+                raise ConfigError(f"layer {i} reads the cache of layer {src_layer}, which has not run before it")
+            out.append(earlier[-1])
+        return out
 
     # ---------------------------------------------------------------------------------- forward
-    def forward(self, batch, layer_caches):
-        """Runs the step's tokens through all layers; returns fp32 logits [R,V] at ``batch.logits_rows``
-        (None if no row is wanted)."""
+    def forward(self, batch, position_caches):
+        """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run.
+        Returns fp32 logits [R,V] at ``batch.logits_rows`` (None if no row is wanted)."""
         residual = self.embedding.forward(batch.token_ids, status=batch.status)
-        for i in self.plan.schedule:
-            self.blocks[i].forward(residual, batch, layer_caches[i])
+        for pos, i in enumerate(self.plan.schedule):
+            self.blocks[i].forward(residual, batch, position_caches[pos])
         if batch.num_logits == 0:
             return None
         x = self.final_norm.forward(residual, rows=batch.logits_rows)

@@ -1,0 +1,296 @@
+"""Each part alone against its plain formula, and the claim that the engine is open to other parts: a toy
+mixer with state of its own and a toy architecture (different mixers in different layers, a layer that
+runs twice, a layer that reads another layer's cache, a windowed layer) are defined HERE, registered, built
+and stepped without touching the framework's files."""
+import json
+import os
+from dataclasses import asdict, dataclass
+
+import pytest
+import torch
+
+from helpers import TOL, max_rel_err, random_tokens
+from plain import llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rt(dtype):
+    from forge_b200.parts import Runtime
+    return Runtime(torch.device(DEV), dtype)
+
+
+def _rand(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+DT = [torch.float32, torch.bfloat16]
+PART_TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_rmsnorm_part(dtype):
+    from forge_b200.config import PartSpec
+    from forge_b200.parts import build_part
+    part = build_part("norm", PartSpec("rmsnorm", {"size": 88, "eps": 1e-4}), _rt(dtype))
+    assert list(part.tensor_specs()) == ["weight"] and part.tensor_specs()["weight"].shape == (88,)
+    w, x = _rand(88, seed=1) + 1.0, _rand(9, 88, scale=2.0)
+    part.bind({"weight": w})
+    got = part.forward(x.to(DEV)).float().cpu()
+    want = P.rms_norm(x.double(), w.double(), 1e-4).float()
+    assert got.dtype == torch.float32 and max_rel_err(got, want) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_swiglu_part(dtype):
+    from forge_b200.config import PartSpec
+    from forge_b200.parts import build_part
+    H, I, T = 72, 200, 11
+    part = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I}), _rt(dtype))
+    specs = part.tensor_specs()
+    assert specs["mlp.gate_proj.weight"].shape == (I, H) and specs["mlp.down_proj.weight"].shape == (H, I)
+    t = {n: _rand(*s.shape, seed=i, scale=0.2).to(torch.bfloat16) for i, (n, s) in enumerate(specs.items())}
+    part.bind(t)
+    x = _rand(T, H, seed=9).to(dtype)
+    residual = _rand(T, H, seed=10)
+    res_dev = residual.clone().to(DEV)
+    part.forward(x.to(DEV), res_dev)
+    want = residual.double() + P.swiglu(x.double(), t["mlp.gate_proj.weight"].double(), t["mlp.up_proj.weight"].double(),
+                                        t["mlp.down_proj.weight"].double())
+    assert max_rel_err(res_dev, want) <= PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embedding_and_tied_head(dtype):
+    from forge_b200.config import PartSpec
+    from forge_b200.parts import build_part
+    V, H = 130, 40
+    emb = build_part("embedding", PartSpec("embedding", {"vocab_size": V, "hidden_size": H}), _rt(dtype))
+    head = build_part("lm_head", PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True}), _rt(dtype))
+    table = _rand(V, H).to(torch.bfloat16)
+    emb.bind({"weight": table})
+    head.bind({}, shared_table=emb.table)
+    assert head.tensor_specs()["weight"].required is False
+    ids = torch.tensor([3, 129, 0], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), table.float()[ids.cpu().long()])
+    x = _rand(4, H, seed=2).to(dtype)
+    want = P.linear(x.double(), table.double())
+    assert max_rel_err(head.forward(x.to(DEV)), want) <= PART_TOL[dtype]
+
+
+def _attention_harness(dtype, window, page_size=8):
+    """An attention mixer with a cache of its own, fed one request in two portions and a decode token."""
+    from forge_b200.cache import CacheStorage
+    from forge_b200.config import PartSpec
+    from forge_b200.engine import StepEntry, build_step_batch
+    from forge_b200.parts import build_part
+    H, NH, NKV, HD, theta = 48, 6, 2, 16, 777.0
+    spec = PartSpec("attention", {"hidden_size": H, "num_heads": NH, "num_kv_heads": NKV, "head_dim": HD,
+                                  "qkv_bias": True, "window": window,
+                                  "position": PartSpec("rope", {"head_dim": HD, "theta": theta})})
+    mixer = build_part("mixer", spec, _rt(dtype))
+    t = {n: _rand(*s.shape, seed=i, scale=0.3).to(torch.bfloat16) for i, (n, s) in enumerate(mixer.tensor_specs().items())}
+    mixer.bind(t)
+    storage = CacheStorage([mixer.cache_spec()], [None], page_size, 16, 2, dtype, torch.device(DEV))
+    T = 29
+    x = _rand(T, H, seed=50).to(dtype)
+    got = torch.zeros(T, H)
+    storage.manager.admit("r")
+    for a, b in [(0, 13), (13, 28), (28, 29)]:
+        batch = build_step_batch([StepEntry("r", [0] * (b - a), [])], storage.manager, torch.device(DEV), 8)
+        res = torch.zeros(b - a, H, device=DEV)
+        mixer.forward(x[a:b].to(DEV), batch, storage.layers[0], res)
+        got[a:b] = res.cpu()
+        storage.manager.release_out_of_window("r")
+        storage.manager.check()
+    # plain: whole sequence
+    xd = x.double()
+    w = {k: v.double() for k, v in t.items()}
+    q = P.linear(xd, w["self_attn.q_proj.weight"], w["self_attn.q_proj.bias"]).view(T, NH, HD)
+    k = P.linear(xd, w["self_attn.k_proj.weight"], w["self_attn.k_proj.bias"]).view(T, NKV, HD)
+    v = P.linear(xd, w["self_attn.v_proj.weight"], w["self_attn.v_proj.bias"]).view(T, NKV, HD)
+    pos = torch.arange(T)
+    o = P.attention(P.rope(q, pos, theta), P.rope(k, pos, theta), v, window=window)
+    want = P.linear(o.reshape(T, NH * HD), w["self_attn.o_proj.weight"])
+    return got, want, storage
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("window", [None, 5])
+def test_attention_part_with_its_position_encoding_and_cache(dtype, window):
+    got, want, storage = _attention_harness(dtype, window)
+    assert max_rel_err(got, want) <= PART_TOL[dtype]
+    if window is not None:      # 29 tokens, window 5, pages of 8: positions 0..23 are behind every future query
+        assert storage.manager.block_table("r", "kv2x16_win5")[:3] == [-1, -1, -1]
+
+
+# ---------------------------------------------------------------------------------------------------
+# A toy mixer with state of its own, and a toy architecture around it, defined in this test file only.
+
+H_TOY = 40
+
+
+def _toy_mixer_class():
+    from forge_b200.parts import Part, StateSpec
+    from forge_b200.weights import TensorSpec
+
+    class RunningMeanMixer(Part):
+        """y_t = W . mean(x_1..x_t): per request it keeps the running sum of its inputs and their count, a
+        state of fixed size that must survive being cut into portions."""
+
+        def __init__(self, rt, hidden_size):
+            self.rt, self.h = rt, hidden_size
+            self.w = None
+
+        def tensor_specs(self):
+            return {"mixer.proj.weight": TensorSpec((self.h, self.h))}
+
+        def bind(self, tensors):
+            self.w = tensors["mixer.proj.weight"].to(device=self.rt.device, dtype=torch.float32)
+
+        def cache_spec(self):
+            return StateSpec((self.h + 1,), torch.float32)
+
+        def forward(self, x, batch, cache, residual):
+            xs = x.float()
+            for s in range(batch.num_requests):
+                a, b = batch.host_q_start[s], batch.host_q_start[s + 1]
+                st = cache.state[batch.host_slots[s]]
+                csum = torch.cumsum(xs[a:b], 0) + st[:self.h]
+                cnt = st[self.h] + torch.arange(1, b - a + 1, device=xs.device)
+                residual[a:b] += (csum / cnt[:, None]) @ self.w.t()
+                st[:self.h] = csum[-1]
+                st[self.h] = cnt[-1]
+
+    return RunningMeanMixer
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = H_TOY
+    intermediate_size: int = 56
+    num_heads: int = 5
+    num_kv_heads: int = 5
+    head_dim: int = 8
+    eps: float = 1e-5
+    theta: float = 100.0
+    window: int = 7
+    max_position_embeddings: int = 256
+
+    @classmethod
+    def from_dict(cls, d, architecture="ToyForCausalLM"):
+        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(asdict(self), architectures=["ToyForCausalLM"])
+
+    def plan(self):
+        from forge_b200.config import LayerSpec, ModelPlan, PartSpec
+        norm = PartSpec("rmsnorm", {"size": self.hidden_size, "eps": self.eps})
+        ffn = PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size})
+
+        def attn(window):
+            return PartSpec("attention", {"hidden_size": self.hidden_size, "num_heads": self.num_heads,
+                                          "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": window,
+                                          "position": PartSpec("rope", {"head_dim": self.head_dim, "theta": self.theta})})
+        toy = PartSpec("toy_running_mean", {"hidden_size": self.hidden_size})
+        norms = {"input": norm, "post_mixer": norm}
+        layers = [
+            LayerSpec("pre_norm", attn(None), ffn, norms, "model.layers.0."),
+            LayerSpec("pre_norm", toy, ffn, norms, "model.layers.1."),
+            LayerSpec("pre_norm", attn(None), ffn, norms, "model.layers.2.", cache_from=0),   # reads layer 0's keys
+            LayerSpec("pre_norm", attn(self.window), ffn, norms, "model.layers.3."),           # a window of its own
+        ]
+        return ModelPlan(hidden_size=self.hidden_size, vocab_size=self.vocab_size, max_positions=self.max_position_embeddings,
+                         embedding=PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}),
+                         final_norm=norm,
+                         lm_head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied": False}),
+                         layers=layers, schedule=[0, 1, 0, 2, 3])                              # layer 0 runs twice
+
+
+def plain_toy_logits(cfg, w, ids):
+    """The toy model on one whole sequence, from the plain functions, float64."""
+    T = len(ids)
+    pos = torch.arange(T)
+    h = P.embedding(torch.tensor(ids), w["model.embed_tokens.weight"])
+    kv_of_run = {}
+
+    def attn_layer(p, h, run, window, read_run=None):
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], cfg.eps)
+        q = P.rope(P.linear(x, w[p + "self_attn.q_proj.weight"]).view(T, cfg.num_heads, cfg.head_dim), pos, cfg.theta)
+        if read_run is None:
+            k = P.rope(P.linear(x, w[p + "self_attn.k_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim), pos, cfg.theta)
+            v = P.linear(x, w[p + "self_attn.v_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim)
+            kv_of_run[run] = (k, v)
+        else:
+            k, v = kv_of_run[read_run]
+        a = P.attention(q, k, v, window=window)
+        return h + P.linear(a.reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+
+    def ffn(p, h):
+        x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg.eps)
+        return h + P.swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+
+    for run, layer in enumerate([0, 1, 0, 2, 3]):
+        p = f"model.layers.{layer}."
+        if layer == 1:
+            x = P.rms_norm(h, w[p + "input_layernorm.weight"], cfg.eps)
+            mean = torch.cumsum(x, 0) / torch.arange(1, T + 1, dtype=x.dtype)[:, None]
+            h = h + P.linear(mean, w[p + "mixer.proj.weight"])
+        elif layer == 2:
+            h = attn_layer(p, h, run, None, read_run=2)        # the latest earlier run of layer 0 is run 2
+        else:
+            h = attn_layer(p, h, run, cfg.window if layer == 3 else None)
+        h = ffn(p, h)
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg.eps), w["lm_head.weight"])
+
+
+@pytest.fixture
+def toy_registered():
+    from forge_b200.config import register_architecture, unregister_architecture
+    from forge_b200.parts import register_part, unregister_part
+    register_part("mixer", "toy_running_mean", _toy_mixer_class())
+    register_architecture("ToyForCausalLM", ToyConfig)
+    yield
+    unregister_part("mixer", "toy_running_mean")
+    unregister_architecture("ToyForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype, tmp_path):
+    import schedules
+    from forge_b200.config import load_config
+    from forge_b200.engine import ModelRunner, StepEntry
+    from forge_b200.weights import write_random_model
+    from plain.safetensors_reader import read_safetensors
+    cfg = ToyConfig()
+    d = write_random_model(cfg, str(tmp_path / "toy"), seed=4, std=0.12, embed_std=0.6, norm_std=0.15)
+    assert isinstance(load_config(d), ToyConfig)
+    assert json.load(open(os.path.join(d, "config.json")))["architectures"] == ["ToyForCausalLM"]
+    w = {k: torch.from_numpy(v).double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
+    assert "model.layers.1.mixer.proj.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+    reqs = {f"t{i}": random_tokens(n, cfg.vocab_size, seed=30 + i) for i, n in enumerate([41, 64, 23, 90])}
+    want = {rid: plain_toy_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
+    # the toy mixer plans its work from host lists, so its steps cannot be replayed as a CUDA graph
+    runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=240, max_requests=3, cuda_graphs=False)
+    groups = set(runner.manager.groups)
+    assert groups == {"kv5x8_full", "kv5x8_win7"}, groups          # two needs, two pools; the toy layer has none
+    for steps in (schedules.whole(reqs), schedules.changing_portions(reqs), schedules.mixed(reqs, max_live=3)):
+        got = {rid: torch.zeros(len(t), cfg.vocab_size) for rid, t in reqs.items()}
+        for entries, end in steps:
+            for rid, p, n in entries:
+                if not runner.is_live(rid):
+                    runner.admit(rid)
+            lg = runner.step([StepEntry(rid, reqs[rid][p:p + n], list(range(n))) for rid, p, n in entries]).cpu()
+            o = 0
+            for rid, p, n in entries:
+                got[rid][p:p + n] = lg[o:o + n]
+                o += n
+            for rid in end:
+                runner.release(rid)
+            runner.manager.check()
+        for rid in reqs:
+            assert max_rel_err(got[rid], want[rid]) <= TOL[dtype], rid
+        assert runner.manager.num_free_pages() == {g: runner.num_pages for g in groups}
