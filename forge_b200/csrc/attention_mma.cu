@@ -15,6 +15,7 @@
 // them.  That is how a single decode token with a long context fills the GPU.
 #include <mma.h>
 
+#include "attention_no_alloc.h"
 #include "common.cuh"
 
 #ifndef FORGE_ATT_HD
@@ -352,6 +353,62 @@ extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* ou
     if (rc != FORGE_OK || num_splits == 1) return rc;
     const long warps = (long)num_tiles * NKV * p.part_rows;
     return forge::check_launch("attention_merge", forge::launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, 1, p, num_tiles));
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_no_alloc.h): same kernels, scratch in a static array.
+namespace {
+
+static __device__ __align__(256) float g_static_scratch[FORGE_ATT_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address of
+// the array on the CURRENT device has to be asked for, once per device.
+int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_mma_static: cannot tell the current device (%s)",
+                           e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_mma_static: cudaGetSymbolAddress failed: %s",
+                               cudaGetErrorString(e));
+        g_static_scratch_addr[dev] = static_cast<float*>(ptr);
+    }
+    *out = g_static_scratch_addr[dev];
+    return FORGE_OK;
+}
+
+}  // namespace
+
+extern "C" int forge_paged_attention_mma_static(const void* q, const void* kv, void* out, const int32_t* block_table,
+                                                const int32_t* tile_req, const int32_t* tile_row0,
+                                                const int32_t* q_start, const int32_t* ctx_before, int num_tiles,
+                                                int max_rows, int NH, int NKV, int head_dim, int page_size,
+                                                int max_pages, int window, int num_splits, float scale,
+                                                cudaStream_t stream) {
+    if (num_tiles < 0 || NKV <= 0 || num_splits < 1 || max_rows < 1)
+        return forge::fail(FORGE_ERR_ARG, "paged_attention_mma_static: bad sizes tiles=%d NKV=%d splits=%d rows=%d",
+                           num_tiles, NKV, num_splits, max_rows);
+    const unsigned long long rows = (unsigned long long)num_tiles * NKV * num_splits * (max_rows <= 16 ? 16 : BQ);
+    const unsigned long long need = rows * (HD + 2);
+    if (need > FORGE_ATT_STATIC_SCRATCH_FLOATS)
+        return forge::fail(FORGE_ERR_UNSUPPORTED,
+                           "paged_attention_mma_static: %llu scratch floats needed (tiles %d x kv heads %d x slices %d), "
+                           "the built-in array holds %u; use fewer slices or forge_paged_attention_mma with your own scratch",
+                           need, num_tiles, NKV, num_splits, FORGE_ATT_STATIC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != FORGE_OK) return rc;
+    // partial outputs first (rows * HD floats, a multiple of 16 floats), then the (max, sum) pairs
+    return forge_paged_attention_mma(q, kv, out, scratch, scratch + rows * HD, block_table, tile_req, tile_row0, q_start,
+                                     ctx_before, num_tiles, max_rows, NH, NKV, head_dim, page_size, max_pages, window,
+                                     num_splits, scale, stream);
 }
 
 extern "C" int forge_attention_head_dim() { return HD; }
