@@ -25,7 +25,7 @@
 namespace {
 
 constexpr int HD = FORGE_ATT_HD;
-constexpr int BQ = 64, BKV = 64;
+constexpr int BQ = 64;
 constexpr int LD = HD + 8;                    // padded row length in shared memory (bf16 elements)
 constexpr int CPR = HD / 8;                   // 16-byte chunks per row
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
@@ -71,21 +71,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // Loads keys/values of token indices [t0, t0+BKV) of the request into one shared-memory buffer; rows
 // outside [lo, hi) are zero-filled (their scores are masked and their values must not be NaN).
+// Each lane first finds the cache row (page * 2 * NKV + kvh) * page_size + slot of tile rows `lane` and
+// `lane + 32` through the block table; the copy loop then gets a row's index by shuffle, so the table is
+// read once per row and not once per 16-byte chunk.
+template <int BKV>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const AttnParams& p,
                                              const int32_t* table, int kvh, int t0, int lo, int hi) {
-    const size_t head_stride = (size_t)p.page_size * HD;
-    const size_t page_stride = 2 * (size_t)p.NKV * head_stride;
+    const int lane = threadIdx.x & 31;
+    int ridx[(BKV + 31) / 32];
+#pragma unroll
+    for (int i = 0; i < (BKV + 31) / 32; ++i) {
+        const int t = t0 + lane + 32 * i;
+        ridx[i] = -1;
+        if (lane + 32 * i < BKV && t >= lo && t < hi)
+            ridx[i] = (table[t / p.page_size] * 2 * p.NKV + kvh) * p.page_size + t % p.page_size;
+    }
+    const int v_rows = p.NKV * p.page_size;                 // a page's values follow its keys
+#pragma unroll 4
     for (int c = threadIdx.x; c < BKV * CPR; c += blockDim.x) {
         const int row = c / CPR, ch = c % CPR;
-        const int t = t0 + row;
+        int r = __shfl_sync(0xffffffffu, ridx[0], row & 31);
+        if (BKV > 32) {
+            const int r1 = __shfl_sync(0xffffffffu, ridx[(BKV + 31) / 32 - 1], row & 31);
+            r = row < 32 ? r : r1;
+        }
         __nv_bfloat16* kd = ks + row * LD + ch * 8;
         __nv_bfloat16* vd = vs + row * LD + ch * 8;
-        if (t >= lo && t < hi) {
-            const int page = table[t / p.page_size];
-            const __nv_bfloat16* kp = p.kv + (size_t)page * page_stride + (size_t)kvh * head_stride +
-                                      (size_t)(t % p.page_size) * HD + ch * 8;
+        if (r >= 0) {
+            const __nv_bfloat16* kp = p.kv + (size_t)r * HD + ch * 8;
             cp_async16(kd, kp);
-            cp_async16(vd, kp + (size_t)p.NKV * head_stride);
+            cp_async16(vd, kp + (size_t)v_rows * HD);
         } else {
             *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
@@ -93,11 +108,14 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
     }
 }
 
-__global__ void __launch_bounds__(128)
+// BKV: keys per iteration; QROWS: query rows staged per CTA (64: four warps of 16 rows, portions of
+// prompts; 16: one warp, decode tokens, where small buffers let many CTAs share an SM).
+template <int BKV, int QROWS>
+__global__ void __launch_bounds__(QROWS * 2)
 paged_attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BQ][LD]
-    __nv_bfloat16* ks = qs + BQ * LD;                                    // [2][BKV][LD]
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [QROWS][LD]
+    __nv_bfloat16* ks = qs + QROWS * LD;                                 // [2][BKV][LD]
     __nv_bfloat16* vs = ks + 2 * BKV * LD;                               // [2][BKV][LD]
 
     forge::pdl_launch_dependents();
@@ -110,13 +128,15 @@ paged_attention_mma_kernel(const AttnParams p) {
     const int rows_here = min(BQ, qlen * G - row0);
     const int32_t* table = p.block_table + (size_t)s * p.max_pages;
 
-    // key range of this tile and of this CTA's slice of it
+    // key range of this tile and of this CTA's slice of it (slices are counted in tiles of 64 keys whatever
+    // BKV is, so that the slicing does not depend on which instantiation runs)
     const int pos_lo = ctx + row0 / G, pos_hi = ctx + (row0 + rows_here - 1) / G;
     const int kv_hi = pos_hi + 1;
     const int kv_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int t_begin = kv_lo / BKV, t_end = (kv_hi + BKV - 1) / BKV;
+    const int t_begin = kv_lo / 64, t_end = (kv_hi + 63) / 64;
     const int per_split = (t_end - t_begin + p.num_splits - 1) / p.num_splits;
-    const int my_begin = t_begin + split * per_split, my_end = min(my_begin + per_split, t_end);
+    const int my_begin = (t_begin + split * per_split) * (64 / BKV);
+    const int my_end = min((t_begin + (split + 1) * per_split) * (64 / BKV), (kv_hi + BKV - 1) / BKV);
 
     // this thread's two rows (of the warp's 16): r_a = lane/4, r_b = r_a + 8
     const int wrow = warp * 16;
@@ -124,6 +144,10 @@ paged_attention_mma_kernel(const AttnParams p) {
     const int ra = row0 + wrow + (lane >> 2), rb = ra + 8;
     const int pos_a = ctx + ra / G, pos_b = ctx + rb / G;
     const bool valid_a = wrow + (lane >> 2) < rows_here, valid_b = wrow + (lane >> 2) + 8 < rows_here;
+    // positions of the warp's first row and of its last valid row: a key tile wholly at or below the first
+    // and wholly inside the window of the last needs no per-element mask
+    const int wpos_first = ctx + (row0 + wrow) / G;
+    const int wpos_last = ctx + (row0 + min(wrow + 15, rows_here - 1)) / G;
 
     float o_acc[HD / 8][4];
 #pragma unroll
@@ -132,7 +156,7 @@ paged_attention_mma_kernel(const AttnParams p) {
 
     if (my_begin < my_end) {
         // stage the query tile: row r -> token r / G, head kvh * G + r % G
-        for (int c = threadIdx.x; c < BQ * CPR; c += blockDim.x) {
+        for (int c = threadIdx.x; c < QROWS * CPR; c += blockDim.x) {
             const int row = c / CPR, ch = c % CPR;
             __nv_bfloat16* dst = qs + row * LD + ch * 8;
             if (row < rows_here) {
@@ -142,13 +166,13 @@ paged_attention_mma_kernel(const AttnParams p) {
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
         }
-        load_kv_tile(ks, vs, p, table, kvh, my_begin * BKV, kv_lo, kv_hi);
+        load_kv_tile<BKV>(ks, vs, p, table, kvh, my_begin * BKV, kv_lo, kv_hi);
         cp_async_commit();
 
         for (int t = my_begin; t < my_end; ++t) {
             const int buf = (t - my_begin) & 1;
             if (t + 1 < my_end) {
-                load_kv_tile(ks + (buf ^ 1) * BKV * LD, vs + (buf ^ 1) * BKV * LD, p, table, kvh, (t + 1) * BKV, kv_lo, kv_hi);
+                load_kv_tile<BKV>(ks + (buf ^ 1) * BKV * LD, vs + (buf ^ 1) * BKV * LD, p, table, kvh, (t + 1) * BKV, kv_lo, kv_hi);
                 cp_async_commit();
                 cp_async_wait<1>();
             } else {
@@ -174,19 +198,30 @@ paged_attention_mma_kernel(const AttnParams p) {
                     }
                 }
                 // scale, mask, online softmax (exp2 domain)
-                const int j0 = t * BKV + 2 * (lane & 3);
                 float mx_a = m_a, mx_b = m_b;
+                const bool unmasked = t * BKV + BKV - 1 <= wpos_first && (p.window <= 0 || t * BKV > wpos_last - p.window);
+                if (unmasked) {
 #pragma unroll
-                for (int i = 0; i < BKV / 8; ++i) {
+                    for (int i = 0; i < BKV / 8; ++i) {
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int j = j0 + i * 8 + e;
-                        const bool va = valid_a && j <= pos_a && (p.window <= 0 || j > pos_a - p.window);
-                        const bool vb2 = valid_b && j <= pos_b && (p.window <= 0 || j > pos_b - p.window);
-                        sc[i][e] = va ? sc[i][e] * p.scale_log2 : -INFINITY;
-                        sc[i][2 + e] = vb2 ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
-                        mx_a = fmaxf(mx_a, sc[i][e]);
-                        mx_b = fmaxf(mx_b, sc[i][2 + e]);
+                        for (int e = 0; e < 4; ++e) sc[i][e] *= p.scale_log2;
+                        mx_a = fmaxf(mx_a, fmaxf(sc[i][0], sc[i][1]));
+                        mx_b = fmaxf(mx_b, fmaxf(sc[i][2], sc[i][3]));
+                    }
+                } else {
+                    const int j0 = t * BKV + 2 * (lane & 3);
+#pragma unroll
+                    for (int i = 0; i < BKV / 8; ++i) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int j = j0 + i * 8 + e;
+                            const bool va = valid_a && j <= pos_a && (p.window <= 0 || j > pos_a - p.window);
+                            const bool vb2 = valid_b && j <= pos_b && (p.window <= 0 || j > pos_b - p.window);
+                            sc[i][e] = va ? sc[i][e] * p.scale_log2 : -INFINITY;
+                            sc[i][2 + e] = vb2 ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
+                            mx_a = fmaxf(mx_a, sc[i][e]);
+                            mx_b = fmaxf(mx_b, sc[i][2 + e]);
+                        }
                     }
                 }
                 mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -341,15 +376,23 @@ extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* ou
     AttnParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (__nv_bfloat16*)out, part_o, part_ml, block_table,
                  tile_req, tile_row0, q_start, ctx_before, NH, NKV, page_size, max_pages, window, num_splits,
                  max_rows <= 16 ? 16 : BQ, scale * 1.4426950408889634f};
-    constexpr int smem = (BQ + 4 * BKV) * LD * 2;
+    // one warp of rows (decode tokens): small buffers, many CTAs per SM; otherwise four warps and 64-key tiles
+    constexpr int smem_big = (64 + 4 * 64) * LD * 2, smem_small = (16 + 4 * 32) * LD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_big);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(paged_attention_mma_kernel<32, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_small);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_mma: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const int threads = 32 * ((max_rows + 15) / 16);
-    int rc = forge::check_launch("paged_attention_mma", forge::launch(paged_attention_mma_kernel, dim3(num_tiles, NKV, num_splits), dim3(threads), smem, stream, 1, p));
+    cudaError_t le;
+    if (max_rows <= 16)
+        le = forge::launch(paged_attention_mma_kernel<32, 16>, dim3(num_tiles, NKV, num_splits), dim3(32), smem_small, stream, 1, p);
+    else
+        le = forge::launch(paged_attention_mma_kernel<64, 64>, dim3(num_tiles, NKV, num_splits),
+                           dim3(32 * ((max_rows + 15) / 16)), smem_big, stream, 1, p);
+    int rc = forge::check_launch("paged_attention_mma", le);
     if (rc != FORGE_OK || num_splits == 1) return rc;
     const long warps = (long)num_tiles * NKV * p.part_rows;
     return forge::check_launch("attention_merge", forge::launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, 1, p, num_tiles));

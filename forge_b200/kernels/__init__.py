@@ -305,11 +305,12 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
     plan = attention_plan(batch, n_heads // n_kv_heads, q.device)
     if num_splits is None:
-        # decode-like steps (every tile one warp): slice the keys until about two CTAs per SM exist
+        # decode-like steps (every tile is one warp with small buffers, ten of which fit an SM): slice the
+        # keys until about eight CTAs per SM exist, so that enough loads are in flight to hide their latency
         base = plan["num_tiles"] * n_kv_heads
         num_splits = 1
         if plan["max_rows"] <= 16:
-            num_splits = max(1, min(plan["max_kv_tiles"], -(-2 * _sm_count(q.device) // base)))
+            num_splits = max(1, min(plan["max_kv_tiles"], -(-8 * _sm_count(q.device) // base)))
     part_o = part_ml = None
     if num_splits > 1:
         pr = 16 if plan["max_rows"] <= 16 else BQ_ROWS

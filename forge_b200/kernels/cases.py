@@ -1,0 +1,79 @@
+"""Runs ONE kernel at a named workload a few times: the small, self-contained cases that profiles/ are
+captured from (`ncu ... python -m forge_b200.kernels.cases <case>`), each also timed with CUDA events.
+
+Cases use the layer sizes of the TinyLlama-1.1B shape: hidden 2048, 32 heads / 4 kv heads of 64, feed-forward 5632.
+"""
+import sys
+from types import SimpleNamespace
+
+import torch
+
+from . import gemm_sm100, paged_attention_mma
+
+DEV = "cuda:0"
+H, I, NH, NKV, HD, PS = 2048, 5632, 32, 4, 64, 16
+
+
+def _bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _attention_inputs(reqs):
+    """reqs: [(context_before, q_len)]; pages laid out in order."""
+    pages = sum(-(-(c + q) // PS) for c, q in reqs)
+    max_pages = max(-(-(c + q) // PS) for c, q in reqs)
+    table = torch.zeros(len(reqs), max_pages, dtype=torch.int32)
+    q_start, nxt = [0], 0
+    for s, (c, q) in enumerate(reqs):
+        n = -(-(c + q) // PS)
+        table[s, :n] = torch.arange(nxt, nxt + n, dtype=torch.int32)
+        nxt += n
+        q_start.append(q_start[-1] + q)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(num_requests=len(reqs), host_q_start=q_start, host_context_before=[c for c, _ in reqs],
+                            q_start=i32(q_start), context_before=i32([c for c, _ in reqs]), attention_plan={})
+    return (_bf16(q_start[-1], NH * HD), _bf16(pages, 2, NKV, PS, HD), SimpleNamespace(block_table=table.to(DEV)), batch)
+
+
+def case(name):
+    if name == "gemm_decode_gateup":         # 8 tokens x [11264, 2048] weights, SwiGLU epilogue: 46 MB streamed
+        x, w = _bf16(8, H), _bf16(2 * I, H, scale=0.02)
+        return (lambda: gemm_sm100(x, w, epilogue="swiglu")), w.numel() * 2, 2 * 8 * w.numel()
+    if name == "gemm_decode_down":           # 8 tokens x [2048, 5632], residual accumulate, K cut over a cluster
+        x, w, r = _bf16(8, I), _bf16(H, I, scale=0.02), torch.zeros(8, H, device=DEV)
+        return (lambda: gemm_sm100(x, w, accumulate_into=r)), w.numel() * 2, 2 * 8 * w.numel()
+    if name == "gemm_prefill_gateup":        # 2048 tokens x [11264, 2048], SwiGLU epilogue: 94.5 GFLOP
+        x, w = _bf16(2048, H), _bf16(2 * I, H, scale=0.02)
+        return (lambda: gemm_sm100(x, w, epilogue="swiglu")), (x.numel() + w.numel() + 2048 * I) * 2, 2 * 2048 * w.numel()
+    if name == "gemm_prefill_down":          # 2048 tokens x [2048, 5632], residual accumulate: 47.2 GFLOP
+        x, w, r = _bf16(2048, I), _bf16(H, I, scale=0.02), torch.zeros(2048, H, device=DEV)
+        return (lambda: gemm_sm100(x, w, accumulate_into=r)), (x.numel() + w.numel()) * 2 + r.numel() * 8, 2 * 2048 * w.numel()
+    if name == "attention_decode":           # 64 requests, 1024 cached tokens each, one new token: 67 MB of K/V
+        q, kv, g, b = _attention_inputs([(1023, 1)] * 64)
+        return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 64 * 1024 * 2 * NKV * HD * 2, 4 * 64 * 1024 * NH * HD
+    if name == "attention_prefill":          # one request, 2048 tokens, causal: 17.2 GFLOP
+        q, kv, g, b = _attention_inputs([(0, 2048)])
+        return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
+    raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_prefill_gateup "
+                     "gemm_prefill_down attention_decode attention_prefill")
+
+
+def main(argv):
+    name = argv[1] if len(argv) > 1 else ""
+    fn, nbytes, flops = case(name)
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / 3 * 1e3
+    print(f"{name}: {us:.1f} us per launch (3 launches back to back, warm L2), "
+          f"{nbytes / us / 1e3:.0f} GB/s of algorithmic bytes, {flops / us / 1e6:.1f} TFLOP/s")
+
+
+if __name__ == "__main__":
+    main(sys.argv)
