@@ -487,6 +487,247 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Few rows, every SM busy: the same weight-major tiles, but the (row tile, k-block) units of work are dealt
+// out evenly to one persistent CTA per SM ("stream-K").  A CTA walks its contiguous range of units, which
+// may end in the middle of one row tile and continue into the next; each piece of a tile it computes is a
+// FRAGMENT.  The fragment that holds a tile's last k-blocks owns the tile: it waits for the other
+// fragments' partial sums (written to a workspace in global memory, announced by a flag), adds them in
+// fragment order (so the sum never depends on timing), applies the epilogue and writes C.  The producers
+// of those partials are CTAs with lower indices, which hold an SM since before the owner started, so the
+// wait cannot starve; it is bounded all the same.
+//   Because the units are equal, all SMs stream the same number of weight bytes whatever N is: this is what
+// makes a [2048 x 2048] projection (16 row tiles) use 128+ SMs and a [11264 x 2048] one (88 tiles) use all.
+template <int NT> struct StreamKCfg {
+    static constexpr int kStageBytes = BM * BK * 2 + NT * BK * 2;
+    static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes > 12 ? 12 : (kSmemLimit - 2048) / kStageBytes;
+    static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
+    static constexpr int smem_bytes(int stages) { return stages * kStageBytes + 1024 + 1024; }
+};
+
+struct StreamKWork {
+    int debug;
+    float* partials;      // [tiles_n][max_parts][NT][128]
+    int* flags;           // [tiles_n][max_parts], zero between launches
+    int per_cta;          // units per CTA
+    int max_parts;
+};
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                          const GemmParams p, const StreamKWork wk, const int kStages) {
+    using C = StreamKCfg<NT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes);
+    uint64_t* full = bars;                          // [kStages]
+    uint64_t* empty = bars + C::kStages;            // [kStages]
+    uint64_t* acc_full = bars + 2 * C::kStages;     // [2]
+    uint64_t* acc_empty = bars + 2 * C::kStages + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int tiles_n = (p.N + BM - 1) / BM;
+    const int total = tiles_n * num_kb;
+    const int u_begin = min((int)blockIdx.x * wk.per_cta, total), u_end = min(u_begin + wk.per_cta, total);
+    // Fragments are worked on from the LAST tile of the range to the first.  The last one is the piece this
+    // CTA may have to hand to its successor, the first one the piece for which it may need its predecessors:
+    // handing on first and collecting last means the partial sums a CTA needs were written long before it
+    // asks for them, so the owners' waits cost (almost) nothing and no CTA waits on a chain of others.
+    const int tile_first = u_begin / num_kb, tile_last = u_end > u_begin ? (u_end - 1) / num_kb : tile_first - 1;
+    // i-th unit in processing order
+    auto unit_at = [&](int i) {
+        int t = tile_last;
+        for (;; --t) {
+            const int lo = max(u_begin, t * num_kb), hi = min(u_end, (t + 1) * num_kb);
+            if (i < hi - lo) return lo + i;
+            i -= hi - lo;
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        *abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        mbar_fence_init();
+        prefetch_tensormap(&tmap_w);
+        prefetch_tensormap(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    forge::pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // the weights do not depend on earlier kernels: the first ring of stages is requested before the wait
+            const int n_units = u_end - u_begin;
+            const int first = min(n_units, kStages);
+            for (int i = 0; i < first; ++i) {
+                const int u = unit_at(i);
+                mbar_arrive_expect_tx(&full[i], C::kStageBytes);
+                tma_load_2d(tiles + i * C::kStageBytes, &tmap_w, &full[i], (u % num_kb) * BK, (u / num_kb) * BM);
+            }
+            forge::pdl_wait();
+            for (int i = 0; i < first; ++i)
+                tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_x, &full[i], (unit_at(i) % num_kb) * BK, 0);
+            bool ok = true;
+            for (int i = first; i < n_units && ok; ++i) {
+                const int s = i % kStages, u = unit_at(i);
+                if (!(ok = mbar_wait(&empty[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
+                mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                uint8_t* dst = tiles + s * C::kStageBytes;
+                tma_load_2d(dst, &tmap_w, &full[s], (u % num_kb) * BK, (u / num_kb) * BM);
+                tma_load_2d(dst + BM * BK * 2, &tmap_x, &full[s], (u % num_kb) * BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, NT);
+            bool ok = true;
+            int frag = 0, i = 0;
+            for (int tile = tile_last; tile >= tile_first && ok; --tile, ++frag) {
+                const int f_begin = max(u_begin, tile * num_kb), f_end = min(u_end, (tile + 1) * num_kb);
+                const int a = frag & 1;
+                if (!(ok = mbar_wait(&acc_empty[a], ((frag >> 1) & 1) ^ 1, abort, p.status))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + a * NT;
+                for (int u = f_begin; u < f_end; ++u, ++i) {
+                    const int s = i % kStages;
+                    if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
+                    tc_fence_after_sync();
+                    const uint32_t w_addr = smem_u32(tiles + s * C::kStageBytes);
+                    const uint32_t x_addr = w_addr + BM * BK * 2;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(d_tmem, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
+                                  umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (u != f_begin || k != 0));
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int n_local = quarter * 32 + lane;
+        const int et = threadIdx.x - 64;            // 0..127 among the epilogue threads
+        forge::pdl_wait();
+        bool ok = true;
+
+        // Finishes a tile this CTA owns: adds the `part` earlier fragments' partial sums (if any) in fragment
+        // order, applies the epilogue and writes C.  Returns false if the bounded wait ran out.
+        auto finish_tile = [&](float (&acc)[NT], int tile, int part) -> bool {
+            if (part > 0) {
+                int* tile_flags = wk.flags + tile * wk.max_parts;
+                if (et < part) {
+                    const unsigned long long t0 = global_ns();
+                    while (ld_acquire(&tile_flags[et]) == 0) {
+                        if (*abort || global_ns() - t0 > kWaitLimitNs) {
+                            *abort = 1;
+                            if (p.status) atomicOr(p.status, 2);
+                            break;
+                        }
+                    }
+                }
+                epilogue_bar();
+                if (*abort) return false;
+                for (int q = 0; q < part; ++q) {
+                    const float* src = wk.partials + ((size_t)tile * wk.max_parts + q) * NT * BM;
+#pragma unroll
+                    for (int m = 0; m < NT; ++m)
+                        if (m < p.M) acc[m] += __ldcg(src + m * BM + n_local);
+                }
+                epilogue_bar();
+                if (et < part) tile_flags[et] = 0;
+            }
+            // a thread holds weight row n for all tokens; per token a warp writes 32 consecutive columns
+            const int n = tile * BM + n_local;
+            const float b = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+#pragma unroll
+            for (int m = 0; m < NT; ++m) {
+                if (m >= p.M) break;
+                const float v = acc[m] + b;
+                if (p.epilogue == EPI_SWIGLU_BF16) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                    if ((lane & 1) == 0 && n + 1 < p.N)
+                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * (p.N >> 1) + (n >> 1)] =
+                            __float2bfloat16_rn(silu(v) * other);
+                } else if (n < p.N) {
+                    if (p.epilogue == EPI_STORE_BF16) {
+                        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                    } else {
+                        float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                        *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;
+                    }
+                }
+            }
+            return true;
+        };
+
+        int frag = 0;
+        for (int tile = tile_last; tile >= tile_first && ok; --tile, ++frag) {
+            const int f_begin = max(u_begin, tile * num_kb), f_end = min(u_end, (tile + 1) * num_kb);
+            const int kb0 = f_begin - tile * num_kb, kb1 = f_end - tile * num_kb;
+            const int a = frag & 1;
+            if (!(ok = mbar_wait(&acc_full[a], (frag >> 1) & 1, abort, p.status))) break;
+            tc_fence_after_sync();
+            float acc[NT];
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * NT;
+#pragma unroll
+            for (int c = 0; c < NT; c += 16) {
+                uint32_t r[16];
+                tmem_ld_32x32b_x16(t_row + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(r[i]);
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[a]);             // the MMA warp may reuse this accumulator now
+            if (wk.debug == 1) continue;
+            // which fragment of its tile is this?  The tile's first unit belongs to CTA c0.
+            const int part = (int)blockIdx.x - (tile * num_kb) / wk.per_cta;
+            if (kb1 < num_kb) {
+                // not the owner: park the partial sum and announce it
+                float* my_partial = wk.partials + ((size_t)tile * wk.max_parts + part) * NT * BM;
+#pragma unroll
+                for (int m = 0; m < NT; ++m)
+                    if (m < p.M) my_partial[m * BM + n_local] = acc[m];
+                __threadfence();
+                epilogue_bar();
+                if (et == 0) st_release(&wk.flags[tile * wk.max_parts + part], 1);
+            } else {
+                ok = finish_tile(acc, tile, kb0 > 0 ? part : 0);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 int g_num_sms = 0;
 
 template <int BN>
@@ -524,12 +765,62 @@ int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams
                                              C::smem_bytes(stages), stream, ksplit, tw, tx, p, ksplit, stages));
 }
 
+// workspace for the stream-K partial sums and flags, per device, handed over once by the caller
+struct Workspace { void* ptr = nullptr; long long bytes = 0; };
+Workspace g_workspace[64];
+constexpr long long kFlagBytes = 256 * 1024;      // flags first (zeroed by the caller), partials after
+
+template <int NT>
+int launch_streamk(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+    using C = StreamKCfg<NT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_streamk_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::smem_bytes(C::kStages));
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
+                                                 C::smem_bytes(C::kStages), cudaGetErrorString(e));
+        configured = true;
+    }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int tiles_n = (p.N + BM - 1) / BM, num_kb = (p.K + BK - 1) / BK;
+    const int total = tiles_n * num_kb;
+    int grid = total < g_num_sms ? total : g_num_sms;
+    const int per_cta = (total + grid - 1) / grid;
+    grid = (total + per_cta - 1) / per_cta;
+    const int max_parts = (num_kb + per_cta - 1) / per_cta + 1;
+    const long long need = kFlagBytes + (long long)tiles_n * max_parts * NT * BM * 4;
+    if (dev < 0 || dev >= 64 || !g_workspace[dev].ptr || g_workspace[dev].bytes < need ||
+        (long long)tiles_n * max_parts * 4 > kFlagBytes)
+        return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: the stream-K workspace of device %d holds %lld bytes, %lld needed "
+                           "(call forge_gemm_sm100_set_workspace)", dev, dev >= 0 && dev < 64 ? g_workspace[dev].bytes : 0LL, need);
+    static const int dbg = getenv("FORGE_SK_DEBUG") ? atoi(getenv("FORGE_SK_DEBUG")) : 0;
+    StreamKWork wk{dbg, reinterpret_cast<float*>(static_cast<char*>(g_workspace[dev].ptr) + kFlagBytes),
+                   static_cast<int*>(g_workspace[dev].ptr), per_cta, max_parts};
+    const int stages = per_cta < C::kStages ? per_cta : C::kStages;
+    return forge::check_launch("gemm_sm100 (few rows, stream-K)",
+                               forge::launch(gemm_sm100_streamk_kernel<NT>, dim3(grid), dim3(kThreads),
+                                             C::smem_bytes(stages), stream, 1, tw, tx, p, wk, stages));
+}
+
 }  // namespace
+
+// Hands the library a zero-initialised device buffer (>= 256 KiB of flags + room for partial sums) that the
+// stream-K kernel of the current device may use from now on.  The buffer must outlive all later calls.
+extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return forge::fail(FORGE_ERR_ARG, "set_workspace: no current device");
+    if (bytes < kFlagBytes + 1024 * 1024) return forge::fail(FORGE_ERR_ARG, "set_workspace: %lld bytes is too small", bytes);
+    g_workspace[dev].ptr = ptr;
+    g_workspace[dev].bytes = bytes;
+    return FORGE_OK;
+}
 
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
 // tile_n: 0 = choose; 16, 32, 64, 128, 256 = token-major tiles of that width; -1, -2, -4, -8 (M <= 64 only) =
-// the few-rows kernel with K cut across a cluster of that many CTAs.  status: device int, bit 1 raised if a wait ran out.
+// the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
+// that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
                                 int K, int epilogue, int tile_n, void* reserved, cudaStream_t stream) {
     (void)reserved;
@@ -549,6 +840,24 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         // few rows: weights are the MMA's M operand, K is cut across a cluster (tile_n < 0: -tile_n CTAs)
         const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
         const int tiles_n = (N + BM - 1) / BM, num_kb = (K + BK - 1) / BK;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const bool have_ws = dev >= 0 && dev < 64 && g_workspace[dev].ptr != nullptr;
+        // worth it when a tile is shared by few CTAs and the partial sums (which cross global memory) are small:
+        // units per CTA >= half a tile, at most 32 tokens
+        const int sk_per_cta = (tiles_n * num_kb + g_num_sms - 1) / g_num_sms;
+        if ((tile_n == 0 && have_ws && nt <= 32 && tiles_n * num_kb >= g_num_sms && 2 * sk_per_cta >= num_kb) || tile_n == -100) {
+            // deal the (row tile, k-block) units out evenly over the SMs
+            CUtensorMap tw, tx;
+            if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+            if (!bf16_tile_map(A, M, K, nt, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+            GemmParams p{C, bias, M, N, K, epilogue, status};
+            switch (nt) {
+                case 16: return launch_streamk<16>(tw, tx, p, stream);
+                case 32: return launch_streamk<32>(tw, tx, p, stream);
+                default: return launch_streamk<64>(tw, tx, p, stream);
+            }
+        }
         int ksplit = 1;
         if (tile_n < 0) {
             ksplit = -tile_n;
@@ -558,7 +867,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             // as many CTAs as fit the GPU at once; a cluster of 8 only when each CTA then still has a short
             // pipeline of its own (measured: with K = 5632, 4 CTAs of 22 k-blocks beat 8 of 11)
             while (ksplit < 8 && tiles_n * ksplit * 2 <= g_num_sms + g_num_sms / 8 && num_kb / (ksplit * 2) >= 2 &&
-                   (ksplit < 4 || num_kb <= 32))
+                   (ksplit < 4 || (num_kb <= 32 && nt == 16)))
                 ksplit *= 2;
         }
         CUtensorMap tw, tx;

@@ -43,6 +43,7 @@ _SIGNATURES = {
     },
     "gemm_sm100": {
         "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "forge_gemm_sm100_set_workspace": [_P, ctypes.c_longlong],
     },
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
@@ -375,6 +376,7 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
         raise KernelError(f"gemm_sm100: output has shape {tuple(out.shape)}, expected {want_shape}")
     if status is None:
         status = _gemm_status(x.device)
+    _gemm_workspace(lib, x.device)
     _check(lib, lib.forge_gemm_sm100(_need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2),
                                      _opt(bias, "bias", torch.float32), _need(out, "out", want_dtype),
                                      _need(status, "status", torch.int32), M, N, K, code, int(tile_n), None, _stream()),
@@ -383,6 +385,22 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
 
 
 _status_words = {}
+_workspaces = {}
+GEMM_WORKSPACE_BYTES = 48 * 1024 * 1024
+
+
+def _gemm_workspace(lib, device):
+    """One zeroed buffer per device for the few-rows GEMM's partial sums and flags, given to the library once."""
+    key = str(device)
+    if key not in _workspaces:
+        ws = torch.zeros(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            rc = lib.forge_gemm_sm100_set_workspace(ws.data_ptr(), GEMM_WORKSPACE_BYTES)
+        if rc != 0:
+            raise KernelError(f"gemm_sm100: {lib.forge_last_error().decode(errors='replace')}")
+        _workspaces[key] = ws
+    return _workspaces[key]
+
 
 
 def _gemm_status(device):

@@ -66,10 +66,11 @@ def test_many_tiles_per_cta_and_both_accumulators():
 
 @pytest.mark.parametrize("M", [1, 8, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
-@pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8])
+@pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8, -100])
 def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
-    """The decode-shaped kernel (weights as the MMA's M operand, K cut over a cluster, partial sums added
-    through distributed shared memory) for every cluster size and every epilogue."""
+    """The decode-shaped kernels (weights as the MMA's M operand) for every epilogue: K cut over a cluster of
+    1/2/4/8 CTAs with partial sums added through distributed shared memory, and (-100) units of work dealt
+    out evenly to persistent CTAs with partial sums added through a workspace."""
     k = _k()
     a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
     bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
