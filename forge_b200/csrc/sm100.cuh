@@ -13,7 +13,10 @@
 
 namespace sm100 {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+#ifndef FORGE_WAIT_LIMIT_NS
+#define FORGE_WAIT_LIMIT_NS 2000000000ull   // 2 s
+#endif
+constexpr unsigned long long kWaitLimitNs = FORGE_WAIT_LIMIT_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -60,21 +63,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Waits for the phase of `parity` to complete.  Returns false (after raising the flags) if another part
 // of the CTA has aborted or the time limit passes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = 0;
-    for (uint32_t spins = 1;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 0x3ff) == 0) {
-            if (*abort) return false;
-            const unsigned long long now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
-                *abort = 1;
-                if (status) atomicOr(status, 2);
-                return false;
-            }
+// `where` (0..26) tags the wait: on expiry bit 4 + where of the status word is raised too, which tells
+// a post-mortem which barrier was never completed.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, int where = 0) {
+    // fast path: a few potentially-suspending tries (the hardware wakes the thread when the phase completes)
+    if (mbar_try_wait(bar, parity) || mbar_try_wait(bar, parity)) return true;
+    // slow path: non-blocking tests, so that the clock is looked at after every one of them (try_wait may
+    // suspend the thread for a system-dependent time that is much longer than the limit)
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (*abort) return false;
+        if (global_ns() - t0 > kWaitLimitNs) {
+            *abort = 1;
+            if (status) atomicOr(status, 2 | (1 << (4 + where)));
+            return false;
         }
+        __nanosleep(32);
     }
 }
 
@@ -91,6 +107,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+
+// 3D tile load: c0 innermost (elements), then c1, c2.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Makes shared-memory writes of this thread (generic proxy) visible to the async proxy (TMA, tcgen05.mma).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------- TMEM
 // Whole-warp operations (.sync.aligned).  ncols: power of two, 32..512.
@@ -127,11 +153,28 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                      // layout type, bits [61,64)
     return d;
 }
+// Descriptor of an MN-major bf16 tile: rows are K indices, each row holds 64 contiguous MN elements (128
+// bytes), written by TMA with 128-byte swizzle.  8-row groups along K are 1024 bytes apart (stride byte
+// offset); the leading byte offset is the distance between 64-element blocks along MN (`mn_block_bytes`,
+// unused when the operand is 64 wide).  Stepping along K by 16 rows adds 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>((mn_block_bytes >> 4) & 0x3fff) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
 // Instruction descriptor of kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 (bits [7,10) and [10,13) = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 at bits [17,23), M >> 4 at bits [24,29).
 __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
+}
+// As above with B MN-major (bit 16).
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_f32_bmn(int m, int n) {
+    return umma_idesc_bf16_f32(m, n) | (1u << 16);
 }
 // D[tmem] (+)= A[smem] . B[smem]^T ; issued by one thread.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -171,6 +214,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 }  // namespace sm100
 
@@ -222,6 +277,35 @@ inline bool bf16_tile_map(const void* ptr, int rows, int cols, int box_rows, CUt
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed"; return false; }
     if (cache.size() > 4096) cache.clear();   // activation buffers come and go; weights re-enter on next use
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+// Map of q [tokens, heads, 64 * blocks] bf16 read in boxes of [box_tokens, box_heads, 64]: a tile of query
+// rows ordered (token, head of one kv group), 128 bytes each, 128-byte swizzle.
+inline bool bf16_q_map(const void* ptr, int tokens, int heads, int head_dim, int box_tokens, int box_heads,
+                       CUtensorMap* out, const char** err) {
+    using Key = std::tuple<const void*, int, int, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key{ptr, tokens, heads, head_dim, box_tokens, box_heads};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    auto fn = encode_fn();
+    if (!fn) { *err = "cuTensorMapEncodeTiled is not available from the driver"; return false; }
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || head_dim % 64 != 0) { *err = "q map needs a 16-byte aligned base and head_dim % 64 == 0"; return false; }
+    CUtensorMap m;
+    const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)heads, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)heads * head_dim * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled (q) failed"; return false; }
+    if (cache.size() > 1024) cache.clear();
     cache.emplace(key, m);
     *out = m;
     return true;

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
     },
+    "attention_sm100": {
+        "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
+    },
 }
 
 _libs = {}
@@ -274,11 +277,16 @@ def _sm_count(device):
     return _NUM_SMS[key]
 
 
-def attention_plan(batch, group, device):
+TC_ROWS = 128       # query rows per tile of the tcgen05 attention kernel
+TC_MIN_ROWS = 64    # requests with at least this many rows in the step go to it
+
+
+def attention_plan(batch, group, device, only_below=None):
     """How the step's query rows are cut into tiles for the tensor-core attention kernel, and into how
     many slices each tile's keys are cut.  Computed once per step and group size (all layers share it).
-    A request with q_len tokens has q_len * group rows; tiles never span requests."""
-    key = ("mma", group)
+    A request with q_len tokens has q_len * group rows; tiles never span requests.  ``only_below``: plan
+    only the requests with fewer rows than that (the others are served by the tcgen05 kernel)."""
+    key = ("mma", group, only_below)
     plan = batch.attention_plan.get(key)
     if plan is not None:
         return plan
@@ -286,6 +294,8 @@ def attention_plan(batch, group, device):
     qs = batch.host_q_start
     for s in range(batch.num_requests):
         rows = (qs[s + 1] - qs[s]) * group
+        if only_below is not None and rows >= only_below:
+            continue
         for r0 in range(0, rows, BQ_ROWS):
             tile_req.append(s)
             tile_row0.append(r0)
@@ -300,11 +310,61 @@ def attention_plan(batch, group, device):
     return plan
 
 
+def attention_plan_tc(batch, group, device):
+    """Tiles of 128 rows for the requests that bring at least TC_MIN_ROWS rows, heaviest (most keys) first."""
+    key = ("tc", group)
+    plan = batch.attention_plan.get(key)
+    if plan is not None:
+        return plan
+    tiles, qs = [], batch.host_q_start
+    for s in range(batch.num_requests):
+        rows = (qs[s + 1] - qs[s]) * group
+        if rows < TC_MIN_ROWS:
+            continue
+        for r0 in range(0, rows, TC_ROWS):
+            tiles.append((batch.host_context_before[s] + min(rows, r0 + TC_ROWS) // group, s, r0))
+    tiles.sort(reverse=True)
+    plan = {"tile_req": torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=device),
+            "tile_row0": torch.tensor([t[2] for t in tiles], dtype=torch.int32, device=device), "num_tiles": len(tiles)}
+    batch.attention_plan[key] = plan
+    return plan
+
+
+def attention_sm100_supports(head_dim, group, page_size):
+    return _TENSOR_CORE_ATTENTION and head_dim == 64 and TC_ROWS % group == 0 and page_size in (8, 16, 32, 64)
+
+
+def paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=0,
+                          scale=None, out=None):
+    """tcgen05/TMEM attention for the requests of the step that bring many rows (prompt portions).  Writes
+    only those requests' rows of ``out``.  Returns (out, number of tiles run)."""
+    lib = library("attention_sm100")
+    plan = attention_plan_tc(batch, n_heads // n_kv_heads, q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    if plan["num_tiles"] == 0:
+        return out, 0
+    scale = head_dim ** -0.5 if scale is None else scale
+    _check(lib, lib.forge_paged_attention_sm100(
+        _need(q, "q", torch.bfloat16, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
+        _need(group_batch.block_table, "block_table", torch.int32, 2), _need(plan["tile_req"], "tile_req"),
+        _need(plan["tile_row0"], "tile_row0"), _need(batch.q_start, "q_start", torch.int32),
+        _need(batch.context_before, "context_before", torch.int32), _need(_gemm_status(q.device), "status", torch.int32),
+        plan["num_tiles"], q.shape[0], kv_cache.shape[0], n_heads, n_kv_heads, head_dim, page_size,
+        group_batch.block_table.shape[1], int(window or 0), float(scale), _stream()), "paged_attention_sm100")
+    return out, plan["num_tiles"]
+
+
 def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=0,
-                        scale=None, out=None, num_splits=None):
-    """bf16 tensor-core attention over the paged cache for every token of the step."""
+                        scale=None, out=None, num_splits=None, only_below=None):
+    """bf16 tensor-core attention over the paged cache for every token of the step (or, with ``only_below``,
+    for the requests that bring fewer rows than that)."""
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
-    plan = attention_plan(batch, n_heads // n_kv_heads, q.device)
+    plan = attention_plan(batch, n_heads // n_kv_heads, q.device, only_below)
+    if out is None:
+        out = torch.empty_like(q)
+    if plan["num_tiles"] == 0:
+        return out
     if num_splits is None:
         # decode-like steps (every tile is one warp with small buffers, ten of which fit an SM): slice the
         # keys until about eight CTAs per SM exist, so that enough loads are in flight to hide their latency
@@ -340,6 +400,13 @@ def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_d
                     scale=None):
     """Attention of every token of the step over its request's pages; picks the kernel by dtype and shape."""
     if q.dtype == torch.bfloat16 and attention_mma_supports(head_dim, n_heads // n_kv_heads, page_size):
+        group = n_heads // n_kv_heads
+        if attention_sm100_supports(head_dim, group, page_size) and not getattr(batch, "decode_only", False):
+            out, n = paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size,
+                                           window=window or 0, scale=scale)
+            if n:       # the requests with few rows (decode tokens, short portions) use the mma.sync kernel
+                return paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size,
+                                           window=window or 0, scale=scale, out=out, only_below=TC_MIN_ROWS)
         return paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size,
                                    window=window or 0, scale=scale)
     return paged_attention_simt(q, kv_cache, group_batch.block_table, batch.tok_req, batch.positions, n_heads,

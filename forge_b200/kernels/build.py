@@ -24,8 +24,10 @@ LIBRARIES = {
              "attention_simt.cu", "sampling.cu"],
     # bf16 tcgen05 + TMA GEMM with fused epilogues
     "gemm_sm100": ["gemm_sm100.cu"],
-    # bf16 tensor-core paged attention for prefill portions and decode
+    # bf16 tensor-core paged attention (mma.sync) for any head size, prompt portions and decode
     "attention_mma": ["attention_mma.cu"],
+    # bf16 tcgen05/TMEM paged attention for prompt portions, head size 64
+    "attention_sm100": ["attention_sm100.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -8,7 +8,7 @@ from types import SimpleNamespace
 
 import torch
 
-from . import gemm_sm100, paged_attention_mma
+from . import gemm_sm100, paged_attention, paged_attention_mma
 
 DEV = "cuda:0"
 H, I, NH, NKV, HD, PS = 2048, 5632, 32, 4, 64, 16
@@ -52,6 +52,9 @@ def case(name):
         q, kv, g, b = _attention_inputs([(1023, 1)] * 64)
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 64 * 1024 * 2 * NKV * HD * 2, 4 * 64 * 1024 * NH * HD
     if name == "attention_prefill":          # one request, 2048 tokens, causal: 17.2 GFLOP
+        q, kv, g, b = _attention_inputs([(0, 2048)])
+        return (lambda: paged_attention(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
+    if name == "attention_prefill_mma":      # the same through the mma.sync kernel, for comparison
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
     raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_prefill_gateup "

@@ -1,0 +1,62 @@
+"""The tcgen05/TMEM attention kernel for prompt portions (head size 64) against a plain fp64 restatement,
+alone and through the dispatcher that sends requests with few rows to the mma.sync kernel."""
+import pytest
+import torch
+
+from plain import kernels_ref as R
+from test_attention_mma_gpu import make_case
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(32, 4, 64, 16), (8, 8, 64, 16), (16, 1, 64, 8), (4, 2, 64, 64), (6, 3, 64, 32)]
+PORTIONS = [(0, 100), (130, 17), (0, 300), (63, 65), (500, 16), (64, 64)]
+
+
+def _rows_of_big(reqs, group, min_rows):
+    rows, t = [], 0
+    for c, q in reqs:
+        if q * group >= min_rows:
+            rows += list(range(t, t + q))
+        t += q
+    return torch.tensor(rows, dtype=torch.long)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", SHAPES)
+@pytest.mark.parametrize("window", [0, 70])
+def test_prompt_portions(nh, nkv, hd, ps, window):
+    from forge_b200 import kernels as k
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, PORTIONS)
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
+    out = torch.full_like(q, float("nan"))
+    got, n = k.paged_attention_sm100(q, cache, group, batch, nh, nkv, hd, ps, window=window, out=out)
+    k.check_kernel_status()
+    big = _rows_of_big(PORTIONS, nh // nkv, k.TC_MIN_ROWS).to(q.device)
+    assert n > 0 and len(big) > 0
+    err = (got.float()[big] - ref[big]).abs().amax(dim=1)
+    bad = torch.nonzero(~(err <= 1e-2 * ref.abs().max()))
+    assert len(bad) == 0, f"first wrong token {int(big[bad[0]])} (request {int(tok_req[big[bad[0]]])}, position {int(positions[big[bad[0]]])})"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", SHAPES[:3])
+def test_dispatcher_covers_every_token(nh, nkv, hd, ps):
+    """Portions of prompts beside decode tokens: big requests by tcgen05, small ones by mma.sync, no row missed."""
+    from forge_b200 import kernels as k
+    reqs = PORTIONS + [(700, 1), (3, 1), (64, 2)]
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=5)
+    batch.tok_req, batch.positions = tok_req, positions
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps)
+    got = k.paged_attention(q, cache, group, batch, nh, nkv, hd, ps).float()
+    k.check_kernel_status()
+    assert not torch.isnan(got).any()
+    assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
+def test_long_causal_prompt_heaviest_tiles_first():
+    from forge_b200 import kernels as k
+    nh, nkv, hd, ps = 32, 4, 64, 16
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, [(0, 1100)], seed=7)
+    ref = R.paged_attention_ref(q[-40:], cache, group.block_table, tok_req[-40:], positions[-40:], nh, nkv, hd, ps)
+    got, n = k.paged_attention_sm100(q, cache, group, batch, nh, nkv, hd, ps)
+    k.check_kernel_status()
+    assert n == -(-1100 * 8 // 128)
+    assert (got.float()[-40:] - ref).abs().max() <= 1e-2 * ref.abs().max()
