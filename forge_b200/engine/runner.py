@@ -140,6 +140,8 @@ class ModelRunner:
 
     def check_status(self):
         """Reads the device error word (synchronises); raises if a kernel flagged a problem."""
+        from .. import kernels
+        kernels.check_kernel_status(self.device)          # tensor-core kernels: a bounded wait that ran out
         s = int(self.status.item())
         if s:
             self.status.zero_()

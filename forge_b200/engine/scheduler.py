@@ -244,6 +244,8 @@ class RequestScheduler:
                 self._finish(r, RequestStatus.Failed, f"error:{type(e).__name__}")
             raise
         self.num_steps += 1
+        if self.num_steps % 256 == 0 and hasattr(self.runner, "check_status"):
+            self.runner.check_status()                    # device error words, read now and then
         for r, start, n, wants in plan:
             r.current_pos = start + n
         if rows:
@@ -263,6 +265,8 @@ class RequestScheduler:
         while self.has_pending():
             if not self.step():
                 break
+        if hasattr(self.runner, "check_status"):
+            self.runner.check_status()
         return self.get_finished()
 
     # ------------------------------------------------------------------------------- internals

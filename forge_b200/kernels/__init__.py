@@ -472,15 +472,21 @@ def _gemm_workspace(lib, device):
 
 def _gemm_status(device):
     """One int32 per device on which tensor-core kernels raise bit 1 when a bounded wait runs out."""
-    key = str(device)
+    dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = str(dev)
     if key not in _status_words:
-        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=dev)
     return _status_words[key]
 
 
 def check_kernel_status(device="cuda:0"):
     """Synchronises and raises if a tensor-core kernel gave up on a wait since the last check."""
-    w = _status_words.get(str(torch.device(device)))
+    dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    w = _status_words.get(str(dev))
     if w is not None:
         v = int(w.item())
         if v:
