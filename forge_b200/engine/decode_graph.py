@@ -14,7 +14,9 @@ from .batch import GroupBatch, StepBatch
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests):
+    def __init__(self, runner, num_requests, max_context=None):
+        """max_context: the longest context (tokens cached + 1) any replay of this graph will see; the attention
+        kernel's slicing of the keys is fixed at capture and sized for it."""
         S, dev = int(num_requests), runner.device
         self.runner, self.S = runner, S
         self.max_pages = mp = runner.max_pages_per_request
@@ -42,12 +44,12 @@ class DecodeGraph:
             logits_rows=ar[:S].contiguous(), groups=groups, status=runner.status,
             host_q_start=list(range(S + 1)), host_context_before=[0] * S, host_slots=[0] * S)
         self.batch.decode_only = True
-        self.batch.max_context = runner.plan.max_positions     # the graph must fit any context length
+        self.batch.max_context = int(max_context or runner.plan.max_positions)
         self.graph = None
         self.logits = self.tokens = None
         self.kernels_per_replay = 0
 
-    def _fill(self, hs, tokens_on_device=False):
+    def _fill(self, hs, tokens_from=None):
         i = self.ring_pos
         self.ring_pos = (i + 1) % len(self.ring)
         if self.ring_events[i] is not None:
@@ -64,8 +66,9 @@ class DecodeGraph:
             for s, t in enumerate(hs.tables[g]):
                 tab[s, :len(t)] = t
             off += S + S * mp
-        if tokens_on_device:     # the token ids are already there (the previous step's argmax)
+        if tokens_from is not None:     # the token ids are on the device already (the previous step's argmax)
             self.dev[S:].copy_(self.ring[i][S:], non_blocking=True)
+            self.dev[0:S].copy_(tokens_from, non_blocking=True)
         else:
             self.dev.copy_(self.ring[i], non_blocking=True)
         ev = self.ring_events[i] or torch.cuda.Event()
@@ -76,11 +79,12 @@ class DecodeGraph:
         logits = self.runner.model.forward(self.batch, self.runner.storage.layers)
         return logits, kernels.argmax(logits)
 
-    def run(self, hs, tokens_on_device=False):
+    def run(self, hs, tokens_from=None):
         """hs: HostStep of S single-token entries.  Returns (logits [S,V], greedy tokens int32 [S]), both
-        device tensors that the next replay overwrites.  ``tokens_on_device``: ignore hs.token_ids and use
-        the greedy tokens of the previous replay, which never left the device."""
-        self._fill(hs, tokens_on_device and self.graph is not None)
+        device tensors that the next replay overwrites.  ``tokens_from``: an int32 [S] device tensor to take
+        the token ids from instead of hs.token_ids (the previous step's greedy tokens, which never left the
+        device)."""
+        self._fill(hs, tokens_from)
         if self.graph is None:
             # first use: once eagerly (sets kernel attributes, warms allocator), then capture
             n0 = kernels.launch_count()
@@ -102,5 +106,4 @@ class DecodeGraph:
             self.graph = g
         self.graph.replay()
         kernels.count_launches(self.kernels_per_replay)
-        self.dev[0:self.S].copy_(self.tokens, non_blocking=True)     # feeds a following device-side step
         return self.logits, self.tokens

@@ -76,6 +76,7 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.cuda_graphs = bool(cuda_graphs)
         self._decode_graphs = {}
+        self._last_greedy = None
 
     # ---------------------------------------------------------------------------------- requests
     def admit(self, req_id):
@@ -128,12 +129,23 @@ class ModelRunner:
         entries' token ids are placeholders; the step consumes the previous decode step's greedy tokens
         straight from device memory."""
         S = len(entries)
-        g = self._decode_graphs.get(S)
+        # graphs are kept per (batch size, context bucket): the key slicing of the decode attention is part of
+        # the graph, and slicing for 32k tokens when the longest request holds 500 wastes CTAs and merge work
+        longest = max(self.manager.num_tokens(e.req_id) for e in entries) + 1
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        bucket = min(bucket, self.plan.max_positions)
+        g = self._decode_graphs.get((S, bucket))
         if g is None:
-            g = self._decode_graphs[S] = DecodeGraph(self, S)
+            g = self._decode_graphs[(S, bucket)] = DecodeGraph(self, S, max_context=bucket)
         hs = layout_step(entries, self.manager)
         self.storage.zero_state_slots(self.manager.take_fresh_slots())
-        out = g.run(hs, tokens_on_device=tokens_on_device)
+        prev = self._last_greedy if tokens_on_device else None
+        if prev is not None and prev.numel() != S:
+            raise StepError("tokens_on_device needs a previous decode step of the same batch size")
+        out = g.run(hs, tokens_from=prev)
+        self._last_greedy = out[1]
         for e in entries:
             self.manager.release_out_of_window(e.req_id)
         return out
