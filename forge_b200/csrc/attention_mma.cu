@@ -355,6 +355,229 @@ attention_merge_kernel(const AttnParams p, int num_tiles) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Decode step in one kernel: position encoding, cache write and attention of ONE new token per request.
+//
+// A CTA serves one (request, kv head).  It rotates the G query heads and the key head of the new token
+// (fp32 angles, as rope_cache.cu does), writes the key and the value into the request's page, and attends
+// over the request's keys: the key range is dealt to the CTA's warps in tiles of 32 keys (warp w takes
+// tiles w, w + W, ...), each warp keeps an online softmax of its own over its tiles, and the warps' partial
+// results are merged through shared memory in warp order.  One launch replaces three (rope + cache write,
+// sliced attention, merge) and no partial result leaves the SM.
+struct DecodeParams {
+    const float* qkv;             // [S, (NH + 2 NKV) * HD] fp32: the new token's projections, one row per request
+    __nv_bfloat16* kv;            // [pages, 2, NKV, page_size, HD]
+    __nv_bfloat16* out;           // [S, NH*HD]
+    const int32_t* block_table;   // [S, max_pages]
+    const int32_t* positions;     // [S] position of the new token = tokens already cached
+    const int32_t* slot_mapping;  // [S] page * page_size + offset of the new token
+    int NH, NKV, page_size, max_pages, window, rotary;
+    float theta, scale_log2;
+};
+
+constexpr int DKV = 32;           // keys per tile
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+decode_attention_fused_kernel(const DecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][LD]  (G heads, zero-padded)
+    __nv_bfloat16* kvs = qs + 16 * LD;                                   // [NWARPS][2 buffers][K | V][DKV][LD]
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int s = blockIdx.x, kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.NH / p.NKV;
+    const int pos = p.positions[s];
+    const int half = HD / 2;
+    const float* row = p.qkv + (size_t)s * (p.NH + 2 * p.NKV) * HD;
+    const int slot = p.slot_mapping[s];
+    __nv_bfloat16* page_base = p.kv + ((size_t)(slot / p.page_size) * 2 * p.NKV + kvh) * p.page_size * HD + (size_t)(slot % p.page_size) * HD;
+
+    // 1. rotate q (G heads) and k (one head), copy v; q to shared memory, k and v to the cache
+    for (int i = threadIdx.x; i < 16 * CPR; i += blockDim.x)             // clear the padding rows of Q
+        if (i / CPR >= G) *reinterpret_cast<uint4*>(qs + (i / CPR) * LD + (i % CPR) * 8) = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < (G + 2) * half; i += blockDim.x) {
+        const int h = i / half, d = i % half;                            // h < G: q head; G: k; G + 1: v
+        const int src_head = h < G ? kvh * G + h : (h == G ? p.NH + kvh : p.NH + p.NKV + kvh);
+        float x0 = row[src_head * HD + d], x1 = row[src_head * HD + d + half];
+        if (p.rotary && h <= G) {
+            const float freq = 1.0f / powf(p.theta, (2.0f * (float)d) / (float)HD);
+            float sn, cs;
+            sincosf((float)pos * freq, &sn, &cs);
+            const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+            x0 = y0;
+            x1 = y1;
+        }
+        if (h < G) {
+            qs[h * LD + d] = __float2bfloat16_rn(x0);
+            qs[h * LD + d + half] = __float2bfloat16_rn(x1);
+        } else {
+            __nv_bfloat16* dst = page_base + (h == G ? 0 : (size_t)p.NKV * p.page_size * HD);
+            dst[d] = __float2bfloat16_rn(x0);
+            dst[d + half] = __float2bfloat16_rn(x1);
+        }
+    }
+    __threadfence_block();        // the new key and value are read back below by whichever warp gets their tile
+    __syncthreads();
+
+    // 2. every warp walks its share of the key tiles
+    const int32_t* table = p.block_table + (size_t)s * p.max_pages;
+    const int kv_hi = pos + 1;
+    const int kv_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int t_begin = kv_lo / DKV, t_end = (kv_hi + DKV - 1) / DKV;
+    __nv_bfloat16* my_k = kvs + (size_t)warp * 4 * DKV * LD;             // [buffer][K | V]
+    const bool valid_a = (lane >> 2) < G, valid_b = (lane >> 2) + 8 < G;
+
+    float o_acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    auto load_tile = [&](int buf, int t) {
+        __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
+        const int tk = t * DKV + lane;                                   // lane = row of the tile
+        int ridx = -1;
+        if (tk >= kv_lo && tk < kv_hi) ridx = (table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
+        const int v_rows = p.NKV * p.page_size;
+#pragma unroll 4
+        for (int c = lane; c < DKV * CPR; c += 32) {
+            const int r_row = c / CPR, ch = c % CPR;
+            const int r = __shfl_sync(0xffffffffu, ridx, r_row);
+            __nv_bfloat16* dk = kd + r_row * LD + ch * 8;
+            __nv_bfloat16* dv = dk + DKV * LD;
+            if (r >= 0) {
+                const __nv_bfloat16* src = p.kv + (size_t)r * HD + ch * 8;
+                cp_async16(dk, src);
+                cp_async16(dv, src + (size_t)v_rows * HD);
+            } else {
+                *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    int t = t_begin + warp, n_done = 0;
+    if (t < t_end) { load_tile(0, t); cp_async_commit(); }
+    for (; t < t_end; t += NWARPS, ++n_done) {
+        const int buf = n_done & 1;
+        if (t + NWARPS < t_end) {
+            load_tile(buf ^ 1, t + NWARPS);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const __nv_bfloat16* kb = my_k + (size_t)buf * 2 * DKV * LD;
+        const __nv_bfloat16* vb = kb + DKV * LD;
+        float sc[DKV / 8][4];
+#pragma unroll
+        for (int i = 0; i < DKV / 8; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t a[4];
+            ldmatrix_x4(a, qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < DKV / 16; ++nb) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kb + (nb * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(sc[2 * nb], a, b[0], b[1]);
+                mma_bf16(sc[2 * nb + 1], a, b[2], b[3]);
+            }
+        }
+        float mx_a = m_a, mx_b = m_b;
+        const bool unmasked = t * DKV + DKV - 1 <= pos && (p.window <= 0 || t * DKV > pos - p.window);
+        const int j0 = t * DKV + 2 * (lane & 3);
+#pragma unroll
+        for (int i = 0; i < DKV / 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j0 + i * 8 + e;
+                const bool vis = unmasked || (j <= pos && (p.window <= 0 || j > pos - p.window));
+                sc[i][e] = (vis && valid_a) ? sc[i][e] * p.scale_log2 : -INFINITY;
+                sc[i][2 + e] = (vis && valid_b) ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
+                mx_a = fmaxf(mx_a, sc[i][e]);
+                mx_b = fmaxf(mx_b, sc[i][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float ref_a = mx_a == -INFINITY ? 0.f : mx_a, ref_b = mx_b == -INFINITY ? 0.f : mx_b;
+        const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+        m_a = mx_a;
+        m_b = mx_b;
+        float sum_a = 0.f, sum_b = 0.f;
+        uint32_t pfrag[DKV / 16][4];
+#pragma unroll
+        for (int i = 0; i < DKV / 8; ++i) {
+            const float p0 = exp2f(sc[i][0] - ref_a), p1 = exp2f(sc[i][1] - ref_a);
+            const float p2 = exp2f(sc[i][2] - ref_b), p3 = exp2f(sc[i][3] - ref_b);
+            sum_a += p0 + p1;
+            sum_b += p2 + p3;
+            pfrag[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
+            pfrag[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_a = l_a * alpha_a + sum_a;
+        l_b = l_b * alpha_b + sum_b;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o_acc[i][0] *= alpha_a; o_acc[i][1] *= alpha_a;
+            o_acc[i][2] *= alpha_b; o_acc[i][3] *= alpha_b;
+        }
+#pragma unroll
+        for (int kk = 0; kk < DKV / 16; ++kk) {
+#pragma unroll
+            for (int db = 0; db < HD / 16; ++db) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vb + (kk * 16 + (lane & 15)) * LD + db * 16 + (lane >> 4) * 8);
+                mma_bf16(o_acc[2 * db], pfrag[kk], b[0], b[1]);
+                mma_bf16(o_acc[2 * db + 1], pfrag[kk], b[2], b[3]);
+            }
+        }
+        __syncwarp();            // the buffer just read is the target of the load after next
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    // 3. merge the warps' partial results in shared memory (the tile buffers are free now), in warp order
+    __syncthreads();
+    float* mo = reinterpret_cast<float*>(kvs);                           // [NWARPS][16][HD]
+    float* ml = mo + NWARPS * 16 * HD;                                   // [NWARPS][16][2]
+    {
+        const int ra = lane >> 2, rb = ra + 8, d0 = 2 * (lane & 3);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + ra) * HD + i * 8 + d0) = make_float2(o_acc[i][0], o_acc[i][1]);
+            *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + rb) * HD + i * 8 + d0) = make_float2(o_acc[i][2], o_acc[i][3]);
+        }
+        if ((lane & 3) == 0) {
+            ml[(warp * 16 + ra) * 2] = m_a; ml[(warp * 16 + ra) * 2 + 1] = l_a;
+            ml[(warp * 16 + rb) * 2] = m_b; ml[(warp * 16 + rb) * 2 + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int r = i / HD, d = i % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, ml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = ml[(w * 16 + r) * 2];
+            const float wt = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += wt * ml[(w * 16 + r) * 2 + 1];
+            acc += wt * mo[((size_t)w * 16 + r) * HD + d];
+        }
+        p.out[(size_t)s * p.NH * HD + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+}
+
 }  // namespace
 
 // Scratch floats needed for num_splits > 1, with R = 16 if max_rows <= 16 else 64:
@@ -452,6 +675,42 @@ extern "C" int forge_paged_attention_mma_static(const void* q, const void* kv, v
     return forge_paged_attention_mma(q, kv, out, scratch, scratch + rows * HD, block_table, tile_req, tile_row0, q_start,
                                      ctx_before, num_tiles, max_rows, NH, NKV, head_dim, page_size, max_pages, window,
                                      num_splits, scale, stream);
+}
+
+// One new token per request: rotary encoding (rotary != 0), cache write and attention in one launch.
+// qkv fp32 [S, (NH + 2 NKV) * HD]; positions / slot_mapping int32 [S]; out bf16 [S, NH*HD].  NH / NKV <= 16.
+extern "C" int forge_decode_attention_fused(const float* qkv, void* kv, void* out, const int32_t* block_table,
+                                            const int32_t* positions, const int32_t* slot_mapping, int S, int NH, int NKV,
+                                            int head_dim, int page_size, int max_pages, int window, int rotary,
+                                            float theta, float scale, cudaStream_t stream) {
+    if (head_dim != HD) return forge::fail(FORGE_ERR_UNSUPPORTED, "this attention library was built for head_dim %d, got %d", HD, head_dim);
+    if (S < 0 || NH <= 0 || NKV <= 0 || NH % NKV != 0 || page_size <= 0 || max_pages <= 0 || NKV > 65535)
+        return forge::fail(FORGE_ERR_ARG, "decode_attention_fused: bad sizes S=%d NH=%d NKV=%d page=%d", S, NH, NKV, page_size);
+    if (NH / NKV > 16) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_fused: %d query heads per kv head (at most 16)", NH / NKV);
+    if (S == 0) return FORGE_OK;
+    DecodeParams p{qkv, (__nv_bfloat16*)kv, (__nv_bfloat16*)out, block_table, positions, slot_mapping, NH, NKV, page_size,
+                   max_pages, window, rotary, theta, scale * 1.4426950408889634f};
+    // eight warps while the CTAs are few (short latency per request), four when there are CTAs enough to fill the SMs
+    int sms = 148, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    constexpr int kLimit = 227 * 1024;
+    constexpr int need4 = (16 + 4 * 4 * DKV) * LD * 2, need8 = (16 + 8 * 4 * DKV) * LD * 2;   // tiles; the merge area is smaller
+    if (need4 > kLimit) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_fused: head_dim %d needs %d bytes of shared memory", HD, need4);
+    const int warps = ((long)S * NKV <= sms && need8 <= kLimit) ? 8 : 4;
+    const int smem = warps == 8 ? need8 : need4;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, need4);
+        if (e == cudaSuccess && need8 <= kLimit)
+            e = cudaFuncSetAttribute(decode_attention_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, need8);
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "decode_attention_fused: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaError_t le = warps == 8
+        ? forge::launch(decode_attention_fused_kernel<8>, dim3(S, NKV), dim3(256), smem, stream, 1, p)
+        : forge::launch(decode_attention_fused_kernel<4>, dim3(S, NKV), dim3(128), smem, stream, 1, p);
+    return forge::check_launch("decode_attention_fused", le);
 }
 
 extern "C" int forge_attention_head_dim() { return HD; }

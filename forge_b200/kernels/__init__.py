@@ -47,6 +47,7 @@ _SIGNATURES = {
     },
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
+        "forge_decode_attention_fused": [_P] * 6 + [_I] * 8 + [_F, _F, _P],
     },
     "attention_sm100": {
         "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
@@ -393,6 +394,32 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
         int(window or 0), int(num_splits), float(scale), _stream()), "paged_attention_mma")
     if num_splits > 1:
         count_launches(1)      # the merge kernel
+    return out
+
+
+def decode_attention_fused_supports(dtype, head_dim, group, num_requests, n_kv_heads, max_context):
+    """One launch for rotary encoding + cache write + attention of a decode step: bfloat16, head sizes in steps
+    of 16 up to 128, at most 16 query heads per kv head.  With very few requests and very long contexts the
+    sliced kernel (keys spread over many CTAs) is the better choice."""
+    if not (_TENSOR_CORE_ATTENTION and dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128 and group <= 16):
+        return False
+    return not (num_requests * n_kv_heads < 64 and max_context > 4096)
+
+
+def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim, page_size,
+                           theta, rotary=True, window=0, scale=None, out=None):
+    """qkv fp32 [S,(NH+2NKV)*HD], one new token per request: rotates q and k (``rotary``), writes k and v into
+    the cache at ``slot_mapping`` and returns the attention output bf16 [S, NH*HD], all in one kernel."""
+    lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
+    S = qkv.shape[0]
+    if out is None:
+        out = torch.empty((S, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    scale = head_dim ** -0.5 if scale is None else scale
+    _check(lib, lib.forge_decode_attention_fused(
+        _need(qkv, "qkv", torch.float32, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
+        _need(block_table, "block_table", torch.int32, 2), _need(positions, "positions", torch.int32),
+        _need(slot_mapping, "slot_mapping", torch.int32), S, n_heads, n_kv_heads, head_dim, page_size, block_table.shape[1],
+        int(window or 0), 1 if rotary else 0, float(theta), float(scale), _stream()), "decode_attention_fused")
     return out
 
 

@@ -50,10 +50,28 @@ class GQAAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def _decode_in_one_kernel(self, batch, cache):
+        """A step of one new token per request, with a position encoding whose kernel is the rotary one (or
+        none): encoding, cache write and attention run as one launch."""
+        if batch.num_tokens != batch.num_requests or not cache.writable or self.rt.full_precision:
+            return False
+        if not (hasattr(self.position, "rotary") and hasattr(self.position, "theta")):
+            return False
+        max_ctx = getattr(batch, "max_context", None) or (max(batch.host_context_before) + 1)
+        return kernels.decode_attention_fused_supports(self.rt.dtype, self.head_dim, self.num_heads // self.num_kv_heads,
+                                                       batch.num_requests, self.num_kv_heads, max_ctx)
+
     def forward(self, x, batch, cache, residual):
         """x [T,H] normed input; cache: the layer's KV cache view; adds the output projection into residual."""
         g = batch.groups[cache.group]
         qkv = self.qkv.forward(x)                                           # fp32 [T,(NH+2NKV)*HD]
+        if self._decode_in_one_kernel(batch, cache):
+            o = kernels.decode_attention_fused(qkv, cache.kv, g.block_table, batch.positions, g.slot_mapping,
+                                               self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
+                                               self.position.theta, rotary=self.position.rotary, window=self.window,
+                                               scale=self.scale)
+            self.o.forward(o, accumulate_into=residual)
+            return
         slots = g.slot_mapping if cache.writable else None
         q = self.position.encode_and_store(qkv, batch.positions, slots, cache.kv if cache.writable else None,
                                            self.num_heads, self.num_kv_heads, cache.page_size)

@@ -83,3 +83,28 @@ def test_far_key_and_page_edges():
     for splits in (1, 4):
         got = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, num_splits=splits).float()
         assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 4, 64, 16), (3, 1, 32, 8), (16, 2, 128, 16), (6, 2, 80, 16), (4, 4, 16, 16)])
+@pytest.mark.parametrize("window,rotary", [(0, True), (40, True), (0, False)])
+def test_decode_step_in_one_kernel(nh, nkv, hd, ps, window, rotary):
+    """Rotary encoding + cache write + attention of one new token per request in one launch, against the
+    plain rope-and-write followed by the plain attention; contexts on and around page and tile edges, few
+    and many requests (8 or 4 warps per CTA)."""
+    from forge_b200 import kernels as k
+    theta = 5e5
+    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 300, 1000], [7] * 70 + [129]):
+        reqs = [(c, 1) for c in ctxs]
+        q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=4)
+        S = len(reqs)
+        qkv = torch.randn(S, (nh + 2 * nkv) * hd, generator=torch.Generator().manual_seed(9)).to(q.device) * 1.5
+        slots = torch.tensor([int(group.block_table[s, c // ps]) * ps + c % ps for s, c in enumerate(ctxs)],
+                             dtype=torch.int32, device=q.device)
+        q_ref, cache_ref = R.rope_kv_write_ref(qkv, positions, slots, cache, nh, nkv, hd, ps, theta, rotary)
+        cache_ref = cache_ref.to(torch.bfloat16)                  # the engine's cache holds bf16
+        ref = R.paged_attention_ref(q_ref.to(torch.bfloat16), cache_ref, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
+        work = cache.clone()
+        got = k.decode_attention_fused(qkv, work, group.block_table, positions, slots, nh, nkv, hd, ps, theta,
+                                       rotary=rotary, window=window).float()
+        assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
+        assert (work.float() - cache_ref.float()).abs().max() <= 1e-2 * cache_ref.float().abs().max()   # k, v landed in their slots
