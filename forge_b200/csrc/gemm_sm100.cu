@@ -506,7 +506,6 @@ template <int NT> struct StreamKCfg {
 };
 
 struct StreamKWork {
-    int debug;
     float* partials;      // [tiles_n][max_parts][NT][128]
     int* flags;           // [tiles_n][max_parts], zero between launches
     int per_cta;          // units per CTA
@@ -702,7 +701,6 @@ gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             }
             tc_fence_before_sync();
             mbar_arrive(&acc_empty[a]);             // the MMA warp may reuse this accumulator now
-            if (wk.debug == 1) continue;
             // which fragment of its tile is this?  The tile's first unit belongs to CTA c0.
             const int part = (int)blockIdx.x - (tile * num_kb) / wk.per_cta;
             if (kb1 < num_kb) {
@@ -794,8 +792,7 @@ int launch_streamk(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParam
         (long long)tiles_n * max_parts * 4 > kFlagBytes)
         return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: the stream-K workspace of device %d holds %lld bytes, %lld needed "
                            "(call forge_gemm_sm100_set_workspace)", dev, dev >= 0 && dev < 64 ? g_workspace[dev].bytes : 0LL, need);
-    static const int dbg = getenv("FORGE_SK_DEBUG") ? atoi(getenv("FORGE_SK_DEBUG")) : 0;
-    StreamKWork wk{dbg, reinterpret_cast<float*>(static_cast<char*>(g_workspace[dev].ptr) + kFlagBytes),
+    StreamKWork wk{reinterpret_cast<float*>(static_cast<char*>(g_workspace[dev].ptr) + kFlagBytes),
                    static_cast<int*>(g_workspace[dev].ptr), per_cta, max_parts};
     const int stages = per_cta < C::kStages ? per_cta : C::kStages;
     return forge::check_launch("gemm_sm100 (few rows, stream-K)",

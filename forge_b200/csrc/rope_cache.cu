@@ -12,13 +12,28 @@
 
 namespace {
 
+// cos/sin of every (token, pair) of a step: the angles depend on the position and the pair only, so one small
+// kernel per step serves every head of every layer.  table[t, d] = (cos, sin) of positions[t] / theta^(2d/HD).
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, float2* __restrict__ table, int T, int HD, float theta) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, half = HD >> 1;
+    if (i >= T * half) return;
+    const int t = i / half, d = i % half;
+    const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
+    float s, c;
+    sincosf((float)positions[t] * freq, &s, &c);
+    table[i] = make_float2(c, s);
+}
+
 // One thread per pair (d, d + HD/2) of one head of one token: q and k heads are rotated, v heads copied.
+// `table` (optional): the step's cos/sin from rope_table_kernel; without it the angles are computed here.
 template <typename TAct, typename TCache>
 __global__ void __launch_bounds__(128)
 rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
                      const int32_t* __restrict__ slot_mapping, TAct* __restrict__ q_out,
                      TCache* __restrict__ kv_cache, int NH, int NKV, int HD, int page_size,
-                     float theta, int rotary) {
+                     float theta, int rotary, const float2* __restrict__ table) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int t = blockIdx.x;
@@ -29,9 +44,15 @@ rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ 
     const float* row = qkv + (size_t)t * (NH + 2 * NKV) * HD;
     float x0 = row[h * HD + d], x1 = row[h * HD + d + half];
     if (rotary && h < NH + NKV) {
-        const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
         float s, c;
-        sincosf((float)positions[t] * freq, &s, &c);
+        if (table) {
+            const float2 cs = table[(size_t)t * half + d];
+            c = cs.x;
+            s = cs.y;
+        } else {
+            const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
+            sincosf((float)positions[t] * freq, &s, &c);
+        }
         const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
         x0 = y0;
         x1 = y1;
@@ -53,9 +74,19 @@ rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ 
 
 }  // namespace
 
+// table: float [T, HD/2, 2] (cos, sin) for the step's tokens.
+extern "C" int forge_rope_table(const int32_t* positions, float* table, int T, int HD, float theta, cudaStream_t stream) {
+    if (T < 0 || HD <= 0 || (HD & 1)) return forge::fail(FORGE_ERR_ARG, "rope_table: bad sizes T=%d HD=%d", T, HD);
+    if (T == 0) return FORGE_OK;
+    const long n = (long)T * (HD / 2);
+    return forge::check_launch("rope_table", forge::launch(rope_table_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0,
+                                                           stream, 1, positions, reinterpret_cast<float2*>(table), T, HD, theta));
+}
+
+// table: optional cos/sin table from forge_rope_table for the same positions, HD and theta (null: compute here).
 extern "C" int forge_rope_kv_write(const float* qkv, const int32_t* positions, const int32_t* slot_mapping,
                                    void* q_out, void* kv_cache, int dtype, int T, int NH, int NKV, int HD,
-                                   int page_size, float theta, int rotary, cudaStream_t stream) {
+                                   int page_size, float theta, int rotary, const float* table, cudaStream_t stream) {
     if (T > 2147483647 / 2 || ((NH + 2 * NKV) * (HD / 2) + 127) / 128 > 65535)
         return forge::fail(FORGE_ERR_UNSUPPORTED, "rope_kv_write: too many heads for one launch");
     if (T < 0 || NH <= 0 || NKV <= 0 || HD <= 0 || (HD & 1) || page_size <= 0)
@@ -65,6 +96,7 @@ extern "C" int forge_rope_kv_write(const float* qkv, const int32_t* positions, c
     cudaError_t e = cudaSuccess;
     FORGE_DISPATCH_DTYPE(dtype, TT,
         e = forge::launch(rope_kv_write_kernel<TT, TT>, dim3(T, ((NH + 2 * NKV) * (HD / 2) + 127) / 128), dim3(128), 0, stream, 1,
-                          qkv, positions, slot_mapping, (TT*)q_out, (TT*)kv_cache, NH, NKV, HD, page_size, theta, rotary));
+                          qkv, positions, slot_mapping, (TT*)q_out, (TT*)kv_cache, NH, NKV, HD, page_size, theta, rotary,
+                          reinterpret_cast<const float2*>(table)));
     return forge::check_launch("rope_kv_write", e);
 }

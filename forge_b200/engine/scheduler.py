@@ -224,7 +224,10 @@ class RequestScheduler:
             return False
         entries, rows = [], []
         for r, start, n, wants in plan:
-            toks = r.tokens_to_compute()[start:start + n]
+            if r.status == RequestStatus.Decoding and n == 1:
+                toks = [r.output_tokens[-1]]              # no need to rebuild prompt + outputs for one token
+            else:
+                toks = r.tokens_to_compute()[start:start + n]
             entries.append(StepEntry(r.request_id, toks, [n - 1] if wants else []))
             if wants:
                 rows.append(r)

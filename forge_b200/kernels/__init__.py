@@ -33,7 +33,8 @@ _SIGNATURES = {
     "core": {
         "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
-        "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+        "forge_rope_table": [_P, _P, _I, _I, _F, _P],
         "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _P],
         "forge_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_paged_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
@@ -150,8 +151,19 @@ def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
     return out
 
 
+def rope_table(positions, head_dim, theta):
+    """float32 [T, head_dim/2, 2]: (cos, sin) of position / theta^(2d/head_dim) for the step's tokens; computed once
+    per step and shared by every head of every layer with the same head size and base."""
+    lib = library("core")
+    T = positions.numel()
+    table = torch.empty((T, head_dim // 2, 2), dtype=torch.float32, device=positions.device)
+    _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
+                                     float(theta), _stream()), "rope_table")
+    return table
+
+
 def rope_kv_write(qkv, positions, slot_mapping, kv_cache, n_heads, n_kv_heads, head_dim, page_size, theta,
-                  act_dtype, rotary=True, q_out=None):
+                  act_dtype, rotary=True, q_out=None, table=None):
     """Rotates q and k of float32 qkv [T,(NH+2NKV)*HD], returns q [T,NH*HD] in ``act_dtype`` and writes
     k, v into ``kv_cache`` [pages,2,NKV,page,HD] at ``slot_mapping`` (int32 [T]; None or negative: no write)."""
     lib = library("core")
@@ -168,7 +180,8 @@ def rope_kv_write(qkv, positions, slot_mapping, kv_cache, n_heads, n_kv_heads, h
     _check(lib, lib.forge_rope_kv_write(_need(qkv, "qkv", torch.float32, 2), _need(positions, "positions", torch.int32),
                                         _opt(slot_mapping, "slot_mapping", torch.int32), _need(q_out, "q_out", act_dtype),
                                         _opt(kv_cache, "kv_cache"), dtype_code(act_dtype), T, n_heads, n_kv_heads,
-                                        head_dim, page_size, float(theta), 1 if rotary else 0, _stream()),
+                                        head_dim, page_size, float(theta), 1 if rotary else 0,
+                                        _opt(table, "table", torch.float32), _stream()),
            "rope_kv_write")
     return q_out
 

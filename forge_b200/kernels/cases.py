@@ -8,7 +8,7 @@ from types import SimpleNamespace
 
 import torch
 
-from . import gemm_sm100, paged_attention, paged_attention_mma
+from . import decode_attention_fused, gemm_sm100, paged_attention, paged_attention_mma
 
 DEV = "cuda:0"
 H, I, NH, NKV, HD, PS = 2048, 5632, 32, 4, 64, 16
@@ -51,6 +51,13 @@ def case(name):
     if name == "attention_decode":           # 64 requests, 1024 cached tokens each, one new token: 67 MB of K/V
         q, kv, g, b = _attention_inputs([(1023, 1)] * 64)
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 64 * 1024 * 2 * NKV * HD * 2, 4 * 64 * 1024 * NH * HD
+    if name == "attention_decode_fused":     # the same decode step as one kernel: rotary + cache write + attention
+        q, kv, g, b = _attention_inputs([(1023, 1)] * 64)
+        qkv = torch.randn(64, (NH + 2 * NKV) * HD, device=DEV)
+        pos = torch.full((64,), 1023, dtype=torch.int32, device=DEV)
+        slots = (g.block_table[:, 1023 // PS] * PS + 1023 % PS).to(torch.int32).contiguous()
+        return (lambda: decode_attention_fused(qkv, kv, g.block_table, pos, slots, NH, NKV, HD, PS, 1e4)), \
+            64 * 1024 * 2 * NKV * HD * 2, 4 * 64 * 1024 * NH * HD
     if name == "attention_prefill":          # one request, 2048 tokens, causal: 17.2 GFLOP
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
@@ -58,7 +65,7 @@ def case(name):
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
     raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_prefill_gateup "
-                     "gemm_prefill_down attention_decode attention_prefill")
+                     "gemm_prefill_down attention_decode attention_decode_fused attention_prefill attention_prefill_mma")
 
 
 def main(argv):

@@ -74,7 +74,7 @@ class GQAAttention(Part):
             return
         slots = g.slot_mapping if cache.writable else None
         q = self.position.encode_and_store(qkv, batch.positions, slots, cache.kv if cache.writable else None,
-                                           self.num_heads, self.num_kv_heads, cache.page_size)
+                                           self.num_heads, self.num_kv_heads, cache.page_size, batch=batch)
         o = kernels.paged_attention(q, cache.kv, g, batch, self.num_heads, self.num_kv_heads, self.head_dim,
                                     cache.page_size, window=self.window, scale=self.scale)
         self.o.forward(o, accumulate_into=residual)

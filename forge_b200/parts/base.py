@@ -6,7 +6,7 @@ the model configuration or at other layers.  Categories and the interface of eac
 
   norm          forward(x_f32[T,H], out_dtype, rows=None) -> [R,H]
   position      encode_and_store(qkv_f32, positions, slot_mapping, kv_cache, num_heads, num_kv_heads,
-                                 page_size, act_dtype) -> q[T,NH*HD]
+                                 page_size, batch=None) -> q[T,NH*HD]
   mixer         cache_spec() -> KVCacheSpec | StateSpec | None
                 forward(x[T,H], batch, cache, residual_f32[T,H])      (adds its output into residual)
   feed_forward  forward(x[T,H], residual_f32[T,H])                     (adds its output into residual)

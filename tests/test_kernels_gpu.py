@@ -68,6 +68,10 @@ def test_rope_kv_write(dtype, nh, nkv, hd, ps, theta):
     tol = 2e-4 if dtype == torch.float32 else 1e-2     # fp32 angles at positions up to 3000
     assert (q.float() - q_ref).abs().max() <= tol * q_ref.abs().max()
     assert (cache.float() - cache_ref).abs().max() <= tol * cache_ref.abs().max()
+    # with the step's cos/sin table instead of angles computed per head: the same numbers
+    cache2 = torch.zeros_like(cache)
+    q_t = k.rope_kv_write(qkv, positions, slots, cache2, nh, nkv, hd, ps, theta, dtype, table=k.rope_table(positions, hd, theta))
+    assert torch.equal(q_t, q) and torch.equal(cache2, cache)
     # no rotation: a plain copy
     q2 = k.rope_kv_write(qkv, positions, None, None, nh, nkv, hd, ps, theta, dtype, rotary=False)
     assert torch.equal(q2.float(), qkv[:, :nh * hd].to(dtype).float())
