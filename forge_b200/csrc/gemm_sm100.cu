@@ -266,14 +266,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 // own shared memory, the cluster synchronises, and each CTA then adds up, in rank order (so the result
 // does not depend on timing), the slice of rows it owns, applies the epilogue and writes C.  No scratch
 // in global memory, no atomics.
+//
+// One TMA instruction keeps an SM's copy engine busy for about one memory latency (measured: ~0.4 us from
+// DRAM, the same for boxes of 8, 16, 32 and 64 KB, and no faster with more instructions in flight), so an SM
+// that asks for one 16 KB k-block at a time pulls 45 GB/s whatever the depth of its pipeline.  A stage here
+// is therefore a GROUP of up to 4 consecutive k-blocks brought by one instruction per operand: the matrix
+// [rows, K] is described to TMA as {64 columns, rows, K / 64 k-blocks} (k-block stride 128 bytes), and a box
+// {64, 128, g} lands in shared memory as g standard 128-byte-swizzled [128 x 64] tiles one after the other.
+// That needs K % 64 == 0; other K take the plain 2D map with one k-block per stage.
 template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
-    static constexpr int kStageBytes = BM * BK * 2 + NT * BK * 2;
+    static constexpr int kBlockBytes = BM * BK * 2 + NT * BK * 2;      // one k-block of W and of the tokens
     static constexpr int kPartialBytes = NT * BM * 4;
-    static constexpr int kMaxStages = (kSmemLimit - 2048 - kPartialBytes) / kStageBytes > 12
-                                          ? 12 : (kSmemLimit - 2048 - kPartialBytes) / kStageBytes;
+    static constexpr int kMaxGroup = 4;
+    static constexpr int kMaxStages = 12;
+    static constexpr int max_stages(int group) {
+        const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * kBlockBytes);
+        return fit > kMaxStages ? kMaxStages : fit;
+    }
     static constexpr int kTmemCols = NT < 32 ? 32 : NT;
-    // a CTA takes only as many stages as it has k-blocks, so that CTAs of the next kernel fit beside it
-    static constexpr int smem_bytes(int stages) { return stages * kStageBytes + kPartialBytes + 1024 + 1024; }
+    // a CTA takes only as many stages as it has work for, so that CTAs of the next kernel fit beside it
+    static constexpr int smem_bytes(int stages, int group) { return stages * group * kBlockBytes + kPartialBytes + 1024 + 1024; }
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -296,28 +308,35 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                         const GemmParams p, const int ksplit, const int kStages) {
+                         const GemmParams p, const int ksplit, const int kStages, const int group) {
+    // group > 0: the maps are the 3D k-block views and a stage holds `group` k-blocks; group == 0: 2D maps,
+    // one k-block per stage
     using C = SkinnyCfg<NT>;
+    const int g = group > 0 ? group : 1;
+    const int w_bytes = g * BM * BK * 2, x_bytes = g * NT * BK * 2;       // one stage of each operand
+    const int x_region = kStages * x_bytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tiles = smem;
-    float* partial = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);          // [NT][BM]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kPartialBytes);
+    uint8_t* w_tiles = smem;                                   // [kStages][g][128 x 64]
+    uint8_t* x_tiles = smem + kStages * w_bytes;               // [kStages][g][NT x 64]
+    float* partial = reinterpret_cast<float*>(x_tiles + x_region);          // [NT][BM]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(x_tiles + x_region + C::kPartialBytes);
     uint64_t* full = bars;
     uint64_t* acc_full = bars + C::kMaxStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kMaxStages + 1);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // A stage is used once per CTA when the CTA has at most kStages k-blocks; beyond that the producer
-    // reuses stage s for k-block s + kStages once the MMA warp has committed it (signalled through `reuse`).
+    // A stage is used once per CTA when the CTA has at most kStages groups; beyond that the producer
+    // reuses stage s for group s + kStages once the MMA warp has committed it (signalled through `reuse`).
     uint64_t* reuse = bars + C::kMaxStages + 2;   // [kStages] MMA -> TMA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int n0 = (blockIdx.x / ksplit) * BM;
     const int num_kb = (p.K + BK - 1) / BK;
-    const int kb_per = (num_kb + ksplit - 1) / ksplit;
+    const int kb_per = ((num_kb + ksplit - 1) / ksplit + g - 1) / g * g;      // whole groups per CTA
     const int kb_begin = rank * kb_per, kb_end = min(kb_begin + kb_per, num_kb);
     const int my_kb = max(kb_end - kb_begin, 0);
+    const int my_groups = (my_kb + g - 1) / g;
 
     if (threadIdx.x == 0) {
         *abort = 0;
@@ -339,39 +358,52 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
+            // a group that sticks out over the end of K is filled with zeros there and counts in full
+            const int stage_tx = w_bytes + x_bytes;
+            auto load_w = [&](int i, int s) {
+                if (group > 0) tma_load_3d(w_tiles + s * w_bytes, &tmap_w, &full[s], 0, n0, kb_begin + i * g);
+                else tma_load_2d(w_tiles + s * w_bytes, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
+            };
+            auto load_x = [&](int i, int s) {
+                if (group > 0) tma_load_3d(x_tiles + s * x_bytes, &tmap_x, &full[s], 0, 0, kb_begin + i * g);
+                else tma_load_2d(x_tiles + s * x_bytes, &tmap_x, &full[s], (kb_begin + i) * BK, 0);
+            };
             // the weights do not depend on earlier kernels: their first stages are requested before the wait
-            const int first = min(my_kb, kStages);
+            const int first = min(my_groups, kStages);
             for (int i = 0; i < first; ++i) {
-                mbar_arrive_expect_tx(&full[i], C::kStageBytes);
-                tma_load_2d(tiles + i * C::kStageBytes, &tmap_w, &full[i], (kb_begin + i) * BK, n0);
+                mbar_arrive_expect_tx(&full[i], stage_tx);
+                load_w(i, i);
             }
             forge::pdl_wait();                    // the activations come from the previous kernel
-            for (int i = 0; i < first; ++i)
-                tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_x, &full[i], (kb_begin + i) * BK, 0);
+            for (int i = 0; i < first; ++i) load_x(i, i);
             bool ok = true;
-            for (int i = first; i < my_kb && ok; ++i) {
+            for (int i = first; i < my_groups && ok; ++i) {
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&reuse[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
-                mbar_arrive_expect_tx(&full[s], C::kStageBytes);
-                uint8_t* w_dst = tiles + s * C::kStageBytes;
-                tma_load_2d(w_dst, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
-                tma_load_2d(w_dst + BM * BK * 2, &tmap_x, &full[s], (kb_begin + i) * BK, 0);
+                mbar_arrive_expect_tx(&full[s], stage_tx);
+                load_w(i, s);
+                load_x(i, s);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, NT);
             bool ok = true;
-            for (int i = 0; i < my_kb && ok; ++i) {
+            for (int i = 0; i < my_groups && ok; ++i) {
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
                 tc_fence_after_sync();
-                const uint32_t w_addr = smem_u32(tiles + s * C::kStageBytes);
-                const uint32_t x_addr = w_addr + BM * BK * 2;
+                const uint32_t w_base = smem_u32(w_tiles + s * w_bytes);
+                const uint32_t x_base = smem_u32(x_tiles + s * x_bytes);
+                const int here = min(g, my_kb - i * g);            // k-blocks of this group inside my range
+                for (int j = 0; j < here; ++j) {
+                    const uint32_t w_addr = w_base + j * (BM * BK * 2);
+                    const uint32_t x_addr = x_base + j * (NT * BK * 2);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem_base, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
-                              umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (i | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(tmem_base, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
+                                  umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (i | j | k) != 0);
+                }
                 umma_commit(&reuse[s]);
             }
             if (ok && my_kb > 0) umma_commit(acc_full);
@@ -744,23 +776,40 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cu
                                                              C::kSmemBytes, stream, 1, ta, tw, p));
 }
 
+// k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps)
+int few_rows_group(int K, int kb_per, int max_group) {
+    if (K % BK != 0) return 0;
+    const int g = kb_per < max_group ? kb_per : max_group;
+    return g < 1 ? 1 : g;
+}
+
 template <int NT>
-int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int ksplit, cudaStream_t stream) {
+int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit, cudaStream_t stream) {
     using C = SkinnyCfg<NT>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             C::smem_bytes(C::kMaxStages));
+        cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
-                                                 C::smem_bytes(C::kMaxStages), cudaGetErrorString(e));
+                                                 kSmemLimit, cudaGetErrorString(e));
         configured = true;
     }
     const int tiles_n = (p.N + BM - 1) / BM;
     const int num_kb = (p.K + BK - 1) / BK, kb_per = (num_kb + ksplit - 1) / ksplit;
-    const int stages = kb_per < C::kMaxStages ? kb_per : C::kMaxStages;
+    const int group = few_rows_group(p.K, kb_per, C::kMaxGroup), g = group > 0 ? group : 1;
+    const int groups_per = (kb_per + g - 1) / g;
+    const int stages = groups_per < C::max_stages(g) ? groups_per : C::max_stages(g);
+    CUtensorMap tw, tx;
+    const char* err = nullptr;
+    if (group > 0) {
+        if (!bf16_kblock_map(W, p.N, p.K, BM, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_kblock_map(A, p.M, p.K, NT, group, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+    } else {
+        if (!bf16_tile_map(W, p.N, p.K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_tile_map(A, p.M, p.K, NT, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+    }
     return forge::check_launch("gemm_sm100 (few rows)",
                                forge::launch(gemm_sm100_skinny_kernel<NT>, dim3(tiles_n * ksplit), dim3(kThreads),
-                                             C::smem_bytes(stages), stream, ksplit, tw, tx, p, ksplit, stages));
+                                             C::smem_bytes(stages, g), stream, ksplit, tw, tx, p, ksplit, stages, group));
 }
 
 // workspace for the stream-K partial sums and flags, per device, handed over once by the caller
@@ -798,6 +847,35 @@ int launch_streamk(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParam
     return forge::check_launch("gemm_sm100 (few rows, stream-K)",
                                forge::launch(gemm_sm100_streamk_kernel<NT>, dim3(grid), dim3(kThreads),
                                              C::smem_bytes(stages), stream, 1, tw, tx, p, wk, stages));
+}
+
+// How many CTAs of the few-rows kernel run at once when launched in clusters of `ks` with all the shared
+// memory an SM has (one CTA per SM): fewer than there are SMs, because a cluster lives inside one GPC
+// (B200: 148, 148, 132 and 120 for clusters of 1, 2, 4 and 8).
+int max_resident_ctas(int ks) {
+    static int cached[9] = {0};
+    if (ks < 1 || ks > 8) return 0;
+    if (cached[ks] == 0) {
+        cudaFuncSetAttribute(gemm_sm100_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ks * 64);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemLimit;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = ks;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_skinny_kernel<16>, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = (g_num_sms - g_num_sms / 8 * (ks > 2 ? (ks > 4 ? 2 : 1) : 0)) / ks;      // a guess on the safe side
+        }
+        cached[ks] = n * ks;
+    }
+    return cached[ks];
 }
 
 }  // namespace
@@ -840,11 +918,11 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         int dev = 0;
         cudaGetDevice(&dev);
         const bool have_ws = dev >= 0 && dev < 64 && g_workspace[dev].ptr != nullptr;
-        // worth it when a tile is shared by few CTAs and the partial sums (which cross global memory) are small:
-        // units per CTA >= half a tile, at most 32 tokens
-        const int sk_per_cta = (tiles_n * num_kb + g_num_sms - 1) / g_num_sms;
-        if ((tile_n == 0 && have_ws && nt <= 32 && tiles_n * num_kb >= g_num_sms && 2 * sk_per_cta >= num_kb) || tile_n == -100) {
-            // deal the (row tile, k-block) units out evenly over the SMs
+        // More row tiles than SMs (a vocabulary): deal the (row tile, k-block) units out evenly over the SMs.
+        // Otherwise one wave of clusters, see below; the partial sums of stream-K cross global memory, which
+        // costs more than an uneven last wave unless there are many tiles (measured at 88 tiles: 13.2 against
+        // 11.0 us).
+        if ((tile_n == 0 && have_ws && nt <= 32 && tiles_n > g_num_sms) || tile_n == -100) {
             CUtensorMap tw, tx;
             if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
             if (!bf16_tile_map(A, M, K, nt, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
@@ -861,20 +939,17 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
                 return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1, 2, 4 or 8, got %d", ksplit);
         } else {
-            // as many CTAs as fit the GPU at once; a cluster of 8 only when each CTA then still has a short
-            // pipeline of its own (measured: with K = 5632, 4 CTAs of 22 k-blocks beat 8 of 11)
-            while (ksplit < 8 && tiles_n * ksplit * 2 <= g_num_sms + g_num_sms / 8 && num_kb / (ksplit * 2) >= 2 &&
-                   (ksplit < 4 || (num_kb <= 32 && nt == 16)))
-                ksplit *= 2;
+            // The widest cluster whose CTAs all run at once (a second wave doubles the time) and still have a
+            // group of four k-blocks each.  An SM's tensor core takes W from shared memory at about 100 GB/s
+            // (the M operand of an N = 16 MMA), so it takes some 64 streaming SMs to keep up with HBM.
+            for (int ks = 2; ks <= 8; ks *= 2)
+                if (tiles_n * ks <= max_resident_ctas(ks) && num_kb / ks >= 4) ksplit = ks;
         }
-        CUtensorMap tw, tx;
-        if (!bf16_tile_map(W, N, K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
-        if (!bf16_tile_map(A, M, K, nt, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
         GemmParams p{C, bias, M, N, K, epilogue, status};
         switch (nt) {
-            case 16: return launch_skinny<16>(tw, tx, p, ksplit, stream);
-            case 32: return launch_skinny<32>(tw, tx, p, ksplit, stream);
-            default: return launch_skinny<64>(tw, tx, p, ksplit, stream);
+            case 16: return launch_skinny<16>(W, A, p, ksplit, stream);
+            case 32: return launch_skinny<32>(W, A, p, ksplit, stream);
+            default: return launch_skinny<64>(W, A, p, ksplit, stream);
         }
     }
     int bn = tile_n;

@@ -76,21 +76,33 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait with an upper limit (ns) on how long the hardware may keep the thread suspended; it still wakes
+// the thread as soon as the phase completes.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t suspend_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, int where = 0) {
-    // fast path: a few potentially-suspending tries (the hardware wakes the thread when the phase completes)
-    if (mbar_try_wait(bar, parity) || mbar_try_wait(bar, parity)) return true;
-    // slow path: non-blocking tests, so that the clock is looked at after every one of them (try_wait may
-    // suspend the thread for a system-dependent time that is much longer than the limit)
+    // Suspending waits: the hardware wakes the thread the moment the phase completes (a polling loop with
+    // sleeps in it notices a completed phase late, and in a short pipeline that delay is a bubble); the
+    // suspend limit bounds how long an abort or the time limit can go unnoticed.
+    if (mbar_try_wait_for(bar, parity, 1000)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
-        if (mbar_test_wait(bar, parity)) return true;
+        if (mbar_try_wait_for(bar, parity, 4000)) return true;
         if (*abort) return false;
         if (global_ns() - t0 > kWaitLimitNs) {
             *abort = 1;
             if (status) atomicOr(status, 2 | (1 << (4 + where)));
             return false;
         }
-        __nanosleep(32);
     }
 }
 
@@ -295,6 +307,39 @@ inline bool bf16_tile_map(const void* ptr, int rows, int cols, int box_rows, CUt
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed"; return false; }
     if (cache.size() > 4096) cache.clear();   // activation buffers come and go; weights re-enter on next use
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+// Map of the same row-major bf16 matrix [rows, cols], cols % 64 == 0, seen as {64 columns, rows, cols / 64
+// k-blocks}: a box {64, box_rows, group} brings `group` consecutive k-blocks of `box_rows` rows with ONE
+// instruction and lands as `group` 128-byte-swizzled [box_rows x 64] tiles one after the other.  Coordinates
+// are (0, row, k-block).  Rows and k-blocks out of range are filled with zeros.
+inline bool bf16_kblock_map(const void* ptr, int rows, int cols, int box_rows, int group, CUtensorMap* out, const char** err) {
+    using Key = std::tuple<const void*, int, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key{ptr, rows, cols, box_rows, group};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    auto fn = encode_fn();
+    if (!fn) { *err = "cuTensorMapEncodeTiled is not available from the driver"; return false; }
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (cols % 64) != 0 || group < 1 || group > 256 || box_rows > 256) {
+        *err = "the k-block view needs a 16-byte aligned base, a row of a multiple of 64 bf16 and boxes of at most 256";
+        return false;
+    }
+    CUtensorMap m;
+    const cuuint64_t dims[3] = {64u, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(cols / 64)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128u};
+    const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(group)};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed (k-block view)"; return false; }
+    if (cache.size() > 4096) cache.clear();
     cache.emplace(key, m);
     *out = m;
     return true;
