@@ -8,8 +8,9 @@ the decode step's HBM roofline.  Prints ONE JSON line.
 A "step" is one decode step (one new token for every request of the batch).  `value` is timed on the
 device with CUDA events around exactly K steps whose input tokens are the previous step's argmax, fed back
 on the device; `e2e` runs the same decoding through the Python entry point (RequestScheduler.submit/step):
-every step copies that step's integers from pinned host memory to the device and reads the sampled tokens
-back.  Weights (2.07 GB) exceed the 126 MB L2, so every step streams them from HBM.
+every step copies that step's integers from pinned host memory to the device and reads sampled tokens back
+to the host (the scheduler launches step k before it reads step k-1's tokens, so the read of every step's
+result happens one step late and off the device's critical path).  Weights (2.07 GB) exceed the 126 MB L2, so every step streams them from HBM.
 """
 import argparse
 import json

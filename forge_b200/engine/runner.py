@@ -77,6 +77,7 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs)
         self._decode_graphs = {}
         self._last_greedy = None
+        self._token_rings = {}
 
     # ---------------------------------------------------------------------------------- requests
     def admit(self, req_id):
@@ -150,6 +151,23 @@ class ModelRunner:
             self.manager.release_out_of_window(e.req_id)
         return out
 
+    def decode_step_async(self, entries, from_previous=False):
+        """decode_step whose greedy tokens are not waited for: returns a handle whose ``tokens()`` blocks until
+        the step has run and gives them as a list.  ``from_previous``: take the input tokens from the previous
+        decode step's greedy tokens on the device (the entries' token ids are placeholders)."""
+        _, greedy = self.decode_step(entries, tokens_on_device=from_previous)
+        S = greedy.numel()
+        ring = self._token_rings.get(S)
+        if ring is None:
+            # a handle is read at the latest after the NEXT step has been launched: four buffers are plenty
+            ring = self._token_rings[S] = {"bufs": [torch.empty(S, dtype=torch.int32, pin_memory=True) for _ in range(4)],
+                                           "events": [torch.cuda.Event() for _ in range(4)], "pos": 0}
+        i = ring["pos"]
+        ring["pos"] = (i + 1) % len(ring["bufs"])
+        ring["bufs"][i].copy_(greedy, non_blocking=True)
+        ring["events"][i].record()
+        return PendingTokens(ring["bufs"][i], ring["events"][i])
+
     def check_status(self):
         """Reads the device error word (synchronises); raises if a kernel flagged a problem."""
         from .. import kernels
@@ -162,4 +180,15 @@ class ModelRunner:
                                + ("a bounded wait ran out; " if s & 2 else ""))
 
 
-__all__ = ["ModelRunner", "StepEntry", "StepError", "OutOfPages", "resolve_dtype"]
+class PendingTokens:
+    """Greedy tokens of a decode step on their way to pinned host memory."""
+
+    def __init__(self, host, event):
+        self.host, self.event = host, event
+
+    def tokens(self):
+        self.event.synchronize()
+        return self.host.tolist()
+
+
+__all__ = ["ModelRunner", "PendingTokens", "StepEntry", "StepError", "OutOfPages", "resolve_dtype"]

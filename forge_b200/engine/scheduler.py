@@ -13,7 +13,12 @@ requests Waiting -> Prefilling -> Decoding -> Finished | Failed with finish_reas
     prompt plus the tokens it has generated become the prompt to recompute, and it returns to the front of
     the queue; a request that cannot make progress even alone fails with "error:out_of_pages" (the
     reference logs "cache overflow" and carries on, src/inference/kv_cache.cpp:629-633);
-  * every request has its own sampler state.
+  * every request has its own sampler state;
+  * greedy decoding runs one step AHEAD of the host: while the same requests keep decoding, step k is launched
+    with its input tokens taken on the device from step k-1's argmax, and only then are step k-1's tokens read
+    and handed to their requests.  A request that turns out to have ended (eos, a stop token) has then computed
+    one token too many, which is dropped; anything else that would change the batch (a request about to reach
+    its length, an admission, pages running short) first waits for the step in flight.
 """
 from collections import deque
 from dataclasses import dataclass, field
@@ -78,6 +83,7 @@ class RequestScheduler:
         self.num_steps = 0
         self.num_preemptions = 0
         self.last_step = None            # what the last step ran, for tests and logs
+        self._inflight = None            # (requests, handle) of a decode step whose tokens have not been read yet
 
     # ------------------------------------------------------------------------------- public API
     def submit(self, prompt_tokens, max_new_tokens=256, eos_token_id=-1, sampler_config=None, callback=None,
@@ -138,6 +144,7 @@ class RequestScheduler:
         self.waiting.clear()
         self.active.clear()
         self.finished.clear()
+        self._inflight = None
 
     # ------------------------------------------------------------------------------- one step
     def plan_step(self):
@@ -219,12 +226,25 @@ class RequestScheduler:
 
     def step(self):
         """Runs one step.  Returns False when there was nothing to do."""
+        handed_out = False
+        if self._inflight is not None and not self._can_run_ahead():
+            self._resolve_inflight()
+            handed_out = True
         plan = self.plan_step()
         if not plan:
-            return False
+            if self._inflight is not None:
+                self._resolve_inflight()
+                return True
+            return handed_out                             # reading the last step's tokens was work too
+        ahead = self._plan_runs_ahead(plan)
+        if self._inflight is not None and not (ahead and [p[0] for p in plan] == self._inflight[0]):
+            self._resolve_inflight()                      # the plan is not the one the check above foresaw
+            return self.step()
         entries, rows = [], []
         for r, start, n, wants in plan:
-            if r.status == RequestStatus.Decoding and n == 1:
+            if self._inflight is not None:
+                toks = [0]                                # placeholder: the token is on the device
+            elif r.status == RequestStatus.Decoding and n == 1:
                 toks = [r.output_tokens[-1]]              # no need to rebuild prompt + outputs for one token
             else:
                 toks = r.tokens_to_compute()[start:start + n]
@@ -233,9 +253,12 @@ class RequestScheduler:
                 rows.append(r)
         self.last_step = [(r.request_id, start, n, wants) for r, start, n, wants in plan]
         decode_only = all(n == 1 and wants for _, _, n, wants in plan) and getattr(self.runner, "cuda_graphs", False)
-        greedy = None
+        greedy = handle = None
         try:
-            if decode_only:
+            if ahead:
+                self.runner.validate(entries)
+                handle = self.runner.decode_step_async(entries, from_previous=self._inflight is not None)
+            elif decode_only:
                 self.runner.validate(entries)
                 logits, greedy = self.runner.decode_step(entries)
             else:
@@ -243,6 +266,7 @@ class RequestScheduler:
         except OutOfPages:
             raise                                         # plan_step reserved pages; this is a bug
         except Exception as e:                            # a failed step fails the requests that were in it
+            self._inflight = None
             for r, _, _, _ in plan:
                 self._finish(r, RequestStatus.Failed, f"error:{type(e).__name__}")
             raise
@@ -251,9 +275,12 @@ class RequestScheduler:
             self.runner.check_status()                    # device error words, read now and then
         for r, start, n, wants in plan:
             r.current_pos = start + n
-        if rows:
-            if greedy is not None and all(r.sampler.config.greedy and r.sampler.config.repeat_penalty == 1.0
-                                          for r in rows):
+        if ahead:
+            previous, self._inflight = self._inflight, (rows, handle)
+            if previous is not None:
+                self._hand_out(previous)
+        elif rows:
+            if greedy is not None and all(self._greedy_only(r) for r in rows):
                 tokens = greedy.tolist()                  # argmax ran inside the decode graph
                 for r, tok in zip(rows, tokens):
                     r.sampler.record(tok)
@@ -263,11 +290,52 @@ class RequestScheduler:
                 self._accept(r, int(tok))
         return True
 
+    # ---------------------------------------------------------------------- running ahead of the host
+    @staticmethod
+    def _greedy_only(r):
+        return r.sampler.config.greedy and r.sampler.config.repeat_penalty == 1.0
+
+    def _plan_runs_ahead(self, plan):
+        """A step of single decoded tokens, all greedy, on a runner that can leave the tokens on the device."""
+        return (getattr(self.runner, "cuda_graphs", False) and hasattr(self.runner, "decode_step_async")
+                and all(n == 1 and wants and r.status == RequestStatus.Decoding and self._greedy_only(r)
+                        for r, _, n, wants in plan))
+
+    def _can_run_ahead(self):
+        """True if the next step is certainly the same requests as the one in flight, one more token each,
+        whatever tokens that one produces (short of eos / stop, which cost one dropped token)."""
+        rows = self._inflight[0]
+        if self.active != [r.request_id for r in rows]:
+            return False
+        if self.waiting and len(self.active) < self.max_num_seqs and self.manager.has_free_slot():
+            return False                                  # somebody could be admitted
+        reserve = {g: 0 for g in self.manager.groups}
+        for r in rows:
+            if r.status != RequestStatus.Decoding or r.num_generated + 1 >= r.max_new_tokens:
+                return False                              # gone, or its token in flight is its last
+            if not self.manager.can_append(r.request_id, 1, reserve):
+                return False                              # pages run short: plan_step must see final states
+            for g, k in self.manager.pages_needed(r.request_id, 1).items():
+                reserve[g] += k
+        return True
+
+    def _hand_out(self, inflight):
+        rows, handle = inflight
+        for r, tok in zip(rows, handle.tokens()):
+            if r.status == RequestStatus.Decoding:        # not ended or aborted since the step was launched
+                r.sampler.record(int(tok))
+                self._accept(r, int(tok))
+
+    def _resolve_inflight(self):
+        inflight, self._inflight = self._inflight, None
+        self._hand_out(inflight)
+
     def run(self):
         """Steps until no request is pending; returns the finished requests."""
         while self.has_pending():
             if not self.step():
                 break
+        self._inflight = None                             # what is left in flight belongs to ended requests
         if hasattr(self.runner, "check_status"):
             self.runner.check_status()
         return self.get_finished()

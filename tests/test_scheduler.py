@@ -172,3 +172,98 @@ def test_xorshift_matches_the_reference_recurrence():
     assert XorShift64(7).state == 7
     assert SamplerConfig(temperature=0.0).greedy and SamplerConfig(do_sample=False).greedy
     assert not SamplerConfig(temperature=0.8).greedy
+
+
+# ------------------------------------------------------------------ decoding one step ahead of the host
+class FakeAheadRunner(FakeRunner):
+    """A runner whose decode steps hand back a handle instead of tokens, and that can take a step's input
+    tokens from the previous step's outputs 'on the device'."""
+    cuda_graphs = True
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.device_tokens = None
+        self.from_previous = 0
+
+    def validate(self, entries):
+        assert len({e.req_id for e in entries}) == len(entries)
+
+    def decode_step_async(self, entries, from_previous=False):
+        toks = [e.tokens[0] for e in entries]
+        if from_previous:
+            assert self.device_tokens is not None and len(self.device_tokens) == len(entries)
+            toks = self.device_tokens
+            self.from_previous += 1
+        self.steps.append([(e.req_id, 1, [0]) for e in entries])
+        for e in entries:
+            self.manager.append(e.req_id, 1)
+        self.manager.check()
+        out = self.device_tokens = [(t + 1) % 100 for t in toks]
+        return SimpleNamespace(tokens=lambda: list(out))
+
+    def decode_step(self, entries):
+        # one-token prompts look like decode steps to the runner; requests that are decoding never come here
+        assert all(self.manager.num_tokens(e.req_id) == 0 for e in entries)
+        return self.step(entries), None
+
+
+GREEDY = SamplerConfig(do_sample=False)
+
+
+def run_both(submissions, late=(), **kw):
+    """The same requests through the plain and the run-ahead scheduler; ``late``: (after step, submission)."""
+    results = []
+    for cls in (FakeRunner, FakeAheadRunner):
+        r = cls(**{k: v for k, v in kw.items() if k in ("pages", "page_size", "max_requests", "max_positions")})
+        s = RequestScheduler(r, max_num_seqs=kw.get("max_num_seqs", 4), max_tokens_per_step=kw.get("budget", 64),
+                             sample_fn=next_token)
+        for sub in submissions:
+            s.submit(sampler_config=GREEDY, **sub)
+        n = 0
+        while s.has_pending():
+            assert s.step()
+            n += 1
+            for after, sub in late:
+                if after == n:
+                    s.submit(sampler_config=GREEDY, **sub)
+        done = {x.request_id: (x.output_tokens, x.finish_reason, x.status) for x in s.get_finished()}
+        assert r.manager.num_free_pages("g") == kw.get("pages", 8)
+        r.manager.check()
+        results.append((done, r, s))
+    return results
+
+
+def test_running_ahead_gives_the_same_tokens_and_reasons():
+    subs = [dict(prompt_tokens=[10], max_new_tokens=30, eos_token_id=17),
+            dict(prompt_tokens=[20, 21], max_new_tokens=9),
+            dict(prompt_tokens=[40], max_new_tokens=30, stop_token_ids=[52]),
+            dict(prompt_tokens=[60, 61, 62], max_new_tokens=25)]
+    (plain, _, _), (ahead, r, s) = run_both(subs, pages=32)
+    assert ahead == plain and len(ahead) == 4
+    assert r.from_previous >= 10                      # most decode steps took their tokens from the device
+    # an eos costs one dropped token: request 0 (a one-token prompt, so every step it is in brings one token)
+    # was in one more step than it has tokens
+    in_steps = sum(1 for step in r.steps for e in step if e[0] == 0)
+    assert in_steps == len(ahead[0][0]) + 1
+
+
+def test_running_ahead_waits_before_admissions_and_when_pages_run_short():
+    subs = [dict(prompt_tokens=list(range(8)), max_new_tokens=12),
+            dict(prompt_tokens=list(range(50, 58)), max_new_tokens=12)]
+    late = [(4, dict(prompt_tokens=[90, 91], max_new_tokens=5))]
+    (plain, _, sp), (ahead, r, sa) = run_both(subs, late=late, pages=6, budget=64)
+    assert ahead == plain and len(ahead) == 3
+    assert sa.num_preemptions >= 1 and sa.num_preemptions == sp.num_preemptions
+
+
+def test_abort_while_a_step_is_in_flight():
+    r = FakeAheadRunner(pages=16)
+    s = RequestScheduler(r, max_num_seqs=4, max_tokens_per_step=64, sample_fn=next_token)
+    a = s.submit([10], max_new_tokens=20, sampler_config=GREEDY)
+    b = s.submit([30], max_new_tokens=6, sampler_config=GREEDY)
+    for _ in range(3):
+        s.step()
+    s.abort(a)
+    done = {x.request_id: x for x in s.run()}
+    assert done[a].finish_reason == "aborted" and done[b].output_tokens == [31, 32, 33, 34, 35, 36]
+    assert r.manager.num_free_pages("g") == 16
