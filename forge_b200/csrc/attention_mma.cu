@@ -384,15 +384,57 @@ decode_attention_fused_kernel(const DecodeParams p) {
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][LD]  (G heads, zero-padded)
     __nv_bfloat16* kvs = qs + 16 * LD;                                   // [NWARPS][2 buffers][K | V][DKV][LD]
     forge::pdl_launch_dependents();
-    forge::pdl_wait();
     const int s = blockIdx.x, kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.NH / p.NKV;
+    // The step's positions, slots and block tables were written before its first kernel started, and the keys
+    // and values of earlier positions in earlier steps: all of that may be read before the dependency wait,
+    // which only orders this kernel after the product that makes q, k and v.
     const int pos = p.positions[s];
     const int half = HD / 2;
     const float* row = p.qkv + (size_t)s * (p.NH + 2 * p.NKV) * HD;
     const int slot = p.slot_mapping[s];
     __nv_bfloat16* page_base = p.kv + ((size_t)(slot / p.page_size) * 2 * p.NKV + kvh) * p.page_size * HD + (size_t)(slot % p.page_size) * HD;
+
+    const int32_t* table = p.block_table + (size_t)s * p.max_pages;
+    const int kv_hi = pos + 1;
+    const int kv_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int t_begin = kv_lo / DKV, t_end = (kv_hi + DKV - 1) / DKV;
+    __nv_bfloat16* my_k = kvs + (size_t)warp * 4 * DKV * LD;             // [buffer][K | V]
+
+    auto load_tile = [&](int buf, int t) {
+        __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
+        const int tk = t * DKV + lane;                                   // lane = row of the tile
+        int ridx = -1;
+        if (tk >= kv_lo && tk < kv_hi) ridx = (table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
+        const int v_rows = p.NKV * p.page_size;
+#pragma unroll 4
+        for (int c = lane; c < DKV * CPR; c += 32) {
+            const int r_row = c / CPR, ch = c % CPR;
+            const int r = __shfl_sync(0xffffffffu, ridx, r_row);
+            __nv_bfloat16* dk = kd + r_row * LD + ch * 8;
+            __nv_bfloat16* dv = dk + DKV * LD;
+            if (r >= 0) {
+                const __nv_bfloat16* src = p.kv + (size_t)r * HD + ch * 8;
+                cp_async16(dk, src);
+                cp_async16(dv, src + (size_t)v_rows * HD);
+            } else {
+                *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    // 0. this warp's first two tiles are requested now if they hold only earlier positions (the tile with the
+    // new token is read after this kernel has written the token's key and value)
+    int issued = 0;                                                      // tiles of this warp requested so far
+    for (; issued < 2; ++issued) {
+        const int t = t_begin + warp + issued * NWARPS;
+        if (t >= t_end - 1) break;
+        load_tile(issued, t);
+        cp_async_commit();
+    }
+    forge::pdl_wait();
 
     // 1. rotate q (G heads) and k (one head), copy v; q to shared memory, k and v to the cache
     for (int i = threadIdx.x; i < 16 * CPR; i += blockDim.x)             // clear the padding rows of Q
@@ -422,11 +464,6 @@ decode_attention_fused_kernel(const DecodeParams p) {
     __syncthreads();
 
     // 2. every warp walks its share of the key tiles
-    const int32_t* table = p.block_table + (size_t)s * p.max_pages;
-    const int kv_hi = pos + 1;
-    const int kv_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int t_begin = kv_lo / DKV, t_end = (kv_hi + DKV - 1) / DKV;
-    __nv_bfloat16* my_k = kvs + (size_t)warp * 4 * DKV * LD;             // [buffer][K | V]
     const bool valid_a = (lane >> 2) < G, valid_b = (lane >> 2) + 8 < G;
 
     float o_acc[HD / 8][4];
@@ -434,40 +471,15 @@ decode_attention_fused_kernel(const DecodeParams p) {
     for (int i = 0; i < HD / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
-    auto load_tile = [&](int buf, int t) {
-        __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
-        const int tk = t * DKV + lane;                                   // lane = row of the tile
-        int ridx = -1;
-        if (tk >= kv_lo && tk < kv_hi) ridx = (table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
-        const int v_rows = p.NKV * p.page_size;
-#pragma unroll 4
-        for (int c = lane; c < DKV * CPR; c += 32) {
-            const int r_row = c / CPR, ch = c % CPR;
-            const int r = __shfl_sync(0xffffffffu, ridx, r_row);
-            __nv_bfloat16* dk = kd + r_row * LD + ch * 8;
-            __nv_bfloat16* dv = dk + DKV * LD;
-            if (r >= 0) {
-                const __nv_bfloat16* src = p.kv + (size_t)r * HD + ch * 8;
-                cp_async16(dk, src);
-                cp_async16(dv, src + (size_t)v_rows * HD);
-            } else {
-                *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
-            }
-        }
-    };
-
-    int t = t_begin + warp, n_done = 0;
-    if (t < t_end) { load_tile(0, t); cp_async_commit(); }
-    for (; t < t_end; t += NWARPS, ++n_done) {
+    int n_done = 0;
+    for (int t = t_begin + warp; t < t_end; t += NWARPS, ++n_done) {
         const int buf = n_done & 1;
-        if (t + NWARPS < t_end) {
-            load_tile(buf ^ 1, t + NWARPS);
+        // tile n_done and, if there is one, the tile after it are on their way before this one is waited for
+        for (; issued < n_done + 2 && t_begin + warp + issued * NWARPS < t_end; ++issued) {
+            load_tile(issued & 1, t_begin + warp + issued * NWARPS);
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
+        if (issued == n_done + 2) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncwarp();
         const __nv_bfloat16* kb = my_k + (size_t)buf * 2 * DKV * LD;
         const __nv_bfloat16* vb = kb + DKV * LD;
