@@ -138,11 +138,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     if (!(ok = mbar_wait(&full[s], ph, abort, p.status))) break;
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-                    const uint32_t w_addr = a_addr + BM * BK * 2;
+                    const uint64_t a_desc = umma_desc_k_sw128(a_addr), w_desc = umma_desc_k_sw128(a_addr + BM * BK * 2);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        umma_bf16(d_tmem, umma_desc_k_sw128(a_addr + k * UMMA_K * 2),
-                                  umma_desc_k_sw128(w_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+                        umma_bf16(d_tmem, umma_desc_advance(a_desc, k * UMMA_K * 2), umma_desc_advance(w_desc, k * UMMA_K * 2),
+                                  idesc, k != 0 || kb != 0);
                     }
                     umma_commit(&empty[s]);       // stage is free once these MMAs have read it
                 }
@@ -393,16 +393,17 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
                 tc_fence_after_sync();
-                const uint32_t w_base = smem_u32(w_tiles + s * w_bytes);
-                const uint32_t x_base = smem_u32(x_tiles + s * x_bytes);
+                const uint64_t w_desc = umma_desc_k_sw128(smem_u32(w_tiles + s * w_bytes));
+                const uint64_t x_desc = umma_desc_k_sw128(smem_u32(x_tiles + s * x_bytes));
                 const int here = min(g, my_kb - i * g);            // k-blocks of this group inside my range
-                for (int j = 0; j < here; ++j) {
-                    const uint32_t w_addr = w_base + j * (BM * BK * 2);
-                    const uint32_t x_addr = x_base + j * (NT * BK * 2);
+#pragma unroll
+                for (int j = 0; j < C::kMaxGroup; ++j) {
+                    if (j >= here) break;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(tmem_base, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
-                                  umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (i | j | k) != 0);
+                        umma_bf16(tmem_base, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
+                                  umma_desc_advance(x_desc, j * (NT * BK * 2) + k * UMMA_K * 2), idesc,
+                                  (j | k) != 0 || i != 0);
                 }
                 umma_commit(&reuse[s]);
             }
@@ -647,11 +648,11 @@ gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                     if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
                     tc_fence_after_sync();
                     const uint32_t w_addr = smem_u32(tiles + s * C::kStageBytes);
-                    const uint32_t x_addr = w_addr + BM * BK * 2;
+                    const uint64_t w_desc = umma_desc_k_sw128(w_addr), x_desc = umma_desc_k_sw128(w_addr + BM * BK * 2);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(d_tmem, umma_desc_k_sw128(w_addr + k * UMMA_K * 2),
-                                  umma_desc_k_sw128(x_addr + k * UMMA_K * 2), idesc, (u != f_begin || k != 0));
+                        umma_bf16(d_tmem, umma_desc_advance(w_desc, k * UMMA_K * 2), umma_desc_advance(x_desc, k * UMMA_K * 2),
+                                  idesc, k != 0 || u != f_begin);
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[a]);

@@ -165,6 +165,14 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                      // layout type, bits [61,64)
     return d;
 }
+// The descriptor of the same kind of tile `bytes` further on in shared memory (a multiple of 16; the start
+// address field holds address >> 4 and shared memory ends below 2^18, so the sum never leaves the field).  One
+// thread issues every MMA of a CTA and, being alone in its warp, runs an instruction every few cycles: building
+// a descriptor from scratch for each MMA costs more than a small MMA takes, adding to a base does not.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+    const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+    return (desc & 0xffffffff00000000ull) | lo;
+}
 // Descriptor of an MN-major bf16 tile: rows are K indices, each row holds 64 contiguous MN elements (128
 // bytes), written by TMA with 128-byte swizzle.  8-row groups along K are 1024 bytes apart (stride byte
 // offset); the leading byte offset is the distance between 64-element blocks along MN (`mn_block_bytes`,
