@@ -72,6 +72,64 @@ rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ 
     dst[d + half] = forge::from_float<TCache>(x1);
 }
 
+template <typename T> struct Store4;
+template <> struct Store4<float> {
+    static __device__ __forceinline__ void put(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Store4<__nv_bfloat16> {
+    static __device__ __forceinline__ void put(__nv_bfloat16* p, const float (&v)[4]) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+};
+
+// The same for head sizes that are a multiple of 8: a thread takes four neighbouring pairs of one head (two
+// float4 loads, two 8- or 16-byte stores); a CTA takes kTokens tokens so that prompts do not launch one small
+// CTA per token and 128 pairs.  Needs the step's cos/sin table.
+constexpr int kRopeTokens = 4;
+template <typename TAct, typename TCache>
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ slot_mapping, TAct* __restrict__ q_out,
+                         TCache* __restrict__ kv_cache, int T, int NH, int NKV, int HD, int page_size, int rotary,
+                         const float2* __restrict__ table) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int half = HD >> 1, quads = half >> 2;                   // quads of pairs per head
+    const int per_token = (NH + 2 * NKV) * quads;
+    for (int i = threadIdx.x; i < kRopeTokens * per_token; i += blockDim.x) {
+        const int t = blockIdx.x * kRopeTokens + i / per_token;
+        if (t >= T) break;
+        const int wq = i % per_token, h = wq / quads, d = (wq % quads) * 4;
+        const float* row = qkv + (size_t)t * (NH + 2 * NKV) * HD + h * HD;
+        const float4 a = *reinterpret_cast<const float4*>(row + d), b = *reinterpret_cast<const float4*>(row + d + half);
+        float x0[4] = {a.x, a.y, a.z, a.w}, x1[4] = {b.x, b.y, b.z, b.w};
+        if (rotary && h < NH + NKV) {
+            const float4* cs = reinterpret_cast<const float4*>(table + (size_t)t * half + d);     // (c, s, c, s) x 2
+            const float4 cs01 = cs[0], cs23 = cs[1];
+            const float c[4] = {cs01.x, cs01.z, cs23.x, cs23.z}, sn[4] = {cs01.y, cs01.w, cs23.y, cs23.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float y0 = x0[j] * c[j] - x1[j] * sn[j], y1 = x0[j] * sn[j] + x1[j] * c[j];
+                x0[j] = y0;
+                x1[j] = y1;
+            }
+        }
+        if (h < NH) {
+            TAct* q = q_out + (size_t)t * NH * HD + h * HD;
+            Store4<TAct>::put(q + d, x0);
+            Store4<TAct>::put(q + d + half, x1);
+            continue;
+        }
+        const int slot = slot_mapping ? slot_mapping[t] : -1;
+        if (slot < 0) continue;
+        const int page = slot / page_size, off = slot % page_size;
+        const int is_v = h >= NH + NKV, kvh = h - NH - (is_v ? NKV : 0);
+        TCache* dst = kv_cache + (((size_t)page * 2 + is_v) * NKV + kvh) * page_size * HD + (size_t)off * HD;
+        Store4<TCache>::put(dst + d, x0);
+        Store4<TCache>::put(dst + d + half, x1);
+    }
+}
+
 }  // namespace
 
 // table: float [T, HD/2, 2] (cos, sin) for the step's tokens.
@@ -94,6 +152,13 @@ extern "C" int forge_rope_kv_write(const float* qkv, const int32_t* positions, c
                            T, NH, NKV, HD, page_size);
     if (T == 0) return FORGE_OK;
     cudaError_t e = cudaSuccess;
+    if ((HD % 8) == 0 && (table != nullptr || !rotary) && T >= kRopeTokens) {
+        FORGE_DISPATCH_DTYPE(dtype, TT,
+            e = forge::launch(rope_kv_write_vec_kernel<TT, TT>, dim3((T + kRopeTokens - 1) / kRopeTokens), dim3(256), 0, stream, 1,
+                              qkv, slot_mapping, (TT*)q_out, (TT*)kv_cache, T, NH, NKV, HD, page_size, rotary,
+                              reinterpret_cast<const float2*>(table)));
+        return forge::check_launch("rope_kv_write", e);
+    }
     FORGE_DISPATCH_DTYPE(dtype, TT,
         e = forge::launch(rope_kv_write_kernel<TT, TT>, dim3(T, ((NH + 2 * NKV) * (HD / 2) + 127) / 128), dim3(128), 0, stream, 1,
                           qkv, positions, slot_mapping, (TT*)q_out, (TT*)kv_cache, NH, NKV, HD, page_size, theta, rotary,
