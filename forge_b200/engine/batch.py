@@ -8,6 +8,7 @@ on the device: attention is the only kernel that looks at request boundaries.
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 
@@ -93,23 +94,39 @@ def layout_step(entries, manager):
 
 
 def build_step_batch(entries, manager, device, max_pages, status=None):
-    """Lays the step out (see ``layout_step``) and copies it to the device as one StepBatch."""
+    """Lays the step out (see ``layout_step``) and copies it to the device as one StepBatch: all integer
+    arrays travel in one buffer and one copy, the batch's tensors are views into it."""
     hs = layout_step(entries, manager)
-
-    def dev(lst):
-        return torch.tensor(lst, dtype=torch.int32, device=device)
-
-    groups = {}
+    T, S, R = len(hs.token_ids), len(entries), len(hs.rows)
+    for s, e in enumerate(entries):
+        for g in manager.groups:
+            if len(hs.tables[g][s]) > max_pages:
+                raise ValueError(f"request {e.req_id!r} holds {len(hs.tables[g][s])} pages, tables have room for {max_pages}")
+    parts = [hs.token_ids, hs.positions, hs.tok_req, hs.q_start, hs.context_before, hs.slots, hs.rows]
+    total = sum(len(p) for p in parts) + len(manager.groups) * (T + S * max_pages)
+    buf = np.empty(total, dtype=np.int32)
+    spans, off = [], 0
+    for p in parts:
+        buf[off:off + len(p)] = p
+        spans.append((off, len(p)))
+        off += len(p)
+    group_spans = {}
     for g in manager.groups:
-        table = torch.full((len(entries), max_pages), -1, dtype=torch.int32)
+        buf[off:off + T] = hs.slot_maps[g]
+        table = buf[off + T:off + T + S * max_pages].reshape(S, max_pages)
+        table.fill(-1)
         for s, t in enumerate(hs.tables[g]):
-            if len(t) > max_pages:
-                raise ValueError(f"request {entries[s].req_id!r} holds {len(t)} pages, tables have room for {max_pages}")
-            table[s, :len(t)] = torch.tensor(t, dtype=torch.int32)
-        groups[g] = GroupBatch(table.to(device), dev(hs.slot_maps[g]))
+            table[s, :len(t)] = t
+        group_spans[g] = (off, off + T)
+        off += T + S * max_pages
+    dev = torch.from_numpy(buf).to(device)
+
+    def view(i):
+        o, n = spans[i]
+        return dev[o:o + n]
+
+    groups = {g: GroupBatch(dev[t0:t0 + S * max_pages].view(S, max_pages), dev[s0:s0 + T]) for g, (s0, t0) in group_spans.items()}
     return StepBatch(
-        num_tokens=len(hs.token_ids), num_requests=len(entries), num_logits=len(hs.rows),
-        token_ids=dev(hs.token_ids), positions=dev(hs.positions), tok_req=dev(hs.tok_req), q_start=dev(hs.q_start),
-        context_before=dev(hs.context_before), slots=dev(hs.slots), logits_rows=dev(hs.rows) if hs.rows else None,
-        groups=groups, status=status, host_q_start=hs.q_start, host_context_before=hs.context_before,
-        host_slots=hs.slots)
+        num_tokens=T, num_requests=S, num_logits=R, token_ids=view(0), positions=view(1), tok_req=view(2), q_start=view(3),
+        context_before=view(4), slots=view(5), logits_rows=view(6) if R else None, groups=groups, status=status,
+        host_q_start=hs.q_start, host_context_before=hs.context_before, host_slots=hs.slots)

@@ -102,9 +102,9 @@ class ModelRunner:
             seen.add(e.req_id)
             if not e.tokens:
                 raise StepError(f"request {e.req_id!r} brings no tokens")
-            for t in e.tokens:
-                if not isinstance(t, int) or not 0 <= t < V:
-                    raise StepError(f"request {e.req_id!r}: token id {t!r} is outside [0, {V})")
+            if not set(map(type, e.tokens)) <= {int} or min(e.tokens) < 0 or max(e.tokens) >= V:
+                bad = next((t for t in e.tokens if type(t) is not int or not 0 <= t < V), e.tokens[0])
+                raise StepError(f"request {e.req_id!r}: token id {bad!r} is outside [0, {V})")
             if self.manager.num_tokens(e.req_id) + len(e.tokens) > limit:
                 raise StepError(f"request {e.req_id!r} would exceed the model's {limit} positions")
 
