@@ -45,7 +45,7 @@ struct GemmParams {
 template <int BN> struct Cfg {
     static constexpr int kStageBytes = (BM + BN) * BK * 2;
     static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes > 12 ? 12 : (kSmemLimit - 2048) / kStageBytes;
-    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers*/;
 };
 
@@ -894,7 +894,7 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
-// tile_n: 0 = choose; 16, 32, 64, 128, 256 = token-major tiles of that width; -1, -2, -4, -8 (M <= 64 only) =
+// tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; -1, -2, -4, -8 (M <= 64 only) =
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
@@ -960,11 +960,14 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         if (M <= BM) {
             bn = N >= 64 * g_num_sms ? 64 : (N >= 32 * g_num_sms ? 32 : 16);
         } else {
+            // A k-step of a [128 x BN] tile moves 2 * (4 KB + BN * 32 B) through shared memory (TMA writes it, the
+            // tensor core reads it) at 128 B per clock, against BN / 2 clocks of arithmetic: 64 + BN / 2 clocks per
+            // k-step, so wide tiles are cheaper per column; what a width wastes in the last wave is weighed against that.
             const long tm = (M + BM - 1) / BM;
             long best = -1;
-            for (int cand : {256, 128}) {
+            for (int cand : {256, 224, 192, 160, 128}) {
                 const long tiles = tm * ((N + cand - 1) / cand);
-                const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * cand;
+                const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * (64 + cand / 2);
                 if (best < 0 || cost < best) { best = cost; bn = cand; }
             }
         }
@@ -975,11 +978,14 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     GemmParams p{C, bias, M, N, K, epilogue, status};
     switch (bn) {
         case 256: return launch<256>(ta, tw, p, stream);
+        case 224: return launch<224>(ta, tw, p, stream);
+        case 192: return launch<192>(ta, tw, p, stream);
+        case 160: return launch<160>(ta, tw, p, stream);
         case 128: return launch<128>(ta, tw, p, stream);
         case 64: return launch<64>(ta, tw, p, stream);
         case 32: return launch<32>(ta, tw, p, stream);
         case 16: return launch<16>(ta, tw, p, stream);
-        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128 or 256, got %d", bn);
+        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224 or 256, got %d", bn);
     }
 }
 

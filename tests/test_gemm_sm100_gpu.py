@@ -24,7 +24,7 @@ SHAPES = [(128, 256, 64), (1, 48, 8), (7, 100, 72), (130, 257, 200), (300, 515, 
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("tile_n", [0, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 16, 32, 64, 128, 160, 192, 224, 256])
 def test_plain_product_every_tile_width(M, N, K, tile_n):
     k = _k()
     a, w = _rand(M, K), _rand(N, K, seed=1)
@@ -58,7 +58,7 @@ def test_many_tiles_per_cta_and_both_accumulators():
     k = _k()
     a, w = _rand(1536, 256), _rand(4096, 256, seed=1)
     ref = R.gemm_ref(a, w)
-    for tile_n in (128, 256):
+    for tile_n in (128, 160, 224, 256):
         got = k.gemm_sm100(a, w, tile_n=tile_n)
         assert (got - ref).abs().max() <= 2e-5 * ref.abs().max()
     k.check_kernel_status()
