@@ -42,6 +42,12 @@ def case(name):
     if name == "gemm_decode_down":           # 8 tokens x [2048, 5632], residual accumulate, K cut over a cluster
         x, w, r = _bf16(8, I), _bf16(H, I, scale=0.02), torch.zeros(8, H, device=DEV)
         return (lambda: gemm_sm100(x, w, accumulate_into=r)), w.numel() * 2, 2 * 8 * w.numel()
+    if name == "gemm_decode_lmhead":         # 8 tokens x [32000, 2048]: 250 row tiles, dealt out evenly (stream-K)
+        x, w = _bf16(8, H), _bf16(32000, H, scale=0.02)
+        return (lambda: gemm_sm100(x, w)), w.numel() * 2, 2 * 8 * w.numel()
+    if name == "gemm_prefill_qkv":           # 2048 tokens x [2560, 2048]: tiles of 128 x 160 fill two waves
+        x, w = _bf16(2048, H), _bf16((NH + 2 * NKV) * HD, H, scale=0.02)
+        return (lambda: gemm_sm100(x, w)), (x.numel() + w.numel()) * 2 + 2048 * w.shape[0] * 4, 2 * 2048 * w.numel()
     if name == "gemm_prefill_gateup":        # 2048 tokens x [11264, 2048], SwiGLU epilogue: 94.5 GFLOP
         x, w = _bf16(2048, H), _bf16(2 * I, H, scale=0.02)
         return (lambda: gemm_sm100(x, w, epilogue="swiglu")), (x.numel() + w.numel() + 2048 * I) * 2, 2 * 2048 * w.numel()
@@ -64,7 +70,8 @@ def case(name):
     if name == "attention_prefill_mma":      # the same through the mma.sync kernel, for comparison
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
-    raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_prefill_gateup "
+    raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
+                     "gemm_prefill_gateup "
                      "gemm_prefill_down attention_decode attention_decode_fused attention_prefill attention_prefill_mma")
 
 
