@@ -51,6 +51,75 @@ template <int BN> struct Cfg {
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
+// Applies the epilogue to 32 consecutive columns (n .. n+31) of output row m held in r (fp32 bits) and stores them.
+template <int BN>
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint32_t (&r)[32], int m, int n) {
+    if (m < p.M && n < p.N) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const int width = min(min(32, BN), p.N - n);
+        if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < width) v[i] += p.bias[n + i];
+        }
+        if (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) {
+            float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+            const bool acc = p.epilogue == EPI_ACCUM_F32;
+            if (width == 32 && (p.N & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    if (acc) {
+                        const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    *reinterpret_cast<float4*>(dst + i) = o;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) if (i < width) dst[i] = acc ? dst[i] + v[i] : v[i];
+            }
+        } else if (p.epilogue == EPI_STORE_BF16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
+            if (width == 32 && (p.N & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                    uint4 o;
+                    o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                    o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>(dst + i) = o;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(v[i]);
+            }
+        } else {   // EPI_SWIGLU_BF16: N is even, pairs never straddle a 32-column chunk
+            const int half_n = p.N >> 1;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * half_n + (n >> 1);
+            if (width == 32 && (half_n & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 8) {
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int q = 2 * (i + 2 * j);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(silu(v[q]) * v[q + 1], silu(v[q + 2]) * v[q + 3]);
+                        w4[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(dst + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(silu(v[2 * i]) * v[2 * i + 1]);
+            }
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -175,71 +244,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     for (int i = 0; i < 16; ++i) { r[i] = h[i]; r[i + 16] = 0; }
                 }
                 tmem_ld_wait();
-                const int n = n0 + c;
-                if (m < p.M && n < p.N) {
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                    const int width = min(min(32, BN), p.N - n);
-                    if (p.bias) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) if (i < width) v[i] += p.bias[n + i];
-                    }
-                    if (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) {
-                        float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
-                        const bool acc = p.epilogue == EPI_ACCUM_F32;
-                        if (width == 32 && (p.N & 3) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                                if (acc) {
-                                    const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *reinterpret_cast<float4*>(dst + i) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) if (i < width) dst[i] = acc ? dst[i] + v[i] : v[i];
-                        }
-                    } else if (p.epilogue == EPI_STORE_BF16) {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.N + n;
-                        if (width == 32 && (p.N & 7) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
-                                uint4 o;
-                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(dst + i) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) if (i < width) dst[i] = __float2bfloat16_rn(v[i]);
-                        }
-                    } else {   // EPI_SWIGLU_BF16: N is even, pairs never straddle a 32-column chunk
-                        const int half_n = p.N >> 1;
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * half_n + (n >> 1);
-                        if (width == 32 && (half_n & 7) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 8) {
-                                uint32_t w4[4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const int q = 2 * (i + 2 * j);
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(silu(v[q]) * v[q + 1], silu(v[q + 2]) * v[q + 3]);
-                                    w4[j] = *reinterpret_cast<uint32_t*>(&h);
-                                }
-                                *reinterpret_cast<uint4*>(dst + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(silu(v[2 * i]) * v[2 * i + 1]);
-                        }
-                    }
-                }
+                store_row_chunk<BN>(p, r, m, n0 + c);
             }
             tc_fence_before_sync();
             mbar_arrive(&acc_empty[a]);
@@ -251,6 +256,212 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Many rows, two CTAs on one tile (tcgen05 cta_group::2).
+//
+// A k-step of the single-CTA [128 x 256] tile moves 24 KB through an SM's shared memory (TMA writes 12 KB, the
+// tensor core reads them) at 128 B per clock: 188 clocks for 128 clocks of arithmetic.  Here the two CTAs of a
+// cluster share a [256 x 256] tile: CTA r stages rows r*128.. of A and rows r*128.. of W (half of the tile's N
+// side), 8 KB per k-step each, and ONE thread of the even CTA issues MMAs of M = 256, N = 256 that read both
+// CTAs' shared memory and accumulate rows r*128.. of the tile into CTA r's tensor memory.  Per SM that is
+// 16 KB per 128 clocks: the arithmetic is the bound again (measured: 125 clocks per MMA in the main loop).
+//   Barriers.  full[s] lives in the even CTA only: both CTAs' TMA loads complete their bytes on it (a
+// cta_group::2 load may signal its pair's barrier), the even CTA's producer arms it with both CTAs' byte count.
+// empty[s] and acc_full[a] exist in both CTAs and are arrived on by multicast commits.  acc_empty[a] lives in
+// the even CTA and collects the 256 epilogue threads of both.  Two accumulators of 256 columns fill the tensor
+// memory of each CTA, so the epilogue of one tile overlaps the MMAs of the next.
+//   G: k-blocks per stage and TMA instruction (through the 3D k-block views); G = 0: 2D maps, one k-block per
+// stage, for a K that is no multiple of 64.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+constexpr int kPairBN = 256;                                   // N of the pair's tile; each CTA stages half of it
+struct PairCfg {
+    static constexpr int kBlockBytes = (BM + kPairBN / 2) * BK * 2;         // one k-block per CTA: 32 KB
+    static constexpr int kRingBlocks = 6;                                   // 192 KB of stages, whatever their size
+    static constexpr int kSmemBytes = kRingBlocks * kBlockBytes + 1024 + 1024;
+    static constexpr int kTmemCols = 512;
+};
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// Tile loads into this CTA's shared memory whose bytes complete on `bar_cluster_addr`, a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs of the pair once all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+    using C = PairCfg;
+    constexpr int g = G > 0 ? G : 1;
+    constexpr int kStages = C::kRingBlocks / g, BNH = kPairBN / 2;
+    constexpr int kABytes = g * BM * BK * 2, kStageBytes = g * C::kBlockBytes;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;                         // [kStages][ g tiles of A | g tiles of this CTA's half of W ]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRingBlocks * C::kBlockBytes);
+    uint64_t* full = bars;                         // [kStages]  both CTAs' TMA -> the even CTA's MMA thread
+    uint64_t* empty = bars + kStages;              // [kStages]  MMA -> each CTA's TMA thread
+    uint64_t* acc_full = bars + 2 * kStages;       // [2]        MMA -> each CTA's epilogue
+    uint64_t* acc_empty = bars + 2 * kStages + 2;  // [2]        both CTAs' epilogues -> the even CTA's MMA thread
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles_n = (p.N + kPairBN - 1) / kPairBN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_groups = (num_kb + g - 1) / g;               // stages per tile; the last may hold fewer k-blocks
+
+    if (threadIdx.x == 0) {
+        *abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 256); }
+        mbar_fence_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                    // both CTAs' barriers exist before either signals across
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();                     // A, bias and C may come from (or still be read by) earlier kernels
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one per CTA)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * kPairBN + rank * BNH;
+                for (int gi = 0; gi < num_groups; ++gi, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort, p.status))) break;
+                    if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);   // k-blocks past K arrive as zeros
+                    const uint32_t bar = full0 + s * 8;
+                    uint8_t* a_dst = tiles + s * kStageBytes;
+                    if constexpr (G > 0) {
+                        tma_load_3d_pair(a_dst, &tmap_a, bar, 0, m0, gi * g);
+                        tma_load_3d_pair(a_dst + kABytes, &tmap_w, bar, 0, n0, gi * g);
+                    } else {
+                        tma_load_2d_pair(a_dst, &tmap_a, bar, gi * BK, m0);
+                        tma_load_2d_pair(a_dst + kABytes, &tmap_w, bar, gi * BK, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (the even CTA's)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * BM, kPairBN);
+            uint32_t it = 0;
+            bool ok = true;
+            int local = 0;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+                const int a = local & 1;
+                const uint32_t aph = (local >> 1) & 1;
+                if (!(ok = mbar_wait(&acc_empty[a], aph ^ 1, abort, p.status))) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + a * kPairBN;
+                for (int gi = 0; gi < num_groups; ++gi, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(&full[s], ph, abort, p.status))) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
+                    const uint64_t a_desc = umma_desc_k_sw128(a_addr), w_desc = umma_desc_k_sw128(a_addr + kABytes);
+                    const int here = min(g, num_kb - gi * g);
+#pragma unroll
+                    for (int j = 0; j < g; ++j) {
+                        if (j >= here) break;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            umma_bf16_pair(d_tmem, umma_desc_advance(a_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
+                                           umma_desc_advance(w_desc, j * (BNH * BK * 2) + k * UMMA_K * 2), idesc,
+                                           (j | k) != 0 || gi != 0);
+                    }
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[a]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5 of each CTA)
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+        bool ok = true;
+        int local = 0;
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+            const int a = local & 1;
+            const uint32_t aph = (local >> 1) & 1;
+            const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * kPairBN;
+            if (!(ok = mbar_wait(&acc_full[a], aph, abort, p.status))) break;
+            tc_fence_after_sync();
+            const int m = m0 + row_in_tile;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kPairBN;
+#pragma unroll 1
+            for (int c = 0; c < kPairBN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + c, r);
+                tmem_ld_wait();
+                store_row_chunk<kPairBN>(p, r, m, n0 + c);
+            }
+            tc_fence_before_sync();
+            mbar_arrive_cluster(acc_empty0 + a * 8);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                    // the pair's MMAs read both CTAs' shared memory: leave together
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
     }
 }
 
@@ -288,14 +499,6 @@ template <int NT> struct SkinnyCfg {                       // NT: token box (UMM
     static constexpr int smem_bytes(int stages, int group) { return stages * group * kBlockBytes + kPartialBytes + 1024 + 1024; }
 };
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float4 v;
@@ -777,6 +980,56 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cu
                                                              C::kSmemBytes, stream, 1, ta, tw, p));
 }
 
+// How many pairs of CTAs of the two-CTA kernel run at once (one CTA per SM, clusters of 2: 74 on B200).
+int resident_pairs() {
+    static int cached = 0;
+    if (cached == 0) {
+        cudaFuncSetAttribute(gemm_sm100_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
+        cudaFuncSetAttribute(gemm_sm100_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
+        cudaFuncSetAttribute(gemm_sm100_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 64);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_pair_kernel<2>, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = g_num_sms / 2;
+        }
+        cached = n;
+    }
+    return cached;
+}
+
+int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t stream) {
+    const int pairs = resident_pairs();                 // also sets the kernels' shared-memory limit
+    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + kPairBN - 1) / kPairBN);
+    const int grid = 2 * (tiles < pairs ? tiles : pairs);
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int group = p.K % BK != 0 ? 0 : (num_kb >= 2 ? 2 : 1);
+    CUtensorMap ta, tw;
+    const char* err = nullptr;
+    if (group > 0) {
+        if (!bf16_kblock_map(A, p.M, p.K, BM, group, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+        if (!bf16_kblock_map(W, p.N, p.K, kPairBN / 2, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+    } else {
+        if (!bf16_tile_map(A, p.M, p.K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+        if (!bf16_tile_map(W, p.N, p.K, kPairBN / 2, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+    }
+    cudaError_t e;
+    if (group == 2) e = forge::launch(gemm_sm100_pair_kernel<2>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
+    else if (group == 1) e = forge::launch(gemm_sm100_pair_kernel<1>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
+    else e = forge::launch(gemm_sm100_pair_kernel<0>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
+    return forge::check_launch("gemm_sm100 (two CTAs per tile)", e);
+}
+
 // k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps)
 int few_rows_group(int K, int kb_per, int max_group) {
     if (K % BK != 0) return 0;
@@ -894,7 +1147,8 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
-// tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; -1, -2, -4, -8 (M <= 64 only) =
+// tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; 512 (M > 128) = a pair
+// of CTAs on a [256 x 256] tile (cta_group::2); -1, -2, -4, -8 (M <= 64 only) =
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
@@ -970,7 +1224,15 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
                 const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * (64 + cand / 2);
                 if (best < 0 || cost < best) { best = cost; bn = cand; }
             }
+            // Two CTAs on a [256 x 256] tile halve the W bytes an SM stages: 128 clocks per k-step (arithmetic-bound).
+            const long pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + kPairBN - 1) / kPairBN), pairs = resident_pairs();
+            if (((pair_tiles + pairs - 1) / pairs) * 128 < best) bn = 512;
         }
+    }
+    if (bn == 512) {
+        if (M <= BM) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: the two-CTA tile is for more than %d rows, got %d", BM, M);
+        GemmParams p{C, bias, M, N, K, epilogue, status};
+        return launch_pair(A, W, p, stream);
     }
     CUtensorMap ta, tw;
     if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
@@ -985,7 +1247,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         case 64: return launch<64>(ta, tw, p, stream);
         case 32: return launch<32>(ta, tw, p, stream);
         case 16: return launch<16>(ta, tw, p, stream);
-        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224 or 256, got %d", bn);
+        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224, 256 or 512 (two CTAs on 256 x 256), got %d", bn);
     }
 }
 

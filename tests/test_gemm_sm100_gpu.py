@@ -64,6 +64,32 @@ def test_many_tiles_per_cta_and_both_accumulators():
     k.check_kernel_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (130, 257, 200), (300, 515, 1032), (2048, 2560, 2048), (1000, 384, 96),
+                                   (257, 130, 4104), (4608, 4608, 128)])
+def test_two_ctas_on_one_tile(M, N, K):
+    """The cta_group::2 kernel: a pair of CTAs on a [256 x 256] tile, every epilogue; row, column and reduction
+    tails; (4608, 4608): 324 tiles for 74 pairs, so every pair walks several tiles and both accumulators."""
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    ref = R.gemm_ref(a, w, bias)
+    tol = 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
+    got = k.gemm_sm100(a, w, bias=bias, tile_n=512)
+    assert (got - ref).abs().max() <= tol
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    got = k.gemm_sm100(a, w, bias=bias, accumulate_into=res.clone(), tile_n=512)
+    assert (got - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max()
+    got = k.gemm_sm100(a, w, bias=bias, epilogue="cast", tile_n=512)
+    assert (got.float() - ref).abs().max() <= 8e-3 * ref.abs().max()
+    if N % 2 == 0:
+        got = k.gemm_sm100(a, w, bias=bias, epilogue="swiglu", tile_n=512)
+        want = R.silu_mul_interleaved_ref(ref)
+        assert got.shape == (M, N // 2) and (got.float() - want).abs().max() <= 8e-3 * want.abs().max() + 1e-6
+    k.check_kernel_status()
+    with pytest.raises(k.KernelError, match="two-CTA"):
+        k.gemm_sm100(_rand(64, 64), _rand(128, 64), tile_n=512)
+
+
 @pytest.mark.parametrize("M", [1, 8, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
 @pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8, -100])
