@@ -1214,19 +1214,21 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         if (M <= BM) {
             bn = N >= 64 * g_num_sms ? 64 : (N >= 32 * g_num_sms ? 32 : 16);
         } else {
-            // A k-step of a [128 x BN] tile moves 2 * (4 KB + BN * 32 B) through shared memory (TMA writes it, the
-            // tensor core reads it) at 128 B per clock, against BN / 2 clocks of arithmetic: 64 + BN / 2 clocks per
-            // k-step, so wide tiles are cheaper per column; what a width wastes in the last wave is weighed against that.
-            const long tm = (M + BM - 1) / BM;
+            // A k-step (16 of K) of a [128 x BN] tile moves 2 * (4 KB + BN * 32 B) through shared memory (TMA writes
+            // it, the tensor core reads it) at 128 B per clock against BN / 2 clocks of arithmetic: 64 + BN / 2 clocks,
+            // so wide tiles are cheaper per column.  Two CTAs on a [256 x 256] tile stage half the W bytes per SM and
+            // run at the arithmetic's 128 clocks in their main loop; set-up, cluster hand-shakes and the two-SM
+            // scheduling make that about 150 in a whole kernel (fitted to measurements at 512, 2048 and 4096 rows).
+            // The epilogue of a CTA's last tile is not hidden behind a next tile: about 36 clocks per column.
+            const long tm = (M + BM - 1) / BM, ksteps = (K + UMMA_K - 1) / UMMA_K;
             long best = -1;
             for (int cand : {256, 224, 192, 160, 128}) {
                 const long tiles = tm * ((N + cand - 1) / cand);
-                const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * (64 + cand / 2);
+                const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * ksteps * (64 + cand / 2) + 36L * cand;
                 if (best < 0 || cost < best) { best = cost; bn = cand; }
             }
-            // Two CTAs on a [256 x 256] tile halve the W bytes an SM stages: 128 clocks per k-step (arithmetic-bound).
             const long pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + kPairBN - 1) / kPairBN), pairs = resident_pairs();
-            if (((pair_tiles + pairs - 1) / pairs) * 128 < best) bn = 512;
+            if (((pair_tiles + pairs - 1) / pairs) * ksteps * 150 + 36L * kPairBN < best) bn = 512;
         }
     }
     if (bn == 512) {
