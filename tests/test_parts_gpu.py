@@ -294,3 +294,178 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype,
         for rid in reqs:
             assert max_rel_err(got[rid], want[rid]) <= TOL[dtype], rid
         assert runner.manager.num_free_pages() == {g: runner.num_pages for g in groups}
+
+
+# ---------------------------------------------------------------------------------------------------
+# Two more toy parts, again defined here only: a feed-forward with a router, and another position encoding.
+
+def _interleaved_rope(x, positions, theta):
+    """Rotary encoding on neighbouring pairs (2d, 2d+1) instead of the half-split pairs; x [T, heads, HD]."""
+    T, _, hd = x.shape
+    d = torch.arange(hd // 2, dtype=x.dtype, device=x.device)
+    ang = positions.to(x.dtype)[:, None] * (1.0 / torch.pow(torch.tensor(float(theta), dtype=x.dtype, device=x.device), 2.0 * d / hd))
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    return torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1).reshape(x.shape)
+
+
+def _toy_part_classes():
+    from forge_b200.parts import Part
+    from forge_b200.weights import TensorSpec
+
+    class InterleavedRope(Part):
+        """A position encoding the framework does not have.  It meets the interface of the category: rotate q
+        and k, put k and v into the pages at slot_mapping (cache layout [pages, 2, kv heads, page, head]),
+        return q."""
+
+        def __init__(self, rt, head_dim, theta):
+            self.rt, self.head_dim, self.theta = rt, head_dim, theta
+
+        def encode_and_store(self, qkv, positions, slot_mapping, kv_cache, num_heads, num_kv_heads, page_size, batch=None):
+            T, hd = qkv.shape[0], self.head_dim
+            x = qkv.float().view(T, num_heads + 2 * num_kv_heads, hd)
+            q = _interleaved_rope(x[:, :num_heads], positions, self.theta)
+            if slot_mapping is not None and kv_cache is not None:
+                k = _interleaved_rope(x[:, num_heads:num_heads + num_kv_heads], positions, self.theta)
+                v = x[:, num_heads + num_kv_heads:]
+                page, off = (slot_mapping // page_size).long(), (slot_mapping % page_size).long()
+                kv_cache[page, 0, :, off, :] = k.to(kv_cache.dtype)
+                kv_cache[page, 1, :, off, :] = v.to(kv_cache.dtype)
+            return q.reshape(T, num_heads * hd).to(self.rt.dtype).contiguous()
+
+    class RoutedFeedForward(Part):
+        """residual += sum_e softmax(x . Wr^T)_e * W2_e . relu(W1_e . x): the router's logits and weights in
+        32-bit, every expert weighted (no hard choice, so the result is continuous in x)."""
+
+        def __init__(self, rt, hidden_size, expert_size, num_experts):
+            self.rt, self.h, self.f, self.e = rt, hidden_size, expert_size, num_experts
+
+        def tensor_specs(self):
+            specs = {"moe.router.weight": TensorSpec((self.e, self.h))}
+            for i in range(self.e):
+                specs[f"moe.experts.{i}.w1.weight"] = TensorSpec((self.f, self.h))
+                specs[f"moe.experts.{i}.w2.weight"] = TensorSpec((self.h, self.f))
+            return specs
+
+        def bind(self, tensors):
+            dev = self.rt.device
+            self.router = tensors["moe.router.weight"].to(device=dev, dtype=torch.float32)
+            self.w1 = [tensors[f"moe.experts.{i}.w1.weight"].to(device=dev, dtype=self.rt.dtype) for i in range(self.e)]
+            self.w2 = [tensors[f"moe.experts.{i}.w2.weight"].to(device=dev, dtype=self.rt.dtype) for i in range(self.e)]
+
+        def forward(self, x, residual):
+            gate = torch.softmax(x.float() @ self.router.t(), dim=-1)
+            for i in range(self.e):
+                y = torch.relu(x @ self.w1[i].t()) @ self.w2[i].t()
+                residual += gate[:, i:i + 1] * y.float()
+
+    return InterleavedRope, RoutedFeedForward
+
+
+@dataclass(frozen=True)
+class Toy2Config:
+    vocab_size: int = 61
+    hidden_size: int = 48
+    num_heads: int = 6
+    num_kv_heads: int = 2
+    head_dim: int = 16
+    expert_size: int = 24
+    num_experts: int = 3
+    intermediate_size: int = 72
+    eps: float = 1e-6
+    theta: float = 50.0
+    max_position_embeddings: int = 192
+
+    @classmethod
+    def from_dict(cls, d, architecture="Toy2ForCausalLM"):
+        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(asdict(self), architectures=["Toy2ForCausalLM"])
+
+    def plan(self):
+        from forge_b200.config import LayerSpec, ModelPlan, PartSpec
+        norm = PartSpec("rmsnorm", {"size": self.hidden_size, "eps": self.eps})
+
+        def attn(position):
+            return PartSpec("attention", {"hidden_size": self.hidden_size, "num_heads": self.num_heads,
+                                          "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "position": position})
+        norms = {"input": norm, "post_mixer": norm}
+        layers = [
+            LayerSpec("pre_norm", attn(PartSpec("toy_interleaved_rope", {"head_dim": self.head_dim, "theta": self.theta})),
+                      PartSpec("toy_routed", {"hidden_size": self.hidden_size, "expert_size": self.expert_size,
+                                              "num_experts": self.num_experts}), norms, "model.layers.0."),
+            LayerSpec("pre_norm", attn(PartSpec("rope", {"head_dim": self.head_dim, "theta": self.theta})),
+                      PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size}),
+                      norms, "model.layers.1."),
+        ]
+        return ModelPlan(hidden_size=self.hidden_size, vocab_size=self.vocab_size, max_positions=self.max_position_embeddings,
+                         embedding=PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}),
+                         final_norm=norm,
+                         lm_head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied": True}),
+                         layers=layers, schedule=[0, 1])
+
+
+def plain_toy2_logits(cfg, w, ids):
+    T, pos = len(ids), torch.arange(len(ids))
+    h = P.embedding(torch.tensor(ids), w["model.embed_tokens.weight"])
+    for layer, enc in ((0, _interleaved_rope), (1, P.rope)):
+        p = f"model.layers.{layer}."
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], cfg.eps)
+        q = enc(P.linear(x, w[p + "self_attn.q_proj.weight"]).view(T, cfg.num_heads, cfg.head_dim), pos, cfg.theta)
+        k = enc(P.linear(x, w[p + "self_attn.k_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim), pos, cfg.theta)
+        v = P.linear(x, w[p + "self_attn.v_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim)
+        h = h + P.linear(P.attention(q, k, v).reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+        x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg.eps)
+        if layer == 0:
+            gate = torch.softmax(P.linear(x, w[p + "moe.router.weight"]), dim=-1)
+            for e in range(cfg.num_experts):
+                y = P.linear(torch.relu(P.linear(x, w[p + f"moe.experts.{e}.w1.weight"])), w[p + f"moe.experts.{e}.w2.weight"])
+                h = h + gate[:, e:e + 1] * y
+        else:
+            h = h + P.swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg.eps), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_feed_forward_with_a_router_and_toy_position_encoding(dtype, tmp_path):
+    """A feed-forward with routing and a position encoding of another kind, registered from this file, in one
+    layer beside a stock layer; embeddings tied.  Whole, in changing portions and mixed with page reuse."""
+    import schedules
+    from forge_b200.config import register_architecture, unregister_architecture
+    from forge_b200.engine import ModelRunner, StepEntry
+    from forge_b200.parts import register_part, unregister_part
+    from forge_b200.weights import write_random_model
+    from plain.safetensors_reader import read_safetensors
+    rope_cls, ffn_cls = _toy_part_classes()
+    register_part("position", "toy_interleaved_rope", rope_cls)
+    register_part("feed_forward", "toy_routed", ffn_cls)
+    register_architecture("Toy2ForCausalLM", Toy2Config)
+    try:
+        cfg = Toy2Config()
+        d = write_random_model(cfg, str(tmp_path / "toy2"), seed=7, std=0.12, embed_std=0.6, norm_std=0.15)
+        w = {k: torch.from_numpy(v).double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
+        assert "model.layers.0.moe.experts.2.w2.weight" in w and "lm_head.weight" not in w
+        reqs = {f"t{i}": random_tokens(n, cfg.vocab_size, seed=50 + i) for i, n in enumerate([37, 70, 19, 52])}
+        want = {rid: plain_toy2_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
+        runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=200, max_requests=3, cuda_graphs=False)
+        for steps in (schedules.whole(reqs), schedules.changing_portions(reqs), schedules.mixed(reqs, max_live=3)):
+            got = {rid: torch.zeros(len(t), cfg.vocab_size) for rid, t in reqs.items()}
+            for entries, end in steps:
+                for rid, p, n in entries:
+                    if not runner.is_live(rid):
+                        runner.admit(rid)
+                lg = runner.step([StepEntry(rid, reqs[rid][p:p + n], list(range(n))) for rid, p, n in entries]).cpu()
+                o = 0
+                for rid, p, n in entries:
+                    got[rid][p:p + n] = lg[o:o + n]
+                    o += n
+                for rid in end:
+                    runner.release(rid)
+                runner.manager.check()
+            for rid in reqs:
+                assert max_rel_err(got[rid], want[rid]) <= TOL[dtype], rid
+    finally:
+        unregister_part("position", "toy_interleaved_rope")
+        unregister_part("feed_forward", "toy_routed")
+        unregister_architecture("Toy2ForCausalLM")
