@@ -485,6 +485,12 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 // [rows, K] is described to TMA as {64 columns, rows, K / 64 k-blocks} (k-block stride 128 bytes), and a box
 // {64, 128, g} lands in shared memory as g standard 128-byte-swizzled [128 x 64] tiles one after the other.
 // That needs K % 64 == 0; other K take the plain 2D map with one k-block per stage.
+// Two threads issue the MMAs (warps 1 and 6), each into an accumulator of its own: one thread gets a
+// tcgen05.mma out about every 50 clocks, and an M128 N16 K16 MMA that reads its M operand from shared memory
+// keeps the tensor pipe busy for about 39 (measured: 54.8 clocks per MMA with one issuing thread, 2 x 1024 MMAs
+// in 78.4 clocks per pair with two).  The k-blocks of a stage alternate between the two; the epilogue adds the
+// two accumulators (always in the same order).
+constexpr int kSkinnyThreads = 224;
 template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
     static constexpr int kBlockBytes = BM * BK * 2 + NT * BK * 2;      // one k-block of W and of the tokens
     static constexpr int kPartialBytes = NT * BM * 4;
@@ -494,7 +500,7 @@ template <int NT> struct SkinnyCfg {                       // NT: token box (UMM
         const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * kBlockBytes);
         return fit > kMaxStages ? kMaxStages : fit;
     }
-    static constexpr int kTmemCols = NT < 32 ? 32 : NT;
+    static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;      // two accumulators, one per issuing thread
     // a CTA takes only as many stages as it has work for, so that CTAs of the next kernel fit beside it
     static constexpr int smem_bytes(int stages, int group) { return stages * group * kBlockBytes + kPartialBytes + 1024 + 1024; }
 };
@@ -509,7 +515,7 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                          const GemmParams p, const int ksplit, const int kStages, const int group) {
     // group > 0: the maps are the 3D k-block views and a stage holds `group` k-blocks; group == 0: 2D maps,
@@ -543,8 +549,8 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
     if (threadIdx.x == 0) {
         *abort = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&reuse[s], 1); }
-        mbar_init(acc_full, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&reuse[s], 2); }
+        mbar_init(acc_full, 2);
         mbar_fence_init();
         prefetch_tensormap(&tmap_w);
         prefetch_tensormap(&tmap_x);
@@ -557,6 +563,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const bool two_acc = g >= 2 && my_kb >= 2;           // the second issuing thread has k-blocks of its own
     forge::pdl_launch_dependents();
 
     if (warp == 0) {
@@ -588,10 +595,13 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 load_x(i, s);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 6) {
         if (lane == 0) {
+            // issuer 0 (warp 1) takes k-blocks 0 and 2 of every group, issuer 1 (warp 6) k-blocks 1 and 3
+            const int who = warp == 1 ? 0 : 1;
+            const uint32_t d_tmem = tmem_base + who * NT;
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, NT);
-            bool ok = true;
+            bool ok = true, fresh = true;
             for (int i = 0; i < my_groups && ok; ++i) {
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
@@ -600,15 +610,16 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 const uint64_t x_desc = umma_desc_k_sw128(smem_u32(x_tiles + s * x_bytes));
                 const int here = min(g, my_kb - i * g);            // k-blocks of this group inside my range
 #pragma unroll
-                for (int j = 0; j < C::kMaxGroup; ++j) {
+                for (int jj = 0; jj < C::kMaxGroup / 2; ++jj) {
+                    const int j = 2 * jj + who;
                     if (j >= here) break;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(tmem_base, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
-                                  umma_desc_advance(x_desc, j * (NT * BK * 2) + k * UMMA_K * 2), idesc,
-                                  (j | k) != 0 || i != 0);
+                        umma_bf16(d_tmem, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
+                                  umma_desc_advance(x_desc, j * (NT * BK * 2) + k * UMMA_K * 2), idesc, !(fresh && k == 0));
+                    fresh = false;
                 }
-                umma_commit(&reuse[s]);
+                umma_commit(&reuse[s]);           // one of the two arrivals that free the stage
             }
             if (ok && my_kb > 0) umma_commit(acc_full);
         }
@@ -620,6 +631,19 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (my_kb > 0) ok = mbar_wait(acc_full, 0, abort, p.status);
         tc_fence_after_sync();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        // 16 tokens of this thread's row: the first issuer's accumulator plus, if it had work, the second's
+        auto load_acc = [&](int c, uint32_t (&r)[16]) {
+            tmem_ld_32x32b_x16(t_row + c, r);
+            if (two_acc) {
+                uint32_t r2[16];
+                tmem_ld_32x32b_x16(t_row + NT + c, r2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+            } else {
+                tmem_ld_wait();
+            }
+        };
         if (ksplit == 1) {
             // the whole reduction happened in this CTA: straight from tensor memory to C.  A thread holds
             // one weight row n for all tokens, so for each token a warp writes 32 consecutive columns.
@@ -629,8 +653,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
                 for (int c = 0; c < NT; c += 16) {
                     uint32_t r[16];
-                    tmem_ld_32x32b_x16(t_row + c, r);
-                    tmem_ld_wait();
+                    load_acc(c, r);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int m = c + i;
@@ -657,8 +680,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
             for (int c = 0; c < NT; c += 16) {
                 uint32_t r[16];
-                tmem_ld_32x32b_x16(t_row + c, r);
-                tmem_ld_wait();
+                load_acc(c, r);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) partial[(c + i) * BM + n_local] = __uint_as_float(r[i]);
             }
@@ -670,7 +692,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncwarp();
     cluster_sync_all();                       // every CTA's partial is in place and visible
 
-    if (warp >= 2 && ksplit > 1) {
+    if (warp >= 2 && warp < 6 && ksplit > 1) {
         // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order, four
         // adjacent rows (16 bytes of each peer's shared memory) per thread
         const int rows_per = BM / ksplit;                  // 16, 32 or 64
@@ -1062,7 +1084,7 @@ int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit,
         if (!bf16_tile_map(A, p.M, p.K, NT, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     }
     return forge::check_launch("gemm_sm100 (few rows)",
-                               forge::launch(gemm_sm100_skinny_kernel<NT>, dim3(tiles_n * ksplit), dim3(kThreads),
+                               forge::launch(gemm_sm100_skinny_kernel<NT>, dim3(tiles_n * ksplit), dim3(kSkinnyThreads),
                                              C::smem_bytes(stages, g), stream, ksplit, tw, tx, p, ksplit, stages, group));
 }
 
@@ -1113,7 +1135,7 @@ int max_resident_ctas(int ks) {
         cudaFuncSetAttribute(gemm_sm100_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ks * 64);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(kSkinnyThreads);
         cfg.dynamicSmemBytes = kSmemLimit;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
