@@ -564,6 +564,10 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const bool two_acc = g >= 2 && my_kb >= 2;           // the second issuing thread has k-blocks of its own
+    // An unsplit tile with few tokens and an fp32 result goes straight from tensor memory to C; every other case
+    // passes through `partial` in shared memory, where a thread then holds four neighbouring features of a token
+    // (vector stores, gate and up side by side) instead of one feature of every token.
+    const bool direct = ksplit == 1 && p.epilogue <= EPI_ACCUM_F32 && p.M <= 16;
     forge::pdl_launch_dependents();
 
     if (warp == 0) {
@@ -644,7 +648,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 tmem_ld_wait();
             }
         };
-        if (ksplit == 1) {
+        if (direct) {
             // the whole reduction happened in this CTA: straight from tensor memory to C.  A thread holds
             // one weight row n for all tokens, so for each token a warp writes 32 consecutive columns.
             const int n = n0 + n_local;
@@ -692,7 +696,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncwarp();
     cluster_sync_all();                       // every CTA's partial is in place and visible
 
-    if (warp >= 2 && warp < 6 && ksplit > 1) {
+    if (warp >= 2 && warp < 6 && !direct) {
         // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order, four
         // adjacent rows (16 bytes of each peer's shared memory) per thread
         const int rows_per = BM / ksplit;                  // 16, 32 or 64
