@@ -8,7 +8,7 @@
 
 namespace {
 
-constexpr int kNormThreads = 256;
+constexpr int kNormThreads = 128;
 
 template <typename TOut> struct Pack4;
 template <> struct Pack4<float> {
