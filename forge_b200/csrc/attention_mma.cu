@@ -25,6 +25,13 @@
 namespace {
 
 constexpr int HD = FORGE_ATT_HD;
+
+// 2^x by the special-function unit (2 ulp, ex2(-inf) = 0); the weights are rounded to bfloat16 right after
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 constexpr int BQ = 64;
 constexpr int LD = HD + 8;                    // padded row length in shared memory (bf16 elements)
 constexpr int CPR = HD / 8;                   // 16-byte chunks per row
@@ -230,15 +237,15 @@ paged_attention_mma_kernel(const AttnParams p) {
                 mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
                 // a row that has seen no visible key yet keeps max -inf: use 0 as the reference so exp2 gives 0
                 const float ref_a = mx_a == -INFINITY ? 0.f : mx_a, ref_b = mx_b == -INFINITY ? 0.f : mx_b;
-                const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+                const float alpha_a = ex2_approx(m_a - ref_a), alpha_b = ex2_approx(m_b - ref_b);
                 m_a = mx_a;
                 m_b = mx_b;
                 float sum_a = 0.f, sum_b = 0.f;
                 uint32_t pfrag[BKV / 16][4];
 #pragma unroll
                 for (int i = 0; i < BKV / 8; ++i) {
-                    const float p0 = exp2f(sc[i][0] - ref_a), p1 = exp2f(sc[i][1] - ref_a);
-                    const float p2 = exp2f(sc[i][2] - ref_b), p3 = exp2f(sc[i][3] - ref_b);
+                    const float p0 = ex2_approx(sc[i][0] - ref_a), p1 = ex2_approx(sc[i][1] - ref_a);
+                    const float p2 = ex2_approx(sc[i][2] - ref_b), p3 = ex2_approx(sc[i][3] - ref_b);
                     sum_a += p0 + p1;
                     sum_b += p2 + p3;
                     pfrag[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -518,15 +525,15 @@ decode_attention_fused_kernel(const DecodeParams p) {
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
         const float ref_a = mx_a == -INFINITY ? 0.f : mx_a, ref_b = mx_b == -INFINITY ? 0.f : mx_b;
-        const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+        const float alpha_a = ex2_approx(m_a - ref_a), alpha_b = ex2_approx(m_b - ref_b);
         m_a = mx_a;
         m_b = mx_b;
         float sum_a = 0.f, sum_b = 0.f;
         uint32_t pfrag[DKV / 16][4];
 #pragma unroll
         for (int i = 0; i < DKV / 8; ++i) {
-            const float p0 = exp2f(sc[i][0] - ref_a), p1 = exp2f(sc[i][1] - ref_a);
-            const float p2 = exp2f(sc[i][2] - ref_b), p3 = exp2f(sc[i][3] - ref_b);
+            const float p0 = ex2_approx(sc[i][0] - ref_a), p1 = ex2_approx(sc[i][1] - ref_a);
+            const float p2 = ex2_approx(sc[i][2] - ref_b), p3 = ex2_approx(sc[i][3] - ref_b);
             sum_a += p0 + p1;
             sum_b += p2 + p3;
             pfrag[i >> 1][(i & 1) * 2 + 0] = pack_bf16(p0, p1);
