@@ -380,19 +380,41 @@ struct DecodeParams {
     const int32_t* slot_mapping;  // [S] page * page_size + offset of the new token
     int NH, NKV, page_size, max_pages, window, rotary;
     float theta, scale_log2;
+    int ksplit;                   // CTAs of a cluster that share one (request, kv head) and deal its key tiles out
 };
 
 constexpr int DKV = 32;           // keys per tile
 
-template <int NWARPS>
+__device__ __forceinline__ uint32_t att_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void att_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float att_ld_peer(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int NWARPS, bool CLUSTER>
 __global__ void __launch_bounds__(NWARPS * 32)
 decode_attention_fused_kernel(const DecodeParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][LD]  (G heads, zero-padded)
     __nv_bfloat16* kvs = qs + 16 * LD;                                   // [NWARPS][2 buffers][K | V][DKV][LD]
     forge::pdl_launch_dependents();
-    const int s = blockIdx.x, kvh = blockIdx.y;
+    // ksplit CTAs (a cluster) share a (request, kv head): the key tiles go round all their warps, each CTA merges
+    // its warps' results, and CTA 0 of the cluster merges the CTAs' through distributed shared memory.
+    const int KS = CLUSTER ? p.ksplit : 1;             // without a cluster everything below folds to the one-CTA form
+    const int rank = CLUSTER ? static_cast<int>(att_cluster_rank()) : 0;
+    const int s = blockIdx.x / KS, kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int vwarp = rank * NWARPS + warp, vwarps = NWARPS * KS;        // this warp among all warps of the cluster
     const int G = p.NH / p.NKV;
     // The step's positions, slots and block tables were written before its first kernel started, and the keys
     // and values of earlier positions in earlier steps: all of that may be read before the dependency wait,
@@ -436,11 +458,13 @@ decode_attention_fused_kernel(const DecodeParams p) {
     // new token is read after this kernel has written the token's key and value)
     int issued = 0;                                                      // tiles of this warp requested so far
     for (; issued < 2; ++issued) {
-        const int t = t_begin + warp + issued * NWARPS;
+        const int t = t_begin + vwarp + issued * vwarps;
         if (t >= t_end - 1) break;
         load_tile(issued, t);
         cp_async_commit();
     }
+    // the CTA whose warp gets the tile with the new token is the one that writes the token's key and value
+    const bool writes_kv = ((t_end - 1 - t_begin) % vwarps) / NWARPS == rank;
     forge::pdl_wait();
 
     // 1. rotate q (G heads) and k (one head), copy v; q to shared memory, k and v to the cache
@@ -461,7 +485,7 @@ decode_attention_fused_kernel(const DecodeParams p) {
         if (h < G) {
             qs[h * LD + d] = __float2bfloat16_rn(x0);
             qs[h * LD + d + half] = __float2bfloat16_rn(x1);
-        } else {
+        } else if (writes_kv) {
             __nv_bfloat16* dst = page_base + (h == G ? 0 : (size_t)p.NKV * p.page_size * HD);
             dst[d] = __float2bfloat16_rn(x0);
             dst[d + half] = __float2bfloat16_rn(x1);
@@ -479,11 +503,11 @@ decode_attention_fused_kernel(const DecodeParams p) {
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     int n_done = 0;
-    for (int t = t_begin + warp; t < t_end; t += NWARPS, ++n_done) {
+    for (int t = t_begin + vwarp; t < t_end; t += vwarps, ++n_done) {
         const int buf = n_done & 1;
         // tile n_done and, if there is one, the tile after it are on their way before this one is waited for
-        for (; issued < n_done + 2 && t_begin + warp + issued * NWARPS < t_end; ++issued) {
-            load_tile(issued & 1, t_begin + warp + issued * NWARPS);
+        for (; issued < n_done + 2 && t_begin + vwarp + issued * vwarps < t_end; ++issued) {
+            load_tile(issued & 1, t_begin + vwarp + issued * vwarps);
             cp_async_commit();
         }
         if (issued == n_done + 2) cp_async_wait<1>(); else cp_async_wait<0>();
@@ -580,6 +604,8 @@ decode_attention_fused_kernel(const DecodeParams p) {
         }
     }
     __syncthreads();
+    float* cta_o = ml + NWARPS * 16 * 2;                                 // [16][HD] this CTA's un-normalised output
+    float* cta_ml = cta_o + 16 * HD;                                     // [16][2]  its maximum and sum
     for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
         const int r = i / HD, d = i % HD;
         float M = -INFINITY;
@@ -593,7 +619,32 @@ decode_attention_fused_kernel(const DecodeParams p) {
             L += wt * ml[(w * 16 + r) * 2 + 1];
             acc += wt * mo[((size_t)w * 16 + r) * HD + d];
         }
-        p.out[(size_t)s * p.NH * HD + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        if (!CLUSTER) {
+            p.out[(size_t)s * p.NH * HD + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            cta_o[r * HD + d] = acc;
+            if (d == 0) { cta_ml[r * 2] = M; cta_ml[r * 2 + 1] = L; }
+        }
+    }
+    if (CLUSTER) {
+        // 4. the cluster's CTAs, in rank order, by CTA 0
+        att_cluster_sync();
+        if (rank == 0) {
+            for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+                const int r = i / HD, d = i % HD;
+                float M = -INFINITY;
+                for (int q = 0; q < KS; ++q) M = fmaxf(M, att_ld_peer(cta_ml + r * 2, q));
+                float L = 0.f, acc = 0.f;
+                for (int q = 0; q < KS; ++q) {
+                    const float mq = att_ld_peer(cta_ml + r * 2, q);
+                    const float wt = mq == -INFINITY ? 0.f : exp2f(mq - M);
+                    L += wt * att_ld_peer(cta_ml + r * 2 + 1, q);
+                    acc += wt * att_ld_peer(cta_o + r * HD + d, q);
+                }
+                p.out[(size_t)s * p.NH * HD + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            }
+        }
+        att_cluster_sync();                  // nobody leaves while CTA 0 may still read its shared memory
     }
 }
 
@@ -701,14 +752,16 @@ extern "C" int forge_paged_attention_mma_static(const void* q, const void* kv, v
 extern "C" int forge_decode_attention_fused(const float* qkv, void* kv, void* out, const int32_t* block_table,
                                             const int32_t* positions, const int32_t* slot_mapping, int S, int NH, int NKV,
                                             int head_dim, int page_size, int max_pages, int window, int rotary,
-                                            float theta, float scale, cudaStream_t stream) {
+                                            float theta, float scale, int max_context, cudaStream_t stream) {
+    // max_context: an upper bound of the requests' cached tokens + 1 (0: unknown); it only steers how many CTAs
+    // share a request's keys
     if (head_dim != HD) return forge::fail(FORGE_ERR_UNSUPPORTED, "this attention library was built for head_dim %d, got %d", HD, head_dim);
     if (S < 0 || NH <= 0 || NKV <= 0 || NH % NKV != 0 || page_size <= 0 || max_pages <= 0 || NKV > 65535)
         return forge::fail(FORGE_ERR_ARG, "decode_attention_fused: bad sizes S=%d NH=%d NKV=%d page=%d", S, NH, NKV, page_size);
     if (NH / NKV > 16) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_fused: %d query heads per kv head (at most 16)", NH / NKV);
     if (S == 0) return FORGE_OK;
     DecodeParams p{qkv, (__nv_bfloat16*)kv, (__nv_bfloat16*)out, block_table, positions, slot_mapping, NH, NKV, page_size,
-                   max_pages, window, rotary, theta, scale * 1.4426950408889634f};
+                   max_pages, window, rotary, theta, scale * 1.4426950408889634f, 1};
     // eight warps while the CTAs are few (short latency per request), four when there are CTAs enough to fill the SMs
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
@@ -718,17 +771,29 @@ extern "C" int forge_decode_attention_fused(const float* qkv, void* kv, void* ou
     if (need4 > kLimit) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_fused: head_dim %d needs %d bytes of shared memory", HD, need4);
     const int warps = ((long)S * NKV <= sms && need8 <= kLimit) ? 8 : 4;
     const int smem = warps == 8 ? need8 : need4;
+    // while SMs are idle, 2 or 4 CTAs (a cluster) share a request's keys, as long as every warp keeps four tiles:
+    // the cluster's hand-shakes cost about 1.4 us, which two tiles per warp do not pay back (measured at 8
+    // requests: 640 cached tokens 0.837 -> 0.868 ms per step with 2 CTAs, 6,000 tokens 1.72 -> 1.10 ms with 4)
+    // (a single request, 4 CTAs, gains from 4-way splitting already at 1,500 tokens: 0.88 -> 0.82 ms; below 64
+    // tiles nothing gains)
+    if (warps == 8 && max_context > 0) {
+        const long tiles = (max_context + DKV - 1) / DKV, keep = (long)S * NKV >= 16 ? 4 : 2;
+        while (tiles >= 64 && p.ksplit < 4 && (long)S * NKV * p.ksplit * 2 <= sms && tiles >= keep * warps * p.ksplit * 2) p.ksplit *= 2;
+    }
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, need4);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, need4);
         if (e == cudaSuccess && need8 <= kLimit)
-            e = cudaFuncSetAttribute(decode_attention_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, need8);
+            e = cudaFuncSetAttribute(decode_attention_fused_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, need8);
+        if (e == cudaSuccess && need8 <= kLimit)
+            e = cudaFuncSetAttribute(decode_attention_fused_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, need8);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "decode_attention_fused: %s", cudaGetErrorString(e));
         configured = true;
     }
-    cudaError_t le = warps == 8
-        ? forge::launch(decode_attention_fused_kernel<8>, dim3(S, NKV), dim3(256), smem, stream, 1, p)
-        : forge::launch(decode_attention_fused_kernel<4>, dim3(S, NKV), dim3(128), smem, stream, 1, p);
+    cudaError_t le;
+    if (p.ksplit > 1) le = forge::launch(decode_attention_fused_kernel<8, true>, dim3(S * p.ksplit, NKV), dim3(256), smem, stream, p.ksplit, p);
+    else if (warps == 8) le = forge::launch(decode_attention_fused_kernel<8, false>, dim3(S, NKV), dim3(256), smem, stream, 1, p);
+    else le = forge::launch(decode_attention_fused_kernel<4, false>, dim3(S, NKV), dim3(128), smem, stream, 1, p);
     return forge::check_launch("decode_attention_fused", le);
 }
 

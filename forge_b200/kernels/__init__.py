@@ -48,7 +48,7 @@ _SIGNATURES = {
     },
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
-        "forge_decode_attention_fused": [_P] * 6 + [_I] * 8 + [_F, _F, _P],
+        "forge_decode_attention_fused": [_P] * 6 + [_I] * 8 + [_F, _F, _I, _P],
     },
     "attention_sm100": {
         "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
@@ -416,16 +416,18 @@ def decode_attention_fused_supports(dtype, head_dim, group, num_requests, n_kv_h
     sliced kernel (keys spread over many CTAs) is the better choice."""
     if not (_TENSOR_CORE_ATTENTION and dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128 and group <= 16):
         return False
-    # measured (22 layers, 4 kv heads): with 4 or 32 CTAs the sliced kernel wins from about 2,500 cached tokens on
-    # (8 requests x 3,000: 1.16 against 1.23 ms per step; x 6,000: 1.26 against 1.72); with 128 CTAs this kernel
-    # still wins at 3,000
-    return not (num_requests * n_kv_heads < 64 and max_context > 2048)
+    # with few requests the kernel spreads a request's keys over a cluster of up to 4 CTAs; measured (22 layers, 4 kv
+    # heads, 8 requests x 6,000 cached tokens) 1.10 ms per step against 1.26 for the sliced kernel + merge.  Beyond
+    # 16k cached tokens with a handful of CTAs the sliced kernel's many CTAs are the better choice again.
+    return not (num_requests * n_kv_heads < 64 and max_context > 16384)
 
 
 def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim, page_size,
-                           theta, rotary=True, window=0, scale=None, out=None):
+                           theta, rotary=True, window=0, scale=None, out=None, max_context=0):
     """qkv fp32 [S,(NH+2NKV)*HD], one new token per request: rotates q and k (``rotary``), writes k and v into
-    the cache at ``slot_mapping`` and returns the attention output bf16 [S, NH*HD], all in one kernel."""
+    the cache at ``slot_mapping`` and returns the attention output bf16 [S, NH*HD], all in one kernel.
+    ``max_context``: an upper bound of any request's cached tokens + 1, if known: with few requests and many keys
+    the kernel then spreads a request's keys over 2 or 4 CTAs."""
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
     S = qkv.shape[0]
     if out is None:
@@ -435,7 +437,8 @@ def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, 
         _need(qkv, "qkv", torch.float32, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
         _need(block_table, "block_table", torch.int32, 2), _need(positions, "positions", torch.int32),
         _need(slot_mapping, "slot_mapping", torch.int32), S, n_heads, n_kv_heads, head_dim, page_size, block_table.shape[1],
-        int(window or 0), 1 if rotary else 0, float(theta), float(scale), _stream()), "decode_attention_fused")
+        int(window or 0), 1 if rotary else 0, float(theta), float(scale), int(max_context or 0), _stream()),
+        "decode_attention_fused")
     return out
 
 

@@ -69,7 +69,8 @@ class GQAAttention(Part):
             o = kernels.decode_attention_fused(qkv, cache.kv, g.block_table, batch.positions, g.slot_mapping,
                                                self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
                                                self.position.theta, rotary=self.position.rotary, window=self.window,
-                                               scale=self.scale)
+                                               scale=self.scale,
+                                               max_context=getattr(batch, "max_context", None) or max(batch.host_context_before) + 1)
             self.o.forward(o, accumulate_into=residual)
             return
         slots = g.slot_mapping if cache.writable else None

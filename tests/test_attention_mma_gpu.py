@@ -103,8 +103,10 @@ def test_decode_step_in_one_kernel(nh, nkv, hd, ps, window, rotary):
         q_ref, cache_ref = R.rope_kv_write_ref(qkv, positions, slots, cache, nh, nkv, hd, ps, theta, rotary)
         cache_ref = cache_ref.to(torch.bfloat16)                  # the engine's cache holds bf16
         ref = R.paged_attention_ref(q_ref.to(torch.bfloat16), cache_ref, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
-        work = cache.clone()
-        got = k.decode_attention_fused(qkv, work, group.block_table, positions, slots, nh, nkv, hd, ps, theta,
-                                       rotary=rotary, window=window).float()
-        assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
-        assert (work.float() - cache_ref.float()).abs().max() <= 1e-2 * cache_ref.float().abs().max()   # k, v landed in their slots
+        # max_context steers how many CTAs share a request's keys (1, 2 or 4): unknown, the real bound, a huge one
+        for max_context in (0, max(ctxs) + 1, 100000):
+            work = cache.clone()
+            got = k.decode_attention_fused(qkv, work, group.block_table, positions, slots, nh, nkv, hd, ps, theta,
+                                           rotary=rotary, window=window, max_context=max_context).float()
+            assert (got - ref).abs().max() <= 1e-2 * ref.abs().max(), max_context
+            assert (work.float() - cache_ref.float()).abs().max() <= 1e-2 * cache_ref.float().abs().max()   # k, v landed in their slots
