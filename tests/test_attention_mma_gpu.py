@@ -93,7 +93,7 @@ def test_decode_step_in_one_kernel(nh, nkv, hd, ps, window, rotary):
     and many requests (8 or 4 warps per CTA)."""
     from forge_b200 import kernels as k
     theta = 5e5
-    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 300, 1000], [7] * 70 + [129]):
+    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 300, 1000], [7] * 70 + [129], [2500, 3100]):     # the last: many tiles per warp, 4 CTAs per request
         reqs = [(c, 1) for c in ctxs]
         q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=4)
         S = len(reqs)
