@@ -1238,7 +1238,13 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         // few rows (decode): narrow tiles so that many SMs stream W; many rows: the widest tile whose tile
         // count wastes the least of the last wave
         if (M <= BM) {
-            bn = N >= 64 * g_num_sms ? 64 : (N >= 32 * g_num_sms ? 32 : 16);
+            // 65..128 rows: one row tile, so the column tiles alone must spread over the SMs; the narrowest width
+            // that leaves at most ~0.6 tiles per SM (measured at 96 and 128 rows: 32 for N = 2048 and 2560, 128 for
+            // N = 11264 beat 16 and 64 by 10-40 %)
+            bn = 256;
+            for (int cand : {16, 32, 64, 128}) {
+                if ((N + cand - 1) / cand <= (g_num_sms * 6) / 10) { bn = cand; break; }
+            }
         } else {
             // A k-step (16 of K) of a [128 x BN] tile moves 2 * (4 KB + BN * 32 B) through shared memory (TMA writes
             // it, the tensor core reads it) at 128 B per clock against BN / 2 clocks of arithmetic: 64 + BN / 2 clocks,
