@@ -494,7 +494,7 @@ constexpr int kSkinnyThreads = 224;
 template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
     static constexpr int kBlockBytes = BM * BK * 2 + NT * BK * 2;      // one k-block of W and of the tokens
     static constexpr int kPartialBytes = NT * BM * 4;
-    static constexpr int kMaxGroup = 4;
+    static constexpr int kMaxGroup = NT <= 64 ? 4 : 2;      // 128 tokens: a k-block is 32 KB, two of them per stage
     static constexpr int kMaxStages = 12;
     static constexpr int max_stages(int group) {
         const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * kBlockBytes);
@@ -1174,7 +1174,7 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
 // tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; 512 (M > 128) = a pair
-// of CTAs on a [256 x 256] tile (cta_group::2); -1, -2, -4, -8 (M <= 64 only) =
+// of CTAs on a [256 x 256] tile (cta_group::2); -1, -2, -4, -8 (M <= 128 only) =
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
@@ -1192,9 +1192,11 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         if (g_num_sms <= 0) g_num_sms = 148;
     }
     const char* err = nullptr;
-    if (M <= 64 && tile_n <= 0) {
-        // few rows: weights are the MMA's M operand, K is cut across a cluster (tile_n < 0: -tile_n CTAs)
-        const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (M <= 128 && tile_n <= 0) {
+        // few rows: weights are the MMA's M operand, K is cut across a cluster (tile_n < 0: -tile_n CTAs).  Up to
+        // 128 tokens: with one row tile the token-major kernel would reload all tokens for every narrow column
+        // tile (measured at 128 rows, [2048 x 5632]: 25.8 us against this kernel's 14).
+        const int nt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         const int tiles_n = (N + BM - 1) / BM, num_kb = (K + BK - 1) / BK;
         int dev = 0;
         cudaGetDevice(&dev);
@@ -1211,7 +1213,8 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             switch (nt) {
                 case 16: return launch_streamk<16>(tw, tx, p, stream);
                 case 32: return launch_streamk<32>(tw, tx, p, stream);
-                default: return launch_streamk<64>(tw, tx, p, stream);
+                case 64: return launch_streamk<64>(tw, tx, p, stream);
+                default: return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: the evenly dealt kernel takes at most 64 rows, got %d", M);
             }
         }
         int ksplit = 1;
@@ -1226,11 +1229,15 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             for (int ks = 2; ks <= 8; ks *= 2)
                 if (tiles_n * ks <= max_resident_ctas(ks) && num_kb / ks >= 4) ksplit = ks;
         }
+        // 65..128 tokens with an unsplit tile per CTA (many row tiles, e.g. gate/up): the token-major kernel with
+        // 128-wide tiles is the faster one there (22 against 28-33 us at [11264 x 2048])
+        const bool token_major_instead = nt == 128 && tile_n == 0 && ksplit == 1;
         GemmParams p{C, bias, M, N, K, epilogue, status};
-        switch (nt) {
+        if (!token_major_instead) switch (nt) {
             case 16: return launch_skinny<16>(W, A, p, ksplit, stream);
             case 32: return launch_skinny<32>(W, A, p, ksplit, stream);
-            default: return launch_skinny<64>(W, A, p, ksplit, stream);
+            case 64: return launch_skinny<64>(W, A, p, ksplit, stream);
+            default: return launch_skinny<128>(W, A, p, ksplit, stream);
         }
     }
     int bn = tile_n;

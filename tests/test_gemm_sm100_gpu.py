@@ -90,7 +90,7 @@ def test_two_ctas_on_one_tile(M, N, K):
         k.gemm_sm100(_rand(64, 64), _rand(128, 64), tile_n=512)
 
 
-@pytest.mark.parametrize("M", [1, 8, 16, 33, 64])
+@pytest.mark.parametrize("M", [1, 8, 16, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
 @pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8, -100])
 def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
@@ -100,6 +100,10 @@ def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
     k = _k()
     a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
     bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    if cluster == -100 and M > 64:                       # the evenly dealt kernel stops at 64 rows and says so
+        with pytest.raises(k.KernelError, match="at most 64 rows"):
+            k.gemm_sm100(a, w, bias=bias, tile_n=cluster)
+        return
     ref = R.gemm_ref(a, w, bias)
     tol = 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
     got = k.gemm_sm100(a, w, bias=bias, tile_n=cluster)
