@@ -21,11 +21,15 @@ namespace {
 using namespace sm100;
 
 constexpr int HD = 64, BQ = 128, BKV = 64, UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;                     // warps 0-3: copies, P V, Q K^T, (idle); warps 4-7: the softmax rows
+constexpr int kQkWarp = 2;
+constexpr int kRegsFew = 64, kRegsMany = 192;      // registers per thread of the two warpgroups (sum * 128 = half an SM's file)
 constexpr int kTileBytes = BQ * 128;              // Q or P: 128 rows of 128 bytes
 constexpr int kKVBytes = BKV * 128;               // K or V tile: 64 rows of 128 bytes
-constexpr int kSmemBytes = kTileBytes * 2 + 4 * kKVBytes + 1024 + 1024;
-constexpr int kTmemCols = 128;                    // S: columns 0..63, O: columns 64..127
+constexpr int kStages = 3;                        // ring slots for key tiles, and as many for value tiles
+constexpr int kPageWindow = 256;                  // block-table entries staged in shared memory at a time
+constexpr int kSmemBytes = kTileBytes * 3 + 2 * kStages * kKVBytes + 1024 + 1024 + kPageWindow * 4;
+constexpr int kTmemCols = 256;                    // S of even / odd tiles: columns 0..63 / 64..127, O: 128..191
 
 struct AttnTcParams {
     __nv_bfloat16* out;           // [T, NH*HD]
@@ -46,44 +50,91 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 3)
+// two fp32 lanes per instruction (the packed fp32 pipe): d = a * b + c and d = a + b on register pairs
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// A row's reference exponent moves only when its maximum has grown by more than this (in the exp2 domain):
+// until then the weights are at most 2^8, which fp32 sums and bfloat16 weights hold with the same relative
+// precision, and the accumulator in TMEM needs no rescaling.  The final division by the row's sum, taken
+// with the same references, makes the result independent of when the reference moved.
+constexpr float kRefSlack = 8.0f;
+
+// score i of the row's 64 (i is a constant after unrolling)
+#define SV(i) ((i) < 32 ? sv_lo[(i) & 31] : sv_hi[(i) & 31])
+
+__global__ void __launch_bounds__(kThreads, 2)
 paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                              const AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_s = smem;                               // [128][64] bf16, K-major, swizzled
-    uint8_t* p_s = smem + kTileBytes;                  // [128][64 keys] bf16, K-major, swizzled
-    uint8_t* kv_s = smem + 2 * kTileBytes;             // [2 stages][K 8 KB | V 8 KB]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kTileBytes + 4 * kKVBytes);
+    uint8_t* q_s = smem;                                            // [128][64] bf16, K-major, swizzled
+    uint8_t* p_s = smem + kTileBytes;                               // [2][128][64 keys] bf16, K-major, swizzled
+    uint8_t* k_s = smem + 3 * kTileBytes;                           // [kStages][64 keys][64]
+    uint8_t* v_s = k_s + kStages * kKVBytes;                        // [kStages][64 keys][64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kStages * kKVBytes);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;     // [2]
-    uint64_t* kv_empty = bars + 3;    // [2]
-    uint64_t* s_full = bars + 5;
-    uint64_t* s_free = bars + 6;
-    uint64_t* p_ready = bars + 7;
-    uint64_t* o_done = bars + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* k_full = bars + 1;                  // [kStages]
+    uint64_t* k_empty = k_full + kStages;         // [kStages]
+    uint64_t* v_full = k_empty + kStages;         // [kStages]
+    uint64_t* v_empty = v_full + kStages;         // [kStages]
+    uint64_t* s_full = v_empty + kStages;         // [2]
+    uint64_t* p_ready = s_full + 2;               // [2]
+    uint64_t* o_done = p_ready + 2;               // [2]
+    uint64_t* s_free = o_done + 2;                // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int32_t* page_win = reinterpret_cast<int32_t*>(bars) + 256;     // [kPageWindow] block-table entries
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, kvh = blockIdx.y;
+    // tiles come longest first, and CTAs are handed out in the order of blockIdx.x: the kv heads of one tile are
+    // neighbours, so that the long tiles of every head start in the first wave
+    const int tile = blockIdx.x / p.NKV, kvh = blockIdx.x % p.NKV;
     const int G = p.NH / p.NKV;
 
     if (threadIdx.x == 0) {
         *abort = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(s_full, 1);
-        mbar_init(s_free, 128);
-        mbar_init(p_ready, 128);
-        mbar_init(o_done, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&s_full[b], 1);
+            mbar_init(&p_ready[b], 4);
+            mbar_init(&s_free[b], 4);
+            mbar_init(&o_done[b], 1);
+        }
         mbar_fence_init();
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_kv);
     }
     // key/value stages start as zeros: pages that are skipped (beyond the request, or released by the
     // window) leave their rows as they are, and those rows must hold finite numbers (their weights are 0)
-    for (int i = threadIdx.x; i < 4 * kKVBytes / 16; i += kThreads) reinterpret_cast<uint4*>(kv_s)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < 2 * kStages * kKVBytes / 16; i += kThreads) reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -105,167 +156,205 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const int t_begin = kv_lo / BKV, t_end = (kv_hi + BKV - 1) / BKV;
     const int n_iter = t_end - t_begin;
 
+    // the softmax rows keep a row's 64 scores in registers; the other warpgroup runs single threads and gives
+    // its registers up for that
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsFew));
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // The warp stages the request's block-table entries in shared memory, a window at a time (one coalesced
+        // read instead of a dependent global load per page); lane 0 then issues the copies.
+        const int32_t* table = p.block_table + (size_t)s_req * p.max_pages;
+        const int ppt = BKV / p.page_size;                               // pages per key tile
+        const int iters_per_win = kPageWindow / ppt;
+        const uint32_t page_bytes = p.page_size * 128;
         if (lane == 0) {
-            const int32_t* table = p.block_table + (size_t)s_req * p.max_pages;
             mbar_arrive_expect_tx(q_full, kTileBytes);
             tma_load_3d(q_s, &tmap_q, q_full, 0, kvh * G, qs0 + row0 / G);
-            const int ppt = BKV / p.page_size;                           // pages per key tile
-            const uint32_t page_bytes = p.page_size * 128;
-            bool ok = true;
-            for (int it = 0; it < n_iter && ok; ++it) {
-                const int s = it & 1, t0 = (t_begin + it) * BKV;
-                if (!(ok = mbar_wait(&kv_empty[s], ((it >> 1) & 1) ^ 1, abort, p.status, 1))) break;
-                int pages[8], n_valid = 0;
-                for (int i = 0; i < ppt; ++i) {
-                    const int tp = t0 + i * p.page_size;
-                    const bool live = tp < kv_hi && tp + p.page_size > kv_lo;
-                    pages[i] = live ? table[tp / p.page_size] : -1;
-                    n_valid += pages[i] >= 0;
-                }
-                mbar_arrive_expect_tx(&kv_full[s], n_valid * page_bytes * 2);
-                uint8_t* k_dst = kv_s + s * 2 * kKVBytes;
-                for (int i = 0; i < ppt; ++i) {
-                    if (pages[i] < 0) continue;
-                    const int row = (pages[i] * 2 * p.NKV + kvh) * p.page_size;
-                    tma_load_2d(k_dst + i * page_bytes, &tmap_kv, &kv_full[s], 0, row);
-                    tma_load_2d(k_dst + kKVBytes + i * page_bytes, &tmap_kv, &kv_full[s], 0, row + p.NKV * p.page_size);
+        }
+        bool ok = true;
+        int st = 0, ph = 0;                                              // ring slot and its phase
+        for (int it0 = 0; it0 < n_iter && ok; it0 += iters_per_win) {
+            const int it1 = min(n_iter, it0 + iters_per_win);
+            const int first_page = (t_begin + it0) * ppt;
+            __syncwarp();
+            for (int i = lane; i < (it1 - it0) * ppt; i += 32)
+                page_win[i] = first_page + i < p.max_pages ? table[first_page + i] : -1;
+            __syncwarp();
+            if (lane == 0) {
+                for (int it = it0; it < it1 && ok; ++it) {
+                    const int t0 = (t_begin + it) * BKV;
+                    int rows[8], n_valid = 0;
+                    for (int i = 0; i < ppt; ++i) {
+                        const int tp = t0 + i * p.page_size, page = page_win[(it - it0) * ppt + i];
+                        const bool live = tp < kv_hi && tp + p.page_size > kv_lo && page >= 0;
+                        rows[i] = live ? (page * 2 * p.NKV + kvh) * p.page_size : -1;
+                        n_valid += live;
+                    }
+                    // keys first: Q K^T of a tile runs two tiles ahead of its P V
+                    if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort, p.status, 1))) break;
+                    mbar_arrive_expect_tx(&k_full[st], n_valid * page_bytes);
+                    for (int i = 0; i < ppt; ++i)
+                        if (rows[i] >= 0) tma_load_2d(k_s + st * kKVBytes + i * page_bytes, &tmap_kv, &k_full[st], 0, rows[i]);
+                    if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort, p.status, 9))) break;
+                    mbar_arrive_expect_tx(&v_full[st], n_valid * page_bytes);
+                    for (int i = 0; i < ppt; ++i)
+                        if (rows[i] >= 0)
+                            tma_load_2d(v_s + st * kKVBytes + i * page_bytes, &tmap_kv, &v_full[st], 0, rows[i] + p.NKV * p.page_size);
+                    if (++st == kStages) { st = 0; ph ^= 1; }
                 }
             }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ P V issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BQ, BKV);
             constexpr uint32_t idesc_pv = umma_idesc_bf16_f32_bmn(BQ, HD);
-            const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-            bool ok = mbar_wait(q_full, 0, abort, p.status, 2);
+            const uint32_t p_addr = smem_u32(p_s), v_addr = smem_u32(v_s);
+            bool ok = true;
+            int vst = 0, vph = 0;
             for (int it = 0; it < n_iter && ok; ++it) {
-                const int s = it & 1;
-                const uint32_t k_addr = smem_u32(kv_s + s * 2 * kKVBytes), v_addr = k_addr + kKVBytes;
-                if (!(ok = mbar_wait(&kv_full[s], (it >> 1) & 1, abort, p.status, 3))) break;
-                if (it > 0 && !(ok = mbar_wait(s_free, (it - 1) & 1, abort, p.status, 4))) break;
+                const int b = it & 1;
+                if (!(ok = mbar_wait(&v_full[vst], vph, abort, p.status, 4))) break;
+                if (!(ok = mbar_wait(&p_ready[b], (it >> 1) & 1, abort, p.status, 5))) break;
                 tc_fence_after_sync();
-#pragma unroll
-                for (int k = 0; k < HD / UMMA_K; ++k)
-                    umma_bf16(tmem_base, umma_desc_k_sw128(q_addr + k * 32), umma_desc_k_sw128(k_addr + k * 32), idesc_qk, k != 0);
-                umma_commit(s_full);
-                if (!(ok = mbar_wait(p_ready, it & 1, abort, p.status, 5))) break;
-                tc_fence_after_sync();
+                const uint32_t pa = p_addr + b * kTileBytes, va = v_addr + vst * kKVBytes;
 #pragma unroll
                 for (int k = 0; k < BKV / UMMA_K; ++k)
-                    umma_bf16(tmem_base + 64, umma_desc_k_sw128(p_addr + k * 32), umma_desc_mn_sw128(v_addr + k * 2048, 0),
+                    umma_bf16(tmem_base + 2 * BKV, umma_desc_k_sw128(pa + k * 32), umma_desc_mn_sw128(va + k * 2048, 0),
                               idesc_pv, (it | k) != 0);
-                umma_commit(&kv_empty[s]);
-                umma_commit(o_done);
+                umma_commit(&o_done[b]);
+                umma_commit(&v_empty[vst]);
+                if (++vst == kStages) { vst = 0; vph ^= 1; }
             }
         }
+    } else if (warp == kQkWarp) {
+        // ------------------------------------------------------------------ Q K^T issuer
+        // A thread issues one tcgen05 instruction or barrier probe every 50 to 100 clocks, so the two products
+        // have a thread each.  S has two buffers in TMEM, and the rows hold S of tile it in registers from
+        // the start of their work on it: its buffer takes the scores of tile it + 2 while they compute.
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BQ, BKV);
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s);
+            bool ok = mbar_wait(q_full, 0, abort, p.status, 2);
+            int kst = 0, kph = 0;
+            for (int it = 0; it < n_iter && ok; ++it) {
+                const int b = it & 1;
+                if (!(ok = mbar_wait(&k_full[kst], kph, abort, p.status, 3))) break;
+                if (it >= 2 && !(ok = mbar_wait(&s_free[b], ((it - 2) >> 1) & 1, abort, p.status, 11))) break;
+                tc_fence_after_sync();
+                const uint32_t ka = k_addr + kst * kKVBytes;
+#pragma unroll
+                for (int k = 0; k < HD / UMMA_K; ++k)
+                    umma_bf16(tmem_base + b * BKV, umma_desc_k_sw128(q_addr + k * 32), umma_desc_k_sw128(ka + k * 32), idesc_qk, k != 0);
+                umma_commit(&s_full[b]);
+                umma_commit(&k_empty[kst]);
+                if (++kst == kStages) { kst = 0; kph ^= 1; }
+            }
+        }
+    }
     } else {
-        // ------------------------------------------------------------------ softmax rows (warps 2..5)
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------------ softmax rows (warps 4..7)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMany));
+        const int quarter = warp & 3;                            // the quarter of TMEM's lanes that this warp may touch
         const int r_local = quarter * 32 + lane;                 // row of the tile = TMEM lane
         const int r = row0 + r_local;
         const bool valid = r_local < rows_here;
         const int pos = ctx + r / G;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        uint8_t* p_row = p_s + r_local * 128;
+        const uint32_t t_out = t_lane + 2 * BKV;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int it = 0; it < n_iter && ok; ++it) {
-            const int j0 = (t_begin + it) * BKV;
-            if (!(ok = mbar_wait(s_full, it & 1, abort, p.status, 6))) break;
+            const int j0 = (t_begin + it) * BKV, b = it & 1;
+            uint8_t* p_row = p_s + b * kTileBytes + r_local * 128;
+            if (!(ok = mbar_wait(&s_full[b], (it >> 1) & 1, abort, p.status, 6))) break;
             tc_fence_after_sync();
-            // rows whose keys of this tile are all visible skip the per-key tests (all tiles but the ones on
-            // the diagonal or at the window's edge)
-            const bool need_mask = !valid || j0 + BKV - 1 > pos || (p.window > 0 && j0 <= pos - p.window);
-            // pass 1: the row's maximum over this tile
-            float mx = m;
-#pragma unroll
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t sv[32];
-                tmem_ld_32x32b_x32(t_lane + c, sv);
-                tmem_ld_wait();
-                if (!need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]) * p.scale_log2);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int j = j0 + c + i;
-                        const bool vis = valid && j <= pos && (p.window <= 0 || j > pos - p.window);
-                        mx = fmaxf(mx, vis ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY);
-                    }
-                }
-            }
-            const float ref = mx == -INFINITY ? 0.f : mx;
-            const float alpha = ex2_approx(m - ref);
-            m = mx;
-            // the previous tile's P V must be complete before O is rescaled and P overwritten
-            if (it > 0) {
-                if (!(ok = mbar_wait(o_done, (it - 1) & 1, abort, p.status, 7))) break;
-                tc_fence_after_sync();
-                // the accumulator is rescaled only when some row of the warp got a new maximum (the TMEM
-                // loads and stores are warp-wide, so the decision is the warp's)
-                if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-#pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
-                        uint32_t ov[32];
-                        tmem_ld_32x32b_x32(t_lane + 64 + c, ov);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-                        tmem_st_32x32b_x32(t_lane + 64 + c, ov);
-                    }
-                    tmem_st_wait();
-                }
-            }
-            // pass 2: weights, their sum, and P in the MMA's shared-memory layout (16-byte chunk ^ row % 8)
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t sv[32];
-                tmem_ld_32x32b_x32(t_lane + c, sv);
-                tmem_ld_wait();
-                uint32_t packed[16];
-                if (!need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -ref));
-                        const float p1 = ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -ref));
-                        sum += p0 + p1;
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float pr[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int j = j0 + c + i + e;
-                            const bool vis = valid && j <= pos && (p.window <= 0 || j > pos - p.window);
-                            pr[e] = vis ? ex2_approx(fmaf(__uint_as_float(sv[i + e]), p.scale_log2, -ref)) : 0.f;
-                        }
-                        sum += pr[0] + pr[1];
-                        __nv_bfloat162 h = __floats2bfloat162_rn(pr[0], pr[1]);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-                    }
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c >> 3) + q4;                        // 16-byte chunk of the row: 8 keys
-                    *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r_local & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
-            }
-            l = l * alpha + sum;
+            // the row's 64 scores stay in registers for both passes
+            uint32_t sv_lo[32], sv_hi[32];
+            tmem_ld_32x32b_x32(t_lane + b * BKV, sv_lo);
+            tmem_ld_32x32b_x32(t_lane + b * BKV + 32, sv_hi);
+            tmem_ld_wait();
             tc_fence_before_sync();
-            mbar_arrive(s_free);                   // S may be overwritten by the next Q K^T
-            fence_proxy_async();                   // P is in shared memory for the tensor core to read
-            mbar_arrive(p_ready);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[b]);
+            // rows whose keys of this tile are all visible skip the per-key tests (all tiles but the ones on the
+            // diagonal or at the window's edge); masked scores become -inf here, once
+            const bool need_mask = !valid || j0 + BKV - 1 > pos || (p.window > 0 && j0 <= pos - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BKV; ++i) {
+                    const int j = j0 + i;
+                    const bool vis = valid && j <= pos && (p.window <= 0 || j > pos - p.window);
+                    if (!vis) SV(i) = __float_as_uint(-INFINITY);
+                }
+            }
+            // pass 1: the maximum of the raw scores (the scale is positive, so it commutes with the maximum),
+            // in two independent chains of three-input maxima
+            float a0 = -INFINITY, a1 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+                a0 = max3(a0, __uint_as_float(SV(i)), __uint_as_float(SV(i + 1)));
+                a1 = max3(a1, __uint_as_float(SV(i + 2)), __uint_as_float(SV(i + 3)));
+            }
+            const float mx_tile = fmaxf(a0, a1) * p.scale_log2;
+            // m is the reference of the row's exponents; -inf + slack is -inf, so the first visible key sets it
+            const float m_new = mx_tile > m + kRefSlack ? mx_tile : m;
+            const float alpha = m_new == m ? 1.0f : ex2_approx(m - m_new);
+            m = m_new;
+            const float ref = m == -INFINITY ? 0.f : m;
+            // the accumulator is rescaled only when some row of the warp moved its reference (the TMEM loads
+            // and stores are warp-wide, so the decision is the warp's); P V of the previous tile must be
+            // complete by then
+            if (it > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+                if (!(ok = mbar_wait(&o_done[b ^ 1], ((it - 1) >> 1) & 1, abort, p.status, 7))) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld_32x32b_x32(t_out + c, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                    tmem_st_32x32b_x32(t_out + c, ov);
+                }
+                tmem_st_wait();
+            }
+            // this P buffer was read by P V of the tile before the previous one
+            if (it > 1 && !(ok = mbar_wait(&o_done[b], ((it - 2) >> 1) & 1, abort, p.status, 10))) break;
+            // pass 2: weights (exp2 of -inf is 0), their sum, and P in the MMA's shared-memory layout
+            // (16-byte chunk ^ row % 8)
+            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), nref2 = pack_f32x2(-ref, -ref);
+            uint64_t acc_a = pack_f32x2(0.f, 0.f), acc_b = acc_a;
+#pragma unroll
+            for (int c = 0; c < BKV; c += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 4) {
+                    float x0, x1, x2, x3;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(SV(c + i)), __uint_as_float(SV(c + i + 1))), scale2, nref2), x0, x1);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(SV(c + i + 2)), __uint_as_float(SV(c + i + 3))), scale2, nref2), x2, x3);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+                    acc_a = add_f32x2(acc_a, pack_f32x2(p0, p1));
+                    acc_b = add_f32x2(acc_b, pack_f32x2(p2, p3));
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+                    packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
+                }
+                *reinterpret_cast<uint4*>(p_row + (((c >> 3) ^ (r_local & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            float s0, s1, s2, s3;
+            unpack_f32x2(acc_a, s0, s1);
+            unpack_f32x2(acc_b, s2, s3);
+            l = l * alpha + ((s0 + s1) + (s2 + s3));
+            // one arrival per warp: P is in shared memory for the tensor core to read (and O, if it was
+            // rescaled, is in TMEM)
+            tc_fence_before_sync();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[b]);
         }
-        if (ok && n_iter > 0) ok = mbar_wait(o_done, (n_iter - 1) & 1, abort, p.status, 8);
+        if (ok && n_iter > 0) ok = mbar_wait(&o_done[(n_iter - 1) & 1], ((n_iter - 1) >> 1) & 1, abort, p.status, 8);
         tc_fence_after_sync();
         if (ok && n_iter > 0) {
             // every lane takes part in the TMEM loads (they are warp-wide instructions); only valid rows store
@@ -274,7 +363,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 #pragma unroll
             for (int c = 0; c < HD; c += 32) {
                 uint32_t ov[32];
-                tmem_ld_32x32b_x32(t_lane + 64 + c, ov);
+                tmem_ld_32x32b_x32(t_out + c, ov);
                 tmem_ld_wait();
                 if (valid) {
 #pragma unroll
@@ -314,7 +403,8 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
         return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: group size %d/%d must divide 128", NH, NKV);
     if (page_size < 8 || BKV % page_size != 0)
         return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: page size %d must be 8, 16, 32 or 64", page_size);
-    if (num_tiles < 0 || T <= 0 || num_pages <= 0 || max_pages <= 0 || NKV > 65535)
+    if (!(scale > 0.f)) return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: scale %g must be positive", (double)scale);
+    if (num_tiles < 0 || T <= 0 || num_pages <= 0 || max_pages <= 0)
         return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: bad sizes tiles=%d T=%d pages=%d", num_tiles, T, num_pages);
     if (num_tiles == 0) return FORGE_OK;
     const int G = NH / NKV;
@@ -332,7 +422,7 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
     AttnTcParams p{(__nv_bfloat16*)out, block_table, tile_req, tile_row0, q_start, ctx_before, NH, NKV, page_size,
                    max_pages, window, scale * 1.4426950408889634f, status};
     return forge::check_launch("paged_attention_sm100",
-                               forge::launch(paged_attention_sm100_kernel, dim3(num_tiles, NKV), dim3(kThreads), kSmemBytes,
+                               forge::launch(paged_attention_sm100_kernel, dim3((unsigned)num_tiles * NKV), dim3(kThreads), kSmemBytes,
                                              stream, 1, tq, tkv, p));
 }
 

@@ -93,6 +93,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     // Suspending waits: the hardware wakes the thread the moment the phase completes (a polling loop with
     // sleeps in it notices a completed phase late, and in a short pipeline that delay is a bubble); the
     // suspend limit bounds how long an abort or the time limit can go unnoticed.
+    if (mbar_test_wait(bar, parity)) return true;      // a phase that is already complete costs one probe
     if (mbar_try_wait_for(bar, parity, 1000)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
