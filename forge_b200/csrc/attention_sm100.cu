@@ -23,7 +23,11 @@ using namespace sm100;
 constexpr int HD = 64, BQ = 128, BKV = 64, UMMA_K = 16;
 constexpr int kThreads = 256;                     // warps 0-3: copies, P V, Q K^T, (idle); warps 4-7: the softmax rows
 constexpr int kQkWarp = 2;
-constexpr int kRegsFew = 64, kRegsMany = 192;      // registers per thread of the two warpgroups (sum * 128 = half an SM's file)
+constexpr int kCtasPerSm = 2;
+constexpr int kLaunchRegs = 65536 / (kThreads * kCtasPerSm) / 8 * 8;     // what the compiler gives every thread at launch
+constexpr int kRegsFew = 64, kRegsMany = 192;      // registers per thread of the two warpgroups after they trade
+// setmaxnreg only moves registers inside the CTA's allocation: asking for more than it holds waits for ever
+static_assert(kRegsFew + kRegsMany <= 2 * kLaunchRegs, "the two warpgroups cannot hold more registers than the CTA was given");
 constexpr int kTileBytes = BQ * 128;              // Q or P: 128 rows of 128 bytes
 constexpr int kKVBytes = BKV * 128;               // K or V tile: 64 rows of 128 bytes
 constexpr int kStages = 3;                        // ring slots for key tiles, and as many for value tiles
@@ -84,7 +88,7 @@ constexpr float kRefSlack = 8.0f;
 // score i of the row's 64 (i is a constant after unrolling)
 #define SV(i) ((i) < 32 ? sv_lo[(i) & 31] : sv_hi[(i) & 31])
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                              const AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -417,6 +421,14 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_sm100: %s", cudaGetErrorString(e));
+        // the warpgroups trade registers inside what the CTA was given at launch; a build that gives less would wait
+        // for registers that never come, so it is refused here
+        cudaFuncAttributes attr;
+        e = cudaFuncGetAttributes(&attr, paged_attention_sm100_kernel);
+        if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_sm100: %s", cudaGetErrorString(e));
+        if (attr.numRegs * 2 < kRegsFew + kRegsMany)
+            return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: built with %d registers per thread, needs %d",
+                               attr.numRegs, (kRegsFew + kRegsMany + 1) / 2);
         configured = true;
     }
     AttnTcParams p{(__nv_bfloat16*)out, block_table, tile_req, tile_row0, q_start, ctx_before, NH, NKV, page_size,
