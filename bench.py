@@ -87,6 +87,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"], help="fewer layers (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
     a = ap.parse_args()
     if a.impl == "reference":
         # Cyxuan0311/Forge is a C++/CUDA project whose build fetches pybind11 over the network and whose
@@ -113,9 +114,10 @@ def main():
     tensors = random_tensors(cfg, seed=0, std=0.02, device="cuda")
     max_b = 64 if not a.no_points else a.batch
     total_steps = a.steps + a.warmup + 2
-    cache_tokens = max(max_b * (PROMPT_LEN + total_steps + 16), PREFILL_TOKENS + 64)
+    per_request = -(-(PROMPT_LEN + total_steps + 16) // a.block_size) * a.block_size      # a request holds whole pages
+    cache_tokens = max(max_b * per_request, PREFILL_TOKENS + a.block_size)
     model = forge.Model(config=cfg, tensors=tensors, dtype="bfloat16", max_num_seqs=max_b, cache_tokens=cache_tokens,
-                        max_tokens_per_step=2048)
+                        max_tokens_per_step=2048, block_size=a.block_size)
     del tensors
     runner = model.runner
     V = cfg.vocab_size

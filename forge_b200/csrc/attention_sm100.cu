@@ -196,11 +196,11 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                         n_valid += live;
                     }
                     // keys first: Q K^T of a tile runs two tiles ahead of its P V
-                    if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort, p.status, 1))) break;
+                    if (!(ok = mbar_wait<true>(&k_empty[st], ph ^ 1, abort, p.status, 1))) break;
                     mbar_arrive_expect_tx(&k_full[st], n_valid * page_bytes);
                     for (int i = 0; i < ppt; ++i)
                         if (rows[i] >= 0) tma_load_2d(k_s + st * kKVBytes + i * page_bytes, &tmap_kv, &k_full[st], 0, rows[i]);
-                    if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort, p.status, 9))) break;
+                    if (!(ok = mbar_wait<true>(&v_empty[st], ph ^ 1, abort, p.status, 9))) break;
                     mbar_arrive_expect_tx(&v_full[st], n_valid * page_bytes);
                     for (int i = 0; i < ppt; ++i)
                         if (rows[i] >= 0)
@@ -219,8 +219,8 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             int vst = 0, vph = 0;
             for (int it = 0; it < n_iter && ok; ++it) {
                 const int b = it & 1;
-                if (!(ok = mbar_wait(&v_full[vst], vph, abort, p.status, 4))) break;
-                if (!(ok = mbar_wait(&p_ready[b], (it >> 1) & 1, abort, p.status, 5))) break;
+                if (!(ok = mbar_wait<true>(&v_full[vst], vph, abort, p.status, 4))) break;
+                if (!(ok = mbar_wait<true>(&p_ready[b], (it >> 1) & 1, abort, p.status, 5))) break;
                 tc_fence_after_sync();
                 const uint32_t pa = p_addr + b * kTileBytes, va = v_addr + vst * kKVBytes;
 #pragma unroll
@@ -240,12 +240,12 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BQ, BKV);
             const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s);
-            bool ok = mbar_wait(q_full, 0, abort, p.status, 2);
+            bool ok = mbar_wait<true>(q_full, 0, abort, p.status, 2);
             int kst = 0, kph = 0;
             for (int it = 0; it < n_iter && ok; ++it) {
                 const int b = it & 1;
-                if (!(ok = mbar_wait(&k_full[kst], kph, abort, p.status, 3))) break;
-                if (it >= 2 && !(ok = mbar_wait(&s_free[b], ((it - 2) >> 1) & 1, abort, p.status, 11))) break;
+                if (!(ok = mbar_wait<true>(&k_full[kst], kph, abort, p.status, 3))) break;
+                if (it >= 2 && !(ok = mbar_wait<true>(&s_free[b], ((it - 2) >> 1) & 1, abort, p.status, 11))) break;
                 tc_fence_after_sync();
                 const uint32_t ka = k_addr + kst * kKVBytes;
 #pragma unroll
@@ -272,7 +272,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         for (int it = 0; it < n_iter && ok; ++it) {
             const int j0 = (t_begin + it) * BKV, b = it & 1;
             uint8_t* p_row = p_s + b * kTileBytes + r_local * 128;
-            if (!(ok = mbar_wait(&s_full[b], (it >> 1) & 1, abort, p.status, 6))) break;
+            if (!(ok = mbar_wait<true>(&s_full[b], (it >> 1) & 1, abort, p.status, 6))) break;
             tc_fence_after_sync();
             // the row's 64 scores stay in registers for both passes
             uint32_t sv_lo[32], sv_hi[32];
@@ -311,7 +311,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             // and stores are warp-wide, so the decision is the warp's); P V of the previous tile must be
             // complete by then
             if (it > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
-                if (!(ok = mbar_wait(&o_done[b ^ 1], ((it - 1) >> 1) & 1, abort, p.status, 7))) break;
+                if (!(ok = mbar_wait<true>(&o_done[b ^ 1], ((it - 1) >> 1) & 1, abort, p.status, 7))) break;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int c = 0; c < HD; c += 32) {
@@ -325,7 +325,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                 tmem_st_wait();
             }
             // this P buffer was read by P V of the tile before the previous one
-            if (it > 1 && !(ok = mbar_wait(&o_done[b], ((it - 2) >> 1) & 1, abort, p.status, 10))) break;
+            if (it > 1 && !(ok = mbar_wait<true>(&o_done[b], ((it - 2) >> 1) & 1, abort, p.status, 10))) break;
             // pass 2: weights (exp2 of -inf is 0), their sum, and P in the MMA's shared-memory layout
             // (16-byte chunk ^ row % 8)
             const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), nref2 = pack_f32x2(-ref, -ref);
@@ -358,7 +358,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[b]);
         }
-        if (ok && n_iter > 0) ok = mbar_wait(&o_done[(n_iter - 1) & 1], ((n_iter - 1) >> 1) & 1, abort, p.status, 8);
+        if (ok && n_iter > 0) ok = mbar_wait<true>(&o_done[(n_iter - 1) & 1], ((n_iter - 1) >> 1) & 1, abort, p.status, 8);
         tc_fence_after_sync();
         if (ok && n_iter > 0) {
             // every lane takes part in the TMEM loads (they are warp-wide instructions); only valid rows store

@@ -89,11 +89,13 @@ __device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity
         : "memory");
     return ok != 0;
 }
+template <bool kProbeFirst = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, int where = 0) {
     // Suspending waits: the hardware wakes the thread the moment the phase completes (a polling loop with
     // sleeps in it notices a completed phase late, and in a short pipeline that delay is a bubble); the
     // suspend limit bounds how long an abort or the time limit can go unnoticed.
-    if (mbar_test_wait(bar, parity)) return true;      // a phase that is already complete costs one probe
+    // where most waits find their phase complete already, a plain probe first is cheaper than a suspending wait
+    if (kProbeFirst && mbar_test_wait(bar, parity)) return true;
     if (mbar_try_wait_for(bar, parity, 1000)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
