@@ -4,12 +4,18 @@
 // group) pair, row r <-> token r / G, head r % G, so a tile is 128 / G tokens and the G heads share every
 // key/value tile.  Per tile of 64 keys:
 //   S = Q K^T      tcgen05.mma M=128 N=64 K=64, Q and K in shared memory (TMA, 128-byte swizzle), S in TMEM
-//   softmax        128 threads, one row each, read S from TMEM, online max/sum in fp32 (exp2 domain), rescale
-//                  the output accumulator in TMEM, write P as bf16 into shared memory in the MMA's layout
+//                  (two buffers: the scores of tile it + 2 are computed while the rows work on tile it)
+//   softmax        128 threads, one row each, hold the row's 64 scores in registers, online max/sum in fp32
+//                  (exp2 domain, packed fp32 arithmetic), write P as bf16 into shared memory in the MMA's
+//                  layout (two buffers); the output accumulator in TMEM is rescaled only when a row's
+//                  reference exponent has to move (a maximum that grew by more than 2^8)
 //   O += P V       tcgen05.mma M=128 N=64 K=64, P K-major, V MN-major (keys are rows of 128 bytes), O in TMEM
-// Warp 0 feeds keys and values page by page through the request's block table (one TMA box per page and
-// operand, two stages), warp 1 issues the MMAs, warps 2-5 are the softmax rows.  Three such CTAs fit an SM
-// (64 KB of shared memory, 128 TMEM columns each), so one CTA's softmax overlaps another's MMAs.
+// Warps 0-3 run one thread each: warp 0 feeds keys and values page by page through the request's block table
+// (one TMA box per page and operand; key and value tiles have rings of three slots each, keys run ahead),
+// warp 1 issues P V, warp 2 issues Q K^T; warps 4-7 are the softmax rows.  The first warpgroup hands most of
+// its registers to the second (setmaxnreg).  Two such CTAs fit an SM (99 KB of shared memory, 256 TMEM
+// columns each).  Tiles are listed longest first and the kv heads of a tile are neighbouring CTAs, so the
+// long tiles of all heads start in the first wave.
 //   s_j = (q . k_j) / sqrt(64) for keys max(0, p - window + 1) <= j <= p of the row's position p;
 //   o = sum_j softmax(s)_j v_j        (formulas of src/operators/cuda/cuda_flash_attn.cu:154-248)
 // Needs 128 % G == 0, 64 % page_size == 0 and page_size >= 8; everything else is served by attention_mma.cu.
