@@ -40,13 +40,17 @@ struct GemmParams {
     int M, N, K;
     int epilogue;
     int* status;
+    int tma_out;        // fp32 results leave through shared memory and TMA stores / adds (the kernels that take a map of C)
 };
 
 template <int BN> struct Cfg {
     static constexpr int kStageBytes = (BM + BN) * BK * 2;
-    static constexpr int kStages = (kSmemLimit - 2048) / kStageBytes > 12 ? 12 : (kSmemLimit - 2048) / kStageBytes;
+    // the wide tiles (many rows) send fp32 results through two [128 rows x 32 fp32] boxes in shared memory
+    static constexpr int kOutBytes = BN >= 128 ? BM * 128 : 0;
+    static constexpr int kRingLimit = kSmemLimit - 2048 - 2 * kOutBytes;
+    static constexpr int kStages = kRingLimit / kStageBytes > 12 ? 12 : kRingLimit / kStageBytes;
     static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers*/;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 1024 /*barriers*/ + 2 * kOutBytes;
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
@@ -123,7 +127,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                  const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -131,6 +135,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes);
+    uint8_t* out_s = smem + kStages * C::kStageBytes + 1024;      // [2][128 rows][32 fp32], swizzled (wide tiles only)
     uint64_t* full = bars;                       // [kStages]  TMA -> MMA
     uint64_t* empty = bars + kStages;            // [kStages]  MMA -> TMA
     uint64_t* acc_full = bars + 2 * kStages;     // [2]        MMA -> epilogue
@@ -223,7 +228,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter .. +31
         const int row_in_tile = quarter * 32 + lane;
         bool ok = true;
-        int local = 0;
+        int local = 0, out_chunk = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             const int a = local & 1;
             const uint32_t aph = (local >> 1) & 1;
@@ -232,6 +237,44 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             tc_fence_after_sync();
             const int m = m0 + row_in_tile;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
+            if constexpr (C::kOutBytes > 0) {
+                if (p.tma_out) {
+                    // fp32 results: a chunk of 32 columns of all 128 rows goes to shared memory (the layout of a
+                    // 128-byte-swizzled box) and from there to global memory with one TMA instruction, a store
+                    // or an add that the L2 performs; the four warps meet at a named barrier around each chunk,
+                    // and two buffers let a chunk be written while the previous one is read
+                    const bool issuer = threadIdx.x == 64;
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 32) {
+                        if (n0 + c >= p.N) break;
+                        uint8_t* buf = out_s + (out_chunk++ & 1) * C::kOutBytes;
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(t_row + c, r);
+                        if (issuer) bulk_wait_group_read<1>();      // the copy that read this buffer two chunks ago
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        tmem_ld_wait();
+                        if (p.bias) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n0 + c + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + p.bias[n0 + c + i]);
+                        }
+                        uint8_t* row = buf + row_in_tile * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4*>(row + ((j ^ (row_in_tile & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        fence_proxy_async();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (issuer) {
+                            if (p.epilogue == EPI_ACCUM_F32) tma_reduce_add_2d(&tmap_c, buf, n0 + c, m0);
+                            else tma_store_2d(&tmap_c, buf, n0 + c, m0);
+                            bulk_commit_group();
+                        }
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(&acc_empty[a]);
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
@@ -249,6 +292,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             tc_fence_before_sync();
             mbar_arrive(&acc_empty[a]);
         }
+        if (C::kOutBytes > 0 && p.tma_out && threadIdx.x == 64) bulk_wait_group<0>();   // results are in global memory before the CTA leaves
     }
 
     tc_fence_before_sync();
@@ -287,7 +331,8 @@ constexpr int kPairBN = 256;                                   // N of the pair'
 struct PairCfg {
     static constexpr int kBlockBytes = (BM + kPairBN / 2) * BK * 2;         // one k-block per CTA: 32 KB
     static constexpr int kRingBlocks = 6;                                   // 192 KB of stages, whatever their size
-    static constexpr int kSmemBytes = kRingBlocks * kBlockBytes + 1024 + 1024;
+    static constexpr int kOutBytes = BM * 128;                              // a [128 rows x 32 fp32] box of results
+    static constexpr int kSmemBytes = kRingBlocks * kBlockBytes + 1024 + 1024 + 2 * kOutBytes;
     static constexpr int kTmemCols = 512;
 };
 
@@ -325,7 +370,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 
 template <int G>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                       const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using C = PairCfg;
     constexpr int g = G > 0 ? G : 1;
     constexpr int kStages = C::kRingBlocks / g, BNH = kPairBN / 2;
@@ -334,6 +380,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;                         // [kStages][ g tiles of A | g tiles of this CTA's half of W ]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRingBlocks * C::kBlockBytes);
+    uint8_t* out_s = smem + C::kRingBlocks * C::kBlockBytes + 1024;       // [2][128 rows][32 fp32], swizzled
     uint64_t* full = bars;                         // [kStages]  both CTAs' TMA -> the even CTA's MMA thread
     uint64_t* empty = bars + kStages;              // [kStages]  MMA -> each CTA's TMA thread
     uint64_t* acc_full = bars + 2 * kStages;       // [2]        MMA -> each CTA's epilogue
@@ -435,7 +482,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
         bool ok = true;
-        int local = 0;
+        int local = 0, out_chunk = 0;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
             const int a = local & 1;
             const uint32_t aph = (local >> 1) & 1;
@@ -444,16 +491,51 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             tc_fence_after_sync();
             const int m = m0 + row_in_tile;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kPairBN;
+            if (p.tma_out) {
+                // fp32 results: a chunk of 32 columns of all 128 rows goes to shared memory (the layout of a
+                // 128-byte-swizzled box) and from there to global memory with one TMA instruction, a store or
+                // an add that the L2 performs; the four warps meet at a named barrier around each chunk, and
+                // two buffers let a chunk be written while the previous one is read
+                const bool issuer = threadIdx.x == 64;
 #pragma unroll 1
-            for (int c = 0; c < kPairBN; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(t_row + c, r);
-                tmem_ld_wait();
-                store_row_chunk<kPairBN>(p, r, m, n0 + c);
+                for (int c = 0; c < kPairBN; c += 32) {
+                    if (n0 + c >= p.N) break;
+                    uint8_t* buf = out_s + (out_chunk++ & 1) * C::kOutBytes;      // the buffers alternate across tiles too
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + c, r);
+                    if (issuer) bulk_wait_group_read<1>();          // the copy that read this buffer two chunks ago
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    tmem_ld_wait();
+                    if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c + i < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + p.bias[n0 + c + i]);
+                    }
+                    uint8_t* row = buf + row_in_tile * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(row + ((j ^ (row_in_tile & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (issuer && m0 < p.M) {
+                        if (p.epilogue == EPI_ACCUM_F32) tma_reduce_add_2d(&tmap_c, buf, n0 + c, m0);
+                        else tma_store_2d(&tmap_c, buf, n0 + c, m0);
+                        bulk_commit_group();
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kPairBN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + c, r);
+                    tmem_ld_wait();
+                    store_row_chunk<kPairBN>(p, r, m, n0 + c);
+                }
             }
             tc_fence_before_sync();
             mbar_arrive_cluster(acc_empty0 + a * 8);
         }
+        if (p.tma_out && threadIdx.x == 64) bulk_wait_group<0>();   // the results are in global memory before the CTA leaves
     }
 
     tc_fence_before_sync();
@@ -1002,8 +1084,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cu
     }
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+    // fp32 results of the wide tiles leave by TMA where a map of C can be made (16-byte aligned rows)
+    GemmParams q = p;
+    CUtensorMap tc = ta;
+    const char* err = nullptr;
+    q.tma_out = C::kOutBytes > 0 && (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) && p.N % 4 == 0 &&
+                (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && f32_tile_map(p.C, p.M, p.N, BM, &tc, &err);
     return forge::check_launch("gemm_sm100", forge::launch(gemm_sm100_kernel<BN>, dim3(grid), dim3(kThreads),
-                                                             C::kSmemBytes, stream, 1, ta, tw, p));
+                                                             C::kSmemBytes, stream, 1, ta, tw, tc, q));
 }
 
 // How many pairs of CTAs of the two-CTA kernel run at once (one CTA per SM, clusters of 2: 74 on B200).
@@ -1049,10 +1137,15 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
         if (!bf16_tile_map(A, p.M, p.K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
         if (!bf16_tile_map(W, p.N, p.K, kPairBN / 2, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
     }
+    // fp32 results leave by TMA where a map of C can be made (16-byte aligned rows)
+    GemmParams q = p;
+    CUtensorMap tc = ta;
+    q.tma_out = (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) && p.N % 4 == 0 &&
+                (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && f32_tile_map(p.C, p.M, p.N, BM, &tc, &err);
     cudaError_t e;
-    if (group == 2) e = forge::launch(gemm_sm100_pair_kernel<2>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
-    else if (group == 1) e = forge::launch(gemm_sm100_pair_kernel<1>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
-    else e = forge::launch(gemm_sm100_pair_kernel<0>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, p);
+    if (group == 2) e = forge::launch(gemm_sm100_pair_kernel<2>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
+    else if (group == 1) e = forge::launch(gemm_sm100_pair_kernel<1>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
+    else e = forge::launch(gemm_sm100_pair_kernel<0>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
     return forge::check_launch("gemm_sm100 (two CTAs per tile)", e);
 }
 

@@ -113,6 +113,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
+// 2D tile store shared -> global (the box is clipped at the tensor's edges), and the same as an fp32 add into
+// global memory, done by the L2; both join the thread's current bulk group.  c0 * element size must be a
+// multiple of 16 bytes, and neither coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of the thread's bulk groups still READ their shared memory / are still in flight
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 // 2D tile load global -> shared; c0 is the innermost (contiguous) coordinate in elements, c1 the row.
 // c0 * element size must be a multiple of 16 bytes.  Out-of-range parts of the box are filled with zeros
 // and still count toward the barrier's byte total.
@@ -318,6 +337,37 @@ inline bool bf16_tile_map(const void* ptr, int rows, int cols, int box_rows, CUt
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed"; return false; }
     if (cache.size() > 4096) cache.clear();   // activation buffers come and go; weights re-enter on next use
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+// Map of a row-major fp32 matrix [rows, cols] written in boxes of [box_rows, 32 columns] (128 bytes a row) with
+// 128-byte swizzle.  Needs a 16-byte aligned base and cols % 4 == 0.
+inline bool f32_tile_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out, const char** err) {
+    using Key = std::tuple<const void*, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key{ptr, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    auto fn = encode_fn();
+    if (!fn) { *err = "cuTensorMapEncodeTiled is not available from the driver"; return false; }
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (cols % 4) != 0) {
+        *err = "TMA needs a 16-byte aligned base and a row of a multiple of 4 floats";
+        return false;
+    }
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 4};
+    const cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed"; return false; }
+    if (cache.size() > 4096) cache.clear();
     cache.emplace(key, m);
     *out = m;
     return true;
