@@ -64,6 +64,30 @@ def test_many_tiles_per_cta_and_both_accumulators():
     k.check_kernel_status()
 
 
+@pytest.mark.parametrize("tile_n", [128, 160, 192, 224, 256, 512])
+@pytest.mark.parametrize("M,N,K", [(300, 1000, 136), (129, 36, 64), (1100, 2052, 72)])
+def test_fp32_results_through_shared_memory_and_tma(M, N, K, tile_n):
+    """The wide tiles store fp32 results with TMA and add into the residual with the L2's reduction: row and
+    column tails that a box overhangs (1000 = 31 boxes of 32 + 8 columns), a bias, and two additions into the
+    same buffer, which must count each product once."""
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    ref = R.gemm_ref(a, w, bias)
+    tol = 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
+    guard = torch.full((M + 2, N), 7.0, device=DEV)            # the rows around the result must stay as they are
+    got = k.gemm_sm100(a, w, bias=bias, tile_n=tile_n, out=guard[1:M + 1])
+    assert (got - ref).abs().max() <= tol
+    assert (guard[0] == 7.0).all() and (guard[M + 1] == 7.0).all()
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    acc = res.clone()
+    k.gemm_sm100(a, w, bias=bias, accumulate_into=acc, tile_n=tile_n)
+    assert (acc - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max()
+    k.gemm_sm100(a, w, bias=bias, accumulate_into=acc, tile_n=tile_n)
+    assert (acc - (res + 2 * ref)).abs().max() <= 2 * tol + 1e-6 * res.abs().max()
+    k.check_kernel_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (130, 257, 200), (300, 515, 1032), (2048, 2560, 2048), (1000, 384, 96),
                                    (257, 130, 4104), (4608, 4608, 128)])
 def test_two_ctas_on_one_tile(M, N, K):
