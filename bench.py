@@ -11,6 +11,8 @@ on the device; `e2e` runs the same decoding through the Python entry point (Requ
 every step copies that step's integers from pinned host memory to the device and reads sampled tokens back
 to the host (the scheduler launches step k before it reads step k-1's tokens, so the read of every step's
 result happens one step late and off the device's critical path).  Weights (2.07 GB) exceed the 126 MB L2, so every step streams them from HBM.
+The cache has pages of 64 tokens (--block-size; `config` names it): the prompt attention moves one TMA box per page,
+and a key tile of 64 is then one box.
 """
 import argparse
 import json
