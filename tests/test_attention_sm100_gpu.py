@@ -60,3 +60,29 @@ def test_long_causal_prompt_heaviest_tiles_first():
     k.check_kernel_status()
     assert n == -(-1100 * 8 // 128)
     assert (got.float()[-40:] - ref).abs().max() <= 1e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("window", [0, 400])
+def test_block_table_longer_than_one_window_and_a_far_key(window):
+    """285 pages of 8 tokens: the kernel stages block-table entries 256 at a time, so this request needs two
+    windows.  One key near the start (position 21, in the first window) and one just past the window's seam
+    (position 2050) are made to stand out for the last tokens: a page taken from the wrong window, or a
+    reference exponent moved at the wrong time, shows in those rows."""
+    from forge_b200 import kernels as k
+    nh, nkv, hd, ps = 8, 2, 64, 8
+    reqs = [(2200, 80), (0, 40)]
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=11)
+    table = group.block_table
+    for pos, gain in ((21, 3.0), (2050, 2.0)):
+        page, slot = int(table[0, pos // ps]), pos % ps
+        for kvh in range(nkv):
+            # head kvh * 4 of the last 8 tokens looks straight at this key
+            direction = q[72:80, kvh * 4 * hd:(kvh * 4 + 1) * hd].float().mean(dim=0)
+            cache[page, 0, kvh, slot] = (gain * direction / direction.norm() * hd ** 0.5).to(torch.bfloat16)
+    ref = R.paged_attention_ref(q, cache, table, tok_req, positions, nh, nkv, hd, ps, window)
+    got, n = k.paged_attention_sm100(q, cache, group, batch, nh, nkv, hd, ps, window=window)
+    k.check_kernel_status()
+    assert n == -(-80 * 4 // 128) + -(-40 * 4 // 128)
+    err = (got.float() - ref).abs().amax(dim=1)
+    bad = torch.nonzero(~(err <= 1e-2 * ref.abs().max()))
+    assert len(bad) == 0, f"first wrong token {int(bad[0])} (request {int(tok_req[bad[0]])}, position {int(positions[bad[0]])})"
