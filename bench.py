@@ -93,7 +93,7 @@ def main():
     a = ap.parse_args()
     if a.impl == "reference":
         # Cyxuan0311/Forge is a C++/CUDA project whose build fetches pybind11 over the network and whose
-        # kernels target sm_86/89; see DESIGN.md for the record of the offline install attempt.
+        # kernels target sm_86/89: an offline install fails in cmake, so there is nothing to import and run.
         print(json.dumps({"impl": "reference", "unavailable":
                           "Forge's pip build needs CMake FetchContent (network) and has no sm_100 target; "
                           "the offline install did not produce an importable module"}))
