@@ -754,8 +754,12 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                             if (p.epilogue == EPI_STORE_BF16) {
                                 reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
                             } else {
+                                // the residual add is a reduction that the L2 performs: nothing is read back, so
+                                // the kernel's last step is a store either way (one add per element: the order
+                                // of CTAs does not matter)
                                 float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
-                                *dst = p.epilogue == EPI_ACCUM_F32 ? *dst + v : v;
+                                if (p.epilogue == EPI_ACCUM_F32) atomicAdd(dst, v);
+                                else *dst = v;
                             }
                         }
                     }
@@ -809,16 +813,18 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             } else {
                 float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
                 const bool accum = p.epilogue == EPI_ACCUM_F32;
+                // (the residual add is a reduction that the L2 performs: nothing is read back)
                 if (n + 3 < p.N && (p.N & 3) == 0) {
-                    float4 o = make_float4(v[0], v[1], v[2], v[3]);
-                    if (accum) {
-                        const float4 old = *reinterpret_cast<const float4*>(dst);
-                        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                    }
-                    *reinterpret_cast<float4*>(dst) = o;
+                    const float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                    if (accum) atomicAdd(reinterpret_cast<float4*>(dst), o);
+                    else *reinterpret_cast<float4*>(dst) = o;
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) if (n + i < p.N) dst[i] = accum ? dst[i] + v[i] : v[i];
+                    for (int i = 0; i < 4; ++i) {
+                        if (n + i >= p.N) continue;
+                        if (accum) atomicAdd(dst + i, v[i]);
+                        else dst[i] = v[i];
+                    }
                 }
             }
         }
