@@ -13,6 +13,20 @@ from .. import kernels
 from .batch import GroupBatch, StepBatch
 
 
+class _OnDeviceOnly:
+    """Stands where a batch keeps host copies of per-step numbers.  A graph is captured once and replayed for
+    later steps, so a part that planned from host numbers would replay the captured step's; every use raises."""
+
+    def __init__(self, what):
+        self._what = what
+
+    def _refuse(self, *a, **k):
+        raise RuntimeError(f"StepBatch.{self._what} does not exist in a decode step that a CUDA graph replays: "
+                           "read the batch's device tensor instead, or leave graph_safe off for this part")
+
+    __getitem__ = __iter__ = __len__ = __bool__ = __contains__ = _refuse
+
+
 class DecodeGraph:
     def __init__(self, runner, num_requests, max_context=None):
         """max_context: the longest context (tokens cached + 1) any replay of this graph will see; the attention
@@ -42,7 +56,8 @@ class DecodeGraph:
             num_tokens=S, num_requests=S, num_logits=S, token_ids=v(0, S), positions=v(S, S),
             tok_req=ar[:S].contiguous(), q_start=ar, context_before=v(2 * S, S), slots=v(3 * S, S),
             logits_rows=ar[:S].contiguous(), groups=groups, status=runner.status,
-            host_q_start=list(range(S + 1)), host_context_before=[0] * S, host_slots=[0] * S)
+            host_q_start=list(range(S + 1)), host_context_before=_OnDeviceOnly("host_context_before"),
+            host_slots=_OnDeviceOnly("host_slots"))
         self.batch.decode_only = True
         self.batch.max_context = int(max_context or runner.plan.max_positions)
         self.graph = None

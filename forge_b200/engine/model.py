@@ -9,6 +9,7 @@ import torch
 
 from ..config.base import ConfigError, ModelPlan
 from ..parts import Runtime, build_block, build_part
+from ..parts.base import is_graph_safe
 from ..weights.loader import WeightError
 
 
@@ -56,10 +57,15 @@ class Model:
                         raise WeightError(where, wrong=[f"{prefix + head_name}: embeddings are tied but the file's "
                                                         "output head differs from the embedding table"])
                     mine = {}
-                part.bind(mine, shared_table=self.embedding.table)
+                part.bind(mine, shared_table=self.embedding.output_table())
             else:
                 part.bind(mine)
         self.loaded = True
+
+    def graph_safe(self):
+        """True if every part that a step runs declares that a CUDA graph may capture it."""
+        parts = [self.embedding, self.final_norm, self.lm_head] + [self.blocks[i] for i in set(self.plan.schedule)]
+        return all(is_graph_safe(p) for p in parts)
 
     # ---------------------------------------------------------------------------------- cache needs
     # Caches belong to positions of the schedule, not to layers: a layer that runs twice shares its weights

@@ -11,6 +11,7 @@ import torch
 from ..cache import CacheStorage, OutOfPages, bytes_per_page
 from ..config import load_config
 from ..parts import Runtime
+from ..parts.base import is_graph_safe
 from ..weights.loader import load_tensors
 from .batch import StepEntry, build_step_batch, layout_step
 from .decode_graph import DecodeGraph
@@ -36,10 +37,16 @@ def resolve_dtype(dtype):
 
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
-                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True):
+                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True,
+                 max_tokens_per_step=None, max_decode_graphs=16):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
         ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the
-        free device memory holds, capped by max_requests * max positions)."""
+        free device memory holds, capped by max_requests * max positions).  ``cuda_graphs``: replay decode
+        steps as CUDA graphs where every part of the model allows it (``Part.graph_safe``); a model with a part
+        that does not takes the ordinary step, whatever this says.  ``max_tokens_per_step``: a step with more
+        tokens is refused (None: no limit); the step's activations live in a workspace of that many rows.
+        ``max_decode_graphs``: how many captured graphs (one per batch size and context bucket) are kept; the
+        one used longest ago goes first."""
         if not torch.cuda.is_available():
             raise RuntimeError("forge_b200 runs on a CUDA device (B200, sm_100a) only; no device is visible")
         self.device = torch.device(device)
@@ -72,9 +79,18 @@ class ModelRunner:
         self.storage = CacheStorage(specs, cfrom, self.page_size, self.num_pages, self.max_requests, self.dtype,
                                     self.device)
         self.manager = self.storage.manager
-        self.max_pages_per_request = min(self.num_pages, -(-self.plan.max_positions // self.page_size))
+        # width of a request's block table.  A group that keeps every key can never give a request more
+        # pages than its pool has; a windowed group hands old pages back but its table keeps its logical
+        # length (-1 where a page went), so it must reach the model's last position.
+        self.max_pages_per_request = -(-self.plan.max_positions // self.page_size)
+        if all(g.window is None for g in self.manager.groups.values()):
+            self.max_pages_per_request = min(self.num_pages, self.max_pages_per_request)
+        self.max_tokens_per_step = None if max_tokens_per_step is None else int(max_tokens_per_step)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.cuda_graphs = bool(cuda_graphs)
+        # decode steps replay a captured graph only if every part of the model says that it may be captured
+        self.graph_safe = self.model.graph_safe()
+        self.cuda_graphs = bool(cuda_graphs) and self.graph_safe
+        self.max_decode_graphs = max(1, int(max_decode_graphs))
         self._decode_graphs = {}
         self._last_greedy = None
         self._token_rings = {}
@@ -94,6 +110,9 @@ class ModelRunner:
         V, limit = self.plan.vocab_size, self.plan.max_positions
         live = set(self.manager.live_requests())
         seen = set()
+        total = sum(len(e.tokens) for e in entries)
+        if self.max_tokens_per_step is not None and total > self.max_tokens_per_step:
+            raise StepError(f"the step brings {total} tokens, the runner was made for {self.max_tokens_per_step} a step")
         for e in entries:
             if e.req_id not in live:
                 raise StepError(f"request {e.req_id!r} was not admitted")
@@ -105,17 +124,23 @@ class ModelRunner:
             if not set(map(type, e.tokens)) <= {int} or min(e.tokens) < 0 or max(e.tokens) >= V:
                 bad = next((t for t in e.tokens if type(t) is not int or not 0 <= t < V), e.tokens[0])
                 raise StepError(f"request {e.req_id!r}: token id {bad!r} is outside [0, {V})")
-            if self.manager.num_tokens(e.req_id) + len(e.tokens) > limit:
+            after = self.manager.num_tokens(e.req_id) + len(e.tokens)
+            if after > limit:
                 raise StepError(f"request {e.req_id!r} would exceed the model's {limit} positions")
+            if -(-after // self.page_size) > self.max_pages_per_request:
+                raise OutOfPages(f"request {e.req_id!r} would hold {-(-after // self.page_size)} pages; block tables "
+                                 f"have room for {self.max_pages_per_request}")
 
     def step(self, entries):
         """entries: list of StepEntry.  Runs exactly the tokens given, as one batch; returns fp32 logits
         [number of wanted places, vocab] on the device in the order of the entries and of their ``want``
-        (None if nothing is wanted).  Raises StepError / OutOfPages before anything has run."""
+        (None if nothing is wanted).  The tensor is the caller's: no later step writes into it.  Raises
+        StepError / OutOfPages before anything has run."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self.validate(entries)
         if self.cuda_graphs and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
-            return self.decode_step(entries)[0]
+            # the graph's own logits buffer is rewritten by the next replay: hand out a copy
+            return self.decode_step(entries)[0].clone()
         batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
         self.storage.zero_state_slots(self.manager.take_fresh_slots())
         logits = self.model.forward(batch, self.storage.layers)
@@ -137,9 +162,15 @@ class ModelRunner:
         while bucket < longest:
             bucket *= 2
         bucket = min(bucket, self.plan.max_positions)
-        g = self._decode_graphs.get((S, bucket))
+        if not self.graph_safe:
+            raise StepError("this model has a part that may not be captured in a CUDA graph; use step()")
+        g = self._decode_graphs.pop((S, bucket), None)
         if g is None:
-            g = self._decode_graphs[(S, bucket)] = DecodeGraph(self, S, max_context=bucket)
+            while len(self._decode_graphs) >= self.max_decode_graphs:      # the one used longest ago goes
+                self._decode_graphs.pop(next(iter(self._decode_graphs)))
+                self._last_greedy = None
+            g = DecodeGraph(self, S, max_context=bucket)
+        self._decode_graphs[(S, bucket)] = g                               # most recently used last
         hs = layout_step(entries, self.manager)
         self.storage.zero_state_slots(self.manager.take_fresh_slots())
         prev = self._last_greedy if tokens_on_device else None

@@ -16,6 +16,11 @@ DEFAULT_NAMES = {"q": "self_attn.q_proj", "k": "self_attn.k_proj", "v": "self_at
 
 
 class GQAAttention(Part):
+    graph_safe = True       # request boundaries, positions and tables are read from the batch's device tensors
+
+    def sub_parts(self):
+        return [self.position]
+
     def __init__(self, rt, hidden_size, num_heads, num_kv_heads, head_dim, position, qkv_bias=False, out_bias=False,
                  window=None, names=None):
         self.rt = rt
@@ -51,24 +56,29 @@ class GQAAttention(Part):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
     def _decode_in_one_kernel(self, batch, cache):
-        """A step of one new token per request, with a position encoding whose kernel is the rotary one (or
-        none): encoding, cache write and attention run as one launch."""
+        """A step of one new token per request, with a position part that offers its encoding to the decode
+        kernel (``fused_decode``): encoding, cache write and attention run as one launch.  Returns the
+        position part's parameters for that kernel, or None."""
         if batch.num_tokens != batch.num_requests or not cache.writable or self.rt.full_precision:
-            return False
-        if not (hasattr(self.position, "rotary") and hasattr(self.position, "theta")):
-            return False
+            return None
+        offer = getattr(self.position, "fused_decode", None)
+        params = offer() if offer is not None else None
+        if params is None:
+            return None
         max_ctx = getattr(batch, "max_context", None) or (max(batch.host_context_before) + 1)
-        return kernels.decode_attention_fused_supports(self.rt.dtype, self.head_dim, self.num_heads // self.num_kv_heads,
-                                                       batch.num_requests, self.num_kv_heads, max_ctx)
+        ok = kernels.decode_attention_fused_supports(self.rt.dtype, self.head_dim, self.num_heads // self.num_kv_heads,
+                                                     batch.num_requests, self.num_kv_heads, max_ctx)
+        return params if ok else None
 
     def forward(self, x, batch, cache, residual):
         """x [T,H] normed input; cache: the layer's KV cache view; adds the output projection into residual."""
         g = batch.groups[cache.group]
         qkv = self.qkv.forward(x)                                           # fp32 [T,(NH+2NKV)*HD]
-        if self._decode_in_one_kernel(batch, cache):
+        fused = self._decode_in_one_kernel(batch, cache)
+        if fused is not None:
             o = kernels.decode_attention_fused(qkv, cache.kv, g.block_table, batch.positions, g.slot_mapping,
                                                self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
-                                               self.position.theta, rotary=self.position.rotary, window=self.window,
+                                               fused["theta"], rotary=fused["rotary"], window=self.window,
                                                scale=self.scale,
                                                max_context=getattr(batch, "max_context", None) or max(batch.host_context_before) + 1)
             self.o.forward(o, accumulate_into=residual)

@@ -70,6 +70,14 @@ def registered_parts(category):
     return sorted(_REGISTRY[category])
 
 
+def is_graph_safe(part):
+    """True if the part and every part inside it declare ``graph_safe``."""
+    if not getattr(part, "graph_safe", False):
+        return False
+    subs = getattr(part, "sub_parts", None)
+    return all(is_graph_safe(p) for p in (subs() if subs else []))
+
+
 def build_part(category, spec: PartSpec, rt: Runtime):
     try:
         cls = _REGISTRY[category][spec.kind]
@@ -79,7 +87,19 @@ def build_part(category, spec: PartSpec, rt: Runtime):
 
 
 class Part:
-    """Base of all parts.  Subclasses define ``tensor_specs`` and ``bind``."""
+    """Base of all parts.  Subclasses define ``tensor_specs`` and ``bind``.
+
+    ``graph_safe``: the part's ``forward`` may be captured once in a CUDA graph and replayed for later decode
+    steps.  That holds only for a part that takes everything that changes from step to step (positions,
+    request slots, block tables, context lengths) from the batch's DEVICE tensors inside its kernels, and plans
+    nothing from the batch's host lists.  A part has to say so itself; the default is no, and a model with one
+    part that does not say so decodes through the ordinary step.  A part made of other parts answers for them
+    (``sub_parts``)."""
+    graph_safe = False
+
+    def sub_parts(self):
+        """The parts this part is made of (for questions that a whole layer has to answer)."""
+        return []
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}

@@ -9,6 +9,10 @@ from .base import Part, build_part, register_part
 
 
 class PreNormBlock(Part):
+    graph_safe = True       # the arrangement itself looks at nothing of the step; its parts answer for themselves
+
+    def sub_parts(self):
+        return [self.mixer, self.feed_forward, self.norm_in, self.norm_post]
     NORM_NAMES = {"input": "input_layernorm.", "post_mixer": "post_attention_layernorm."}
 
     def __init__(self, rt, layer_spec):

@@ -11,22 +11,28 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
     def __init__(self, rt, vocab_size, hidden_size, names=None):
         self.rt, self.vocab_size, self.hidden_size = rt, vocab_size, hidden_size
         self.names = {"weight": "weight", **(names or {})}
         self.table = None
 
     def tensor_specs(self):
-        return {self.names["weight"]: TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.names["weight"]: TensorSpec((self.vocab_size, self.hidden_size), role="embedding")}
 
     def bind(self, tensors):
         self.table = self._matrix(tensors[self.names["weight"]])
+
+    def output_table(self):
+        """The table as an output head reads it when the two are tied: [vocab, hidden] in the compute dtype."""
+        return self.table
 
     def forward(self, token_ids, status=None):
         return kernels.embedding(token_ids, self.table, status=status)
 
 
 class LMHead(Part):
+    graph_safe = True
     def __init__(self, rt, vocab_size, hidden_size, tied=False, names=None):
         self.rt, self.vocab_size, self.hidden_size, self.tied = rt, vocab_size, hidden_size, bool(tied)
         self.names = {"weight": "weight", **(names or {})}

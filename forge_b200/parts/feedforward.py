@@ -13,6 +13,7 @@ DEFAULT_NAMES = {"gate": "mlp.gate_proj", "up": "mlp.up_proj", "down": "mlp.down
 
 
 class SwiGLU(Part):
+    graph_safe = True
     def __init__(self, rt, hidden_size, intermediate_size, names=None):
         self.rt, self.hidden_size, self.intermediate_size = rt, hidden_size, intermediate_size
         self.names = {**DEFAULT_NAMES, **(names or {})}

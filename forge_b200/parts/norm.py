@@ -5,6 +5,7 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
+    graph_safe = True
     def __init__(self, rt, size, eps, names=None):
         self.rt, self.size, self.eps = rt, int(size), float(eps)
         self.names = {"weight": "weight", **(names or {})}

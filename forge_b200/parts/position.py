@@ -3,6 +3,11 @@
 "rope": half-split rotary embedding of the whole head (reference: src/operators/cuda/cuda_rope.cu:8-34,
 generic_engine.cpp:428-433).  "none": no encoding (keys are stored as projected).  Both are one fused
 kernel that also writes k and v into the paged cache.
+
+A position part may also offer its encoding to the decode step's one-launch attention kernel, which rotates
+q and k itself: ``fused_decode()`` returns the kernel's parameters, or None.  Only a part whose
+``encode_and_store`` computes exactly what that kernel computes may return them; a subclass with other
+arithmetic inherits None and keeps one path for prompt and decode steps.
 """
 from .. import kernels
 from .base import Part, register_part
@@ -10,15 +15,24 @@ from .base import Part, register_part
 
 class RotaryEmbedding(Part):
     rotary = True
+    graph_safe = True       # angles come from ``positions`` on the device
 
     def __init__(self, rt, head_dim, theta=10000.0):
         self.rt, self.head_dim, self.theta = rt, int(head_dim), float(theta)
 
+    def fused_decode(self):
+        """{"theta", "rotary"} for the decode attention kernel that encodes by itself, or None.  The kernel
+        hard-wires the half-split rotation of the whole head, so only the two stock classes offer it."""
+        if type(self) not in (RotaryEmbedding, NoPosition):
+            return None
+        return {"theta": self.theta, "rotary": self.rotary}
+
     def encode_and_store(self, qkv, positions, slot_mapping, kv_cache, num_heads, num_kv_heads, page_size, batch=None):
         """``batch`` (optional): the step's batch; its ``attention_plan`` dict keeps the step's cos/sin table so
-        that it is computed once per step, not once per layer."""
+        that it is computed once per step, not once per layer.  A batch that a CUDA graph replays keeps no
+        table: the table of the captured step would be replayed with every later step's positions."""
         table = None
-        if self.rotary and batch is not None and qkv.shape[0] >= 64:
+        if self.rotary and batch is not None and qkv.shape[0] >= 64 and not getattr(batch, "decode_only", False):
             key = ("rope", self.head_dim, self.theta)
             table = batch.attention_plan.get(key)
             if table is None:

@@ -37,7 +37,7 @@ class TensorSpec:
     shape: Tuple[int, ...]
     required: bool = True
     integer: bool = False        # an integer table (kept int32) rather than floating-point weights
-    role: str = "matrix"         # "matrix" | "norm" | "bias": how random weights are drawn for it
+    role: str = "matrix"         # "matrix" | "embedding" | "norm" | "bias": how random weights are drawn for it
 
 
 def check_tensors(where, expected: Dict[str, TensorSpec], present: Dict[str, Tuple[Tuple[int, ...], torch.dtype]]):

@@ -34,7 +34,7 @@ def random_tensors(config, seed=0, std=0.02, embed_std=None, norm_std=0.0, bias_
             s = std
             if spec.role == "bias" and bias_std is not None:
                 s = bias_std
-            if "embed" in name and embed_std is not None:
+            if spec.role == "embedding" and embed_std is not None:
                 s = embed_std
             out[name] = (torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * s).to(dtype)
     return out

@@ -12,18 +12,25 @@ import numpy as np
 # vocab_size >= hidden_size (an embedding table with shape[0] < shape[1] is read as transposed,
 # src/operators/cpu/embedding.cpp:248-260).
 GOLDEN_CONFIGS = {
-    # the two differ in every size and option
-    "gqa_untied": dict(vocab_size=72, hidden_size=64, intermediate_size=88, num_hidden_layers=2,
+    # the first two differ in every size and option
+    "mha_untied": dict(vocab_size=72, hidden_size=64, intermediate_size=88, num_hidden_layers=2,
                        num_attention_heads=5, num_key_value_heads=5, head_dim=8, rope_theta=10000.0,
                        rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=False),
     "mqa_tied_bias": dict(vocab_size=128, hidden_size=96, intermediate_size=80, num_hidden_layers=3,
                           num_attention_heads=3, num_key_value_heads=1, head_dim=16, rope_theta=500000.0,
                           rms_norm_eps=1e-6, tie_word_embeddings=True, attention_bias=True),
+    # 1 < kv heads < heads: with as many kv heads as heads, or with one, "h // group" and "h % kv heads"
+    # pick the same kv head; only a true group tells them apart (src/operators/cpu/attention.cpp:464).
+    # A large eps, so that the reference's use of it shows in the logits as well.
+    "gqa_6_2_bias": dict(vocab_size=100, hidden_size=64, intermediate_size=72, num_hidden_layers=2,
+                         num_attention_heads=6, num_key_value_heads=2, head_dim=8, rope_theta=30000.0,
+                         rms_norm_eps=1e-2, tie_word_embeddings=False, attention_bias=True),
 }
 # steps of (start_pos, tokens): a prefill and then single tokens, as the reference's own
 # incremental tests do (tests/test_operators.py:80-98)
 GOLDEN_STEPS = {
-    "gqa_untied": [(0, [3, 70, 11, 25, 8, 41]), (6, [17]), (7, [2])],
+    "mha_untied": [(0, [3, 70, 11, 25, 8, 41]), (6, [17]), (7, [2])],
+    "gqa_6_2_bias": [(0, [9, 99, 4, 57, 23, 0, 61]), (7, [12]), (8, [88]), (9, [30])],
     "mqa_tied_bias": [(0, [5, 9, 127, 0, 31]), (5, [44]), (6, [7]), (7, [7])],
 }
 

@@ -16,10 +16,11 @@ from plain.llama import PlainLlama
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"A": [70, 129, 33, 200, 64, 97], "B": [150, 47, 16, 240, 81]}
+# C: with 4 query heads per kv head a request brings 128 rows from 32 tokens on; its lengths lie on both sides
+LENGTHS = {"A": [70, 129, 33, 200, 64, 97], "B": [150, 47, 16, 240, 81], "C": [300, 20, 131, 700, 45, 257]}
 
 
-@pytest.fixture(scope="module", params=["A", "B"])
+@pytest.fixture(scope="module", params=["A", "B", "C"])
 def tiny(request, tmp_path_factory):
     name = request.param
     d = make_model_dir(tmp_path_factory, name)
@@ -85,7 +86,7 @@ def test_schedules_equal_plain(tiny, dtype, schedule):
 def test_page_size_does_not_matter(tiny, dtype):
     name, d, plain, reqs, want = tiny
     small = {k: reqs[k] for k in list(reqs)[:3]}
-    for ps in (8, 64):
+    for ps in (8, 16, 64):
         steps = schedules.mixed(small, max_live=3)
         runner = make_runner(d, dtype, schedules.peak_tokens(small, steps, round_to=ps), page_size=ps)
         got = run_schedule(runner, small, steps)
@@ -97,7 +98,7 @@ def test_page_size_does_not_matter(tiny, dtype):
 def test_long_decoding(tiny, dtype):
     """A 3-token prompt, then hundreds of tokens one by one."""
     name, d, plain, reqs, want = tiny
-    n = 400 if name == "A" else 520
+    n = {"A": 400, "B": 520, "C": 330}[name]
     toks = random_tokens(n, TINY[name]["vocab_size"], seed=77)
     ref = plain.logits(toks).float()
     runner = make_runner(d, dtype, -(-n // 16) * 16)
@@ -151,6 +152,26 @@ def test_step_refuses_bad_input(tiny):
     assert runner.manager.num_tokens("a") == 0
     assert runner.step([StepEntry("a", [1] * 32, [31])]) is not None
     runner.manager.check()
+
+
+def test_fp32_schedules_are_bitwise_equal(tiny):
+    """In 32-bit every sum runs in a fixed order (matrix products over k, attention over a token's keys, the
+    norms' reduction tree) whatever the step looks like, so the logits at a position must be the SAME BITS
+    however the tokens were cut into steps, whatever else was in the batch and wherever the pages lie."""
+    name, d, plain, reqs, want = tiny
+    results = {}
+    for schedule in ("whole", "last_one_by_one", "changing_portions", "mixed"):
+        steps = getattr(schedules, schedule)(reqs)
+        for ps in ((16, 64) if schedule == "mixed" else (16,)):
+            runner = make_runner(d, "float32", schedules.peak_tokens(reqs, steps, round_to=ps), page_size=ps)
+            results[(schedule, ps)] = run_schedule(runner, reqs, steps)
+            del runner
+    base = results[("whole", 16)]
+    for key, got in results.items():
+        for rid in reqs:
+            same = (got[rid] == base[rid]).all(dim=1)
+            assert bool(same.all()), (f"{key}: request {rid} position {int(torch.nonzero(~same)[0])} differs from the "
+                                      f"whole-prompt run by {float((got[rid] - base[rid]).abs().max()):.3g}")
 
 
 def _trace_lines(reqs, steps):

@@ -273,8 +273,10 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype,
     assert "model.layers.1.mixer.proj.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
     reqs = {f"t{i}": random_tokens(n, cfg.vocab_size, seed=30 + i) for i, n in enumerate([41, 64, 23, 90])}
     want = {rid: plain_toy_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
-    # the toy mixer plans its work from host lists, so its steps cannot be replayed as a CUDA graph
-    runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=240, max_requests=3, cuda_graphs=False)
+    # the toy mixer plans its work from host lists and does not declare itself graph_safe: the runner finds
+    # that out by itself and decodes through the ordinary step
+    runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=240, max_requests=3)
+    assert runner.graph_safe is False and runner.cuda_graphs is False
     groups = set(runner.manager.groups)
     assert groups == {"kv5x8_full", "kv5x8_win7"}, groups          # two needs, two pools; the toy layer has none
     for steps in (schedules.whole(reqs), schedules.changing_portions(reqs), schedules.mixed(reqs, max_live=3)):
@@ -294,6 +296,21 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype,
         for rid in reqs:
             assert max_rel_err(got[rid], want[rid]) <= TOL[dtype], rid
         assert runner.manager.num_free_pages() == {g: runner.num_pages for g in groups}
+    del runner
+    # and through the Python entry point with its default settings: prompt, then tokens one by one
+    import forge_b200 as forge
+    from helpers import assert_greedy_follows_plain
+    model = forge.Model(d, dtype=dtype, block_size=8, max_num_seqs=3, cache_tokens=240)
+    prompt = reqs["t2"][:11]
+    out = model.generate(prompt, max_new_tokens=14, do_sample=False)
+    assert out["num_generated_tokens"] == 14
+    assert_greedy_follows_plain(lambda ids: plain_toy_logits(cfg, w, ids), prompt, out["token_ids"], TOL[dtype], "toy")
+    # decoding far beyond what the windowed group's pool could hold if its pages were not given back
+    ctx = model.create_context()
+    long = random_tokens(200, cfg.vocab_size, seed=77)
+    got_long = torch.cat([torch.from_numpy(ctx.forward(long[:9], 0))] +
+                         [torch.from_numpy(ctx.forward([t], 9 + i)) for i, t in enumerate(long[9:])])
+    assert max_rel_err(got_long, plain_toy_logits(cfg, w, long).float()) <= TOL[dtype]
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -313,10 +330,21 @@ def _toy_part_classes():
     from forge_b200.parts import Part
     from forge_b200.weights import TensorSpec
 
+    from forge_b200.parts.position import RotaryEmbedding
+
+    class HalfSpeedRope(RotaryEmbedding):
+        """A subclass of the stock rotary part with other arithmetic (positions advance at half speed).  It
+        inherits ``theta`` and ``rotary``, but not the offer to the one-launch decode kernel, which would
+        rotate by the stock angles."""
+
+        def encode_and_store(self, qkv, positions, *args, **kwargs):
+            return super().encode_and_store(qkv, positions // 2, *args, **kwargs)
+
     class InterleavedRope(Part):
         """A position encoding the framework does not have.  It meets the interface of the category: rotate q
         and k, put k and v into the pages at slot_mapping (cache layout [pages, 2, kv heads, page, head]),
-        return q."""
+        return q.  Everything it reads of the step is a device tensor, so it may be captured."""
+        graph_safe = True
 
         def __init__(self, rt, head_dim, theta):
             self.rt, self.head_dim, self.theta = rt, head_dim, theta
@@ -336,6 +364,7 @@ def _toy_part_classes():
     class RoutedFeedForward(Part):
         """residual += sum_e softmax(x . Wr^T)_e * W2_e . relu(W1_e . x): the router's logits and weights in
         32-bit, every expert weighted (no hard choice, so the result is continuous in x)."""
+        graph_safe = True
 
         def __init__(self, rt, hidden_size, expert_size, num_experts):
             self.rt, self.h, self.f, self.e = rt, hidden_size, expert_size, num_experts
@@ -359,7 +388,7 @@ def _toy_part_classes():
                 y = torch.relu(x @ self.w1[i].t()) @ self.w2[i].t()
                 residual += gate[:, i:i + 1] * y.float()
 
-    return InterleavedRope, RoutedFeedForward
+    return InterleavedRope, RoutedFeedForward, HalfSpeedRope
 
 
 @dataclass(frozen=True)
@@ -375,6 +404,7 @@ class Toy2Config:
     eps: float = 1e-6
     theta: float = 50.0
     max_position_embeddings: int = 192
+    second_position: str = "rope"
 
     @classmethod
     def from_dict(cls, d, architecture="Toy2ForCausalLM"):
@@ -395,7 +425,7 @@ class Toy2Config:
             LayerSpec("pre_norm", attn(PartSpec("toy_interleaved_rope", {"head_dim": self.head_dim, "theta": self.theta})),
                       PartSpec("toy_routed", {"hidden_size": self.hidden_size, "expert_size": self.expert_size,
                                               "num_experts": self.num_experts}), norms, "model.layers.0."),
-            LayerSpec("pre_norm", attn(PartSpec("rope", {"head_dim": self.head_dim, "theta": self.theta})),
+            LayerSpec("pre_norm", attn(PartSpec(self.second_position, {"head_dim": self.head_dim, "theta": self.theta})),
                       PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size}),
                       norms, "model.layers.1."),
         ]
@@ -409,7 +439,8 @@ class Toy2Config:
 def plain_toy2_logits(cfg, w, ids):
     T, pos = len(ids), torch.arange(len(ids))
     h = P.embedding(torch.tensor(ids), w["model.embed_tokens.weight"])
-    for layer, enc in ((0, _interleaved_rope), (1, P.rope)):
+    second = P.rope if cfg.second_position == "rope" else (lambda x, pos, theta: P.rope(x, pos // 2, theta))
+    for layer, enc in ((0, _interleaved_rope), (1, second)):
         p = f"model.layers.{layer}."
         x = P.rms_norm(h, w[p + "input_layernorm.weight"], cfg.eps)
         q = enc(P.linear(x, w[p + "self_attn.q_proj.weight"]).view(T, cfg.num_heads, cfg.head_dim), pos, cfg.theta)
@@ -427,29 +458,36 @@ def plain_toy2_logits(cfg, w, ids):
     return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg.eps), w["model.embed_tokens.weight"])
 
 
+@pytest.mark.parametrize("second_position", ["rope", "toy_half_speed_rope"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_feed_forward_with_a_router_and_toy_position_encoding(dtype, tmp_path):
+def test_toy_feed_forward_with_a_router_and_toy_position_encoding(dtype, second_position, tmp_path):
     """A feed-forward with routing and a position encoding of another kind, registered from this file, in one
-    layer beside a stock layer; embeddings tied.  Whole, in changing portions and mixed with page reuse."""
+    layer beside a stock layer; embeddings tied.  Whole, in changing portions (whose single tokens replay the
+    decode graph, the toy parts inside it) and mixed with page reuse.  With ``toy_half_speed_rope`` the second
+    layer's position part is a SUBCLASS of the stock rotary part with other arithmetic: its decode steps must
+    run its own arithmetic too, not the stock rotation of the one-launch decode kernel."""
     import schedules
     from forge_b200.config import register_architecture, unregister_architecture
     from forge_b200.engine import ModelRunner, StepEntry
     from forge_b200.parts import register_part, unregister_part
     from forge_b200.weights import write_random_model
     from plain.safetensors_reader import read_safetensors
-    rope_cls, ffn_cls = _toy_part_classes()
+    rope_cls, ffn_cls, half_cls = _toy_part_classes()
     register_part("position", "toy_interleaved_rope", rope_cls)
+    register_part("position", "toy_half_speed_rope", half_cls)
     register_part("feed_forward", "toy_routed", ffn_cls)
     register_architecture("Toy2ForCausalLM", Toy2Config)
     try:
-        cfg = Toy2Config()
+        cfg = Toy2Config(second_position=second_position)
         d = write_random_model(cfg, str(tmp_path / "toy2"), seed=7, std=0.12, embed_std=0.6, norm_std=0.15)
         w = {k: torch.from_numpy(v).double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
         assert "model.layers.0.moe.experts.2.w2.weight" in w and "lm_head.weight" not in w
         reqs = {f"t{i}": random_tokens(n, cfg.vocab_size, seed=50 + i) for i, n in enumerate([37, 70, 19, 52])}
         want = {rid: plain_toy2_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
-        runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=200, max_requests=3, cuda_graphs=False)
-        for steps in (schedules.whole(reqs), schedules.changing_portions(reqs), schedules.mixed(reqs, max_live=3)):
+        runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=200, max_requests=3)
+        assert runner.graph_safe and runner.cuda_graphs        # both toy parts read device tensors only
+        for steps in (schedules.whole(reqs), schedules.changing_portions(reqs), schedules.last_one_by_one(reqs, tail=12),
+                      schedules.mixed(reqs, max_live=3)):
             got = {rid: torch.zeros(len(t), cfg.vocab_size) for rid, t in reqs.items()}
             for entries, end in steps:
                 for rid, p, n in entries:
@@ -467,5 +505,104 @@ def test_toy_feed_forward_with_a_router_and_toy_position_encoding(dtype, tmp_pat
                 assert max_rel_err(got[rid], want[rid]) <= TOL[dtype], rid
     finally:
         unregister_part("position", "toy_interleaved_rope")
+        unregister_part("position", "toy_half_speed_rope")
         unregister_part("feed_forward", "toy_routed")
         unregister_architecture("Toy2ForCausalLM")
+
+
+# ---------------------------------------------------------------------------------------------------
+# A model whose every layer keeps a window only: its requests may run far past what the pool holds.
+
+@dataclass(frozen=True)
+class ToyWindowConfig:
+    vocab_size: int = 53
+    hidden_size: int = 32
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 16
+    intermediate_size: int = 40
+    eps: float = 1e-5
+    theta: float = 200.0
+    window: int = 11
+    num_layers: int = 2
+    max_position_embeddings: int = 512
+
+    @classmethod
+    def from_dict(cls, d, architecture="ToyWindowForCausalLM"):
+        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(asdict(self), architectures=["ToyWindowForCausalLM"])
+
+    def plan(self):
+        from forge_b200.config import LayerSpec, ModelPlan, PartSpec
+        norm = PartSpec("rmsnorm", {"size": self.hidden_size, "eps": self.eps})
+        mixer = PartSpec("attention", {"hidden_size": self.hidden_size, "num_heads": self.num_heads,
+                                       "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "window": self.window,
+                                       "position": PartSpec("rope", {"head_dim": self.head_dim, "theta": self.theta})})
+        ffn = PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size})
+        layers = [LayerSpec("pre_norm", mixer, ffn, {"input": norm, "post_mixer": norm}, f"model.layers.{i}.")
+                  for i in range(self.num_layers)]
+        return ModelPlan(hidden_size=self.hidden_size, vocab_size=self.vocab_size, max_positions=self.max_position_embeddings,
+                         embedding=PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}),
+                         final_norm=norm,
+                         lm_head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied": True}),
+                         layers=layers, schedule=list(range(self.num_layers)))
+
+
+def plain_window_logits(cfg, w, ids):
+    T, pos = len(ids), torch.arange(len(ids))
+    h = P.embedding(torch.tensor(ids), w["model.embed_tokens.weight"])
+    for layer in range(cfg.num_layers):
+        p = f"model.layers.{layer}."
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], cfg.eps)
+        q = P.rope(P.linear(x, w[p + "self_attn.q_proj.weight"]).view(T, cfg.num_heads, cfg.head_dim), pos, cfg.theta)
+        k = P.rope(P.linear(x, w[p + "self_attn.k_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim), pos, cfg.theta)
+        v = P.linear(x, w[p + "self_attn.v_proj.weight"]).view(T, cfg.num_kv_heads, cfg.head_dim)
+        h = h + P.linear(P.attention(q, k, v, window=cfg.window).reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+        x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg.eps)
+        h = h + P.swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg.eps), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_model_decodes_past_the_pools_capacity(dtype, tmp_path):
+    """Four pages of eight tokens; a request of 300 tokens.  Pages that the window has passed are given back
+    and taken again, the block table keeps its logical length, and a step that the table cannot hold is
+    refused before anything is appended."""
+    import schedules
+    from forge_b200.cache import OutOfPages
+    from forge_b200.config import register_architecture, unregister_architecture
+    from forge_b200.engine import ModelRunner, StepEntry
+    from forge_b200.weights import write_random_model
+    from plain.safetensors_reader import read_safetensors
+    register_architecture("ToyWindowForCausalLM", ToyWindowConfig)
+    try:
+        cfg = ToyWindowConfig()
+        d = write_random_model(cfg, str(tmp_path / "toywin"), seed=9, std=0.15, embed_std=0.6, norm_std=0.15)
+        w = {k: torch.from_numpy(v).double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
+        toks = random_tokens(300, cfg.vocab_size, seed=3)
+        want = plain_window_logits(cfg, w, toks).float()
+        runner = ModelRunner(d, dtype=dtype, page_size=8, cache_tokens=32, max_requests=2)
+        assert runner.num_pages == 4 and runner.max_pages_per_request == 64
+        runner.admit("x")
+        got = [runner.step([StepEntry("x", toks[:5], list(range(5)))]).cpu()]
+        p = 5
+        for n in (3, 1, 1, 7, 2, 1, 1, 1, 6):                      # portions beside single tokens, then decode only
+            got.append(runner.step([StepEntry("x", toks[p:p + n], list(range(n)))]).cpu())
+            p += n
+        while p < 300:
+            got.append(runner.step([StepEntry("x", [toks[p]], [0])]).cpu())
+            p += 1
+            runner.manager.check()
+        assert max_rel_err(torch.cat(got), want) <= TOL[dtype]
+        assert runner.manager.num_tokens("x") == 300 and sum(t >= 0 for t in runner.manager.block_table("x", "kv2x16_win11")) <= 3
+        # a portion that needs more pages than are free is refused, and nothing of it stays behind
+        with pytest.raises(OutOfPages):
+            runner.step([StepEntry("x", toks[:40], [])])
+        assert runner.manager.num_tokens("x") == 300
+        runner.release("x")
+        runner.manager.check()
+        assert runner.manager.num_free_pages() == {"kv2x16_win11": 4}
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")
