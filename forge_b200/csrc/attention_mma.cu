@@ -13,6 +13,7 @@
 // With num_splits > 1 the key range of a tile is cut into slices handled by different CTAs that write
 // unnormalised partial results (o, running max, running sum) to scratch memory; a second kernel merges
 // them.  That is how a single decode token with a long context fills the GPU.
+#include <initializer_list>
 #include <mma.h>
 
 #include "attention_no_alloc.h"
@@ -671,7 +672,8 @@ extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* ou
                  max_rows <= 16 ? 16 : BQ, scale * 1.4426950408889634f};
     // one warp of rows (decode tokens): small buffers, many CTAs per SM; otherwise four warps and 64-key tiles
     constexpr int smem_big = (64 + 4 * 64) * LD * 2, smem_small = (16 + 4 * 32) * LD * 2;
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_big);
         if (e == cudaSuccess)
@@ -728,16 +730,27 @@ extern "C" int forge_paged_attention_mma_static(const void* q, const void* kv, v
                                                 int max_rows, int NH, int NKV, int head_dim, int page_size,
                                                 int max_pages, int window, int num_splits, float scale,
                                                 cudaStream_t stream) {
-    if (num_tiles < 0 || NKV <= 0 || num_splits < 1 || max_rows < 1)
+    if (num_tiles < 0 || NKV <= 0 || num_splits < 1 || max_rows < 1 || max_rows > BQ)
         return forge::fail(FORGE_ERR_ARG, "paged_attention_mma_static: bad sizes tiles=%d NKV=%d splits=%d rows=%d",
                            num_tiles, NKV, num_splits, max_rows);
-    const unsigned long long rows = (unsigned long long)num_tiles * NKV * num_splits * (max_rows <= 16 ? 16 : BQ);
-    const unsigned long long need = rows * (HD + 2);
-    if (need > FORGE_ATT_STATIC_SCRATCH_FLOATS)
+    // with one slice the kernel writes its result straight to `out`: no scratch, nothing to fit, nothing to look up
+    if (num_splits == 1)
+        return forge_paged_attention_mma(q, kv, out, nullptr, nullptr, block_table, tile_req, tile_row0, q_start, ctx_before,
+                                         num_tiles, max_rows, NH, NKV, head_dim, page_size, max_pages, window, 1, scale, stream);
+    // the need is a product of four factors; each partial product is held against the array's size before the
+    // next factor comes in, so that no product wraps round and slips under the limit
+    constexpr unsigned long long kFloats = FORGE_ATT_STATIC_SCRATCH_FLOATS;
+    unsigned long long rows = (unsigned long long)(max_rows <= 16 ? 16 : BQ);
+    bool fits = true;
+    for (unsigned long long factor : {(unsigned long long)num_tiles, (unsigned long long)NKV, (unsigned long long)num_splits}) {
+        if (factor != 0 && rows > kFloats / factor) { fits = false; break; }
+        rows *= factor;
+    }
+    if (!fits || rows * (HD + 2) > kFloats)
         return forge::fail(FORGE_ERR_UNSUPPORTED,
-                           "paged_attention_mma_static: %llu scratch floats needed (tiles %d x kv heads %d x slices %d), "
+                           "paged_attention_mma_static: tiles %d x kv heads %d x slices %d x %d rows x %d scratch floats needed, "
                            "the built-in array holds %u; use fewer slices or forge_paged_attention_mma with your own scratch",
-                           need, num_tiles, NKV, num_splits, FORGE_ATT_STATIC_SCRATCH_FLOATS);
+                           num_tiles, NKV, num_splits, max_rows <= 16 ? 16 : BQ, HD + 2, FORGE_ATT_STATIC_SCRATCH_FLOATS);
     float* scratch = nullptr;
     int rc = static_scratch_for_current_device(&scratch);
     if (rc != FORGE_OK) return rc;
@@ -780,7 +793,8 @@ extern "C" int forge_decode_attention_fused(const float* qkv, void* kv, void* ou
         const long tiles = (max_context + DKV - 1) / DKV, keep = (long)S * NKV >= 16 ? 4 : 2;
         while (tiles >= 64 && p.ksplit < 4 && (long)S * NKV * p.ksplit * 2 <= sms && tiles >= keep * warps * p.ksplit * 2) p.ksplit *= 2;
     }
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, need4);
         if (e == cudaSuccess && need8 <= kLimit)

@@ -10,10 +10,13 @@
 // What the caller should know:
 //  * The scratch is a file-scope device array of FORGE_ATT_STATIC_SCRATCH_FLOATS floats (8 MiB).  Every GPU
 //    on which the library is used keeps that array until the process exits.
-//  * A call needs  tiles * NKV * num_splits * R * (head_dim + 2)  floats, R = 16 if max_rows <= 16 else 64.
-//    If that exceeds the array the call is refused with FORGE_ERR_UNSUPPORTED and a message; nothing runs.
-//  * The first call on each device looks up the array's device address (and sets the kernel's shared-memory
-//    limit).  Make that first call outside of any stream capture.  Later calls only launch kernels.
+//  * A call with num_splits > 1 needs  tiles * NKV * num_splits * R * (head_dim + 2)  floats, R = 16 if
+//    max_rows <= 16 else 64.  If that exceeds the array the call is refused with FORGE_ERR_UNSUPPORTED and a
+//    message; nothing runs.  A call with num_splits == 1 uses no scratch and is never refused for its size.
+//  * The first call on each device that needs the scratch looks up the array's address on that device, and
+//    the first call of either kind on each device sets the kernels' shared-memory limit there (both are kept
+//    per device).  Make those first calls outside of any stream capture, with the device current that the
+//    pointers belong to.  Later calls only launch kernels.
 //  * All calls share the one array, and it keeps what the last call left in it.  Nothing in it has to start
 //    at zero: every slice writes its whole partial result before the merge reads it.  But two calls that
 //    overlap on the GPU (different streams, or graphs replayed concurrently) race on it; serialise them.

@@ -423,7 +423,8 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
     if (!bf16_q_map(q, T, NH, HD, BQ / G, G, &tq, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: q: %s", err);
     if (!bf16_tile_map(kv, num_pages * 2 * NKV * page_size, HD, page_size, &tkv, &err))
         return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: cache: %s", err);
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "paged_attention_sm100: %s", cudaGetErrorString(e));

@@ -35,6 +35,22 @@ inline int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+// cudaFuncSetAttribute and the like hold for the device that was current when they ran: one "done" flag
+// per device.  current() is the flag of the device that is current now (a device index beyond the table
+// shares a flag that never stays set, so its set-up simply runs again).
+struct PerDeviceFlag {
+    static constexpr int kMax = 64;
+    bool done[kMax + 1] = {};
+    bool& current() {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMax) {
+            done[kMax] = false;
+            return done[kMax];
+        }
+        return done[dev];
+    }
+};
+
 inline int check_launch(const char* what, cudaError_t launch_result = cudaSuccess) {
     cudaError_t e = launch_result != cudaSuccess ? launch_result : cudaGetLastError();
     if (e != cudaSuccess) return fail(FORGE_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));

@@ -1081,7 +1081,8 @@ int g_num_sms = 0;
 template <int BN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, cudaStream_t stream) {
     using C = Cfg<BN>;
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
@@ -1165,7 +1166,8 @@ int few_rows_group(int K, int kb_per, int max_group) {
 template <int NT>
 int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit, cudaStream_t stream) {
     using C = SkinnyCfg<NT>;
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_sm100_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
@@ -1199,7 +1201,8 @@ constexpr long long kFlagBytes = 256 * 1024;      // flags first (zeroed by the 
 template <int NT>
 int launch_streamk(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
     using C = StreamKCfg<NT>;
-    static bool configured = false;
+    static forge::PerDeviceFlag configured_on;
+    bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_sm100_streamk_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              C::smem_bytes(C::kStages));

@@ -1,5 +1,5 @@
 """Runs ONE kernel at a named workload a few times: the small, self-contained cases that profiles/ are
-captured from (`ncu ... python -m forge_b200.kernels.cases <case>`), each also timed with CUDA events.
+captured from (`ncu ... python kernel_cases.py <case>`), each also timed with CUDA events.
 
 Cases use the layer sizes of the TinyLlama-1.1B shape: hidden 2048, 32 heads / 4 kv heads of 64, feed-forward 5632.
 """
@@ -8,7 +8,7 @@ from types import SimpleNamespace
 
 import torch
 
-from . import decode_attention_fused, gemm_sm100, paged_attention, paged_attention_mma
+from forge_b200.kernels import decode_attention_fused, gemm_sm100, paged_attention, paged_attention_mma
 
 DEV = "cuda:0"
 H, I, NH, NKV, HD, PS = 2048, 5632, 32, 4, 64, 16

@@ -82,3 +82,20 @@ def paged_attention_ref(q, kv_cache, block_table, tok_req, positions, nh, nkv, h
 
 def argmax_ref(logits):
     return torch.argmax(logits, dim=-1).to(torch.int32)
+
+
+def sample_probabilities_ref(row, temperature, top_k, top_p):
+    """The reference's pipeline (src/inference/sampler.cpp:197-316) in float64; returns kept probabilities."""
+    p = torch.softmax(row.double() / temperature, dim=0)
+    if top_k > 0:
+        kth = torch.topk(p, top_k).values[-1]
+        p = torch.where(p >= kth, p, torch.zeros_like(p))
+        p = p / p.sum()
+    if top_p < 1.0:
+        sp, _ = torch.sort(p, descending=True)
+        c = torch.cumsum(sp, 0)
+        cutoff = int((c > top_p).nonzero()[0]) + 1 if bool((c > top_p).any()) else p.numel()
+        thr = sp[cutoff - 1]
+        p = torch.where(p >= thr, p, torch.zeros_like(p))
+        p = p / p.sum()
+    return p

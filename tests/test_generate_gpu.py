@@ -6,7 +6,7 @@ import sys
 import pytest
 import torch
 
-from helpers import TINY, TOL, make_model_dir, max_rel_err, random_tokens
+from helpers import TINY, TOL, assert_greedy_follows_plain, make_model_dir, max_rel_err, random_tokens
 from plain.llama import PlainLlama
 
 pytestmark = pytest.mark.gpu
@@ -117,8 +117,12 @@ def test_scheduler_many_requests_few_pages(tiny, dtype):
         got = done[rid].output_tokens
         if dtype == "float32":
             assert got == want
-        else:   # a bf16 near-tie may flip when the batch around a request changes; most requests agree wholly
-            assert got[:3] == want[:3]
+        else:
+            # a bf16 near-tie may be decided differently when the batch around a request changes, and the texts
+            # part from there on; but every token, before and after, must be one that the plain implementation
+            # ranks best or within rounding of the best GIVEN THE TOKENS BEFORE IT.  A request whose cache was
+            # damaged by preemption, recomputation or a reused page fails this at the first token after.
+            assert_greedy_follows_plain(plain.logits, prompts[ids.index(rid)], got, TOL[dtype], f"request {rid}")
         assert done[rid].finish_reason == "length"
     model.runner.manager.check()
     assert model.runner.manager.live_requests() == []
@@ -138,3 +142,126 @@ def test_command_line(tiny):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p", "1", "-ngl", "0"],
                          capture_output=True, text=True, timeout=60)
     assert bad.returncode != 0 and "does not have" in bad.stderr
+
+
+# ---------------------------------------------------------------------------------------------------
+# The two small scenarios of the project's baseline, to the letter (sizes, seeds, weights N(0, 0.02) with norm
+# weights 1, prompts, chunking, temperature).
+
+LITERAL = {
+    "A": dict(architectures=["LlamaForCausalLM"], vocab_size=256, hidden_size=64, intermediate_size=176,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16, rope_theta=10000.0,
+              rms_norm_eps=1e-5, attention_bias=False, tie_word_embeddings=False, max_position_embeddings=128),
+    "B": dict(architectures=["LlamaForCausalLM"], vocab_size=384, hidden_size=96, intermediate_size=256,
+              num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=32, rope_theta=500000.0,
+              rms_norm_eps=1e-6, attention_bias=True, tie_word_embeddings=True, max_position_embeddings=256),
+}
+
+
+def _literal_model(tmp_path, name, seed):
+    from forge_b200.config import config_from_dict
+    from forge_b200.weights import write_random_model
+    d = write_random_model(config_from_dict(LITERAL[name]), str(tmp_path / f"literal{name}"), seed=seed, std=0.02)
+    return d, PlainLlama(d)
+
+
+def test_scenario_a_eight_ids_sixteen_greedy_steps(tmp_path):
+    import forge_b200 as forge
+    d, plain = _literal_model(tmp_path, "A", seed=0)
+    prompt = random_tokens(8, 256, seed=0)
+    out = forge.Model(d, dtype="float32", max_num_seqs=1, cache_tokens=128).generate(prompt, max_new_tokens=16, do_sample=False)
+    assert out["num_generated_tokens"] == 16 and out["finish_reason"] == "length"
+    assert_greedy_follows_plain(plain.logits, prompt, out["token_ids"], TOL["float32"], "scenario A")
+
+
+def _interval_holds(plain, prompt, tokens, seed, temperature):
+    """Every drawn token is the one whose interval of the plain distribution holds the generator's number."""
+    from forge_b200.sampling import XorShift64
+    rng, ids = XorShift64(seed), list(prompt)
+    for i, tok in enumerate(tokens):
+        cdf = torch.cumsum(torch.softmax(plain.logits(ids)[-1] / temperature, dim=0), 0)
+        u = rng.uniform()
+        lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+        assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"token {i}: {tok} drawn for u={u:.6f}, its interval is [{lo:.6f}, {float(cdf[tok]):.6f}]"
+        ids.append(tok)
+
+
+def test_scenario_b_three_requests_chunks_of_seven_temperature(tmp_path):
+    """Prompts of 5, 17 and 33 tokens, at most 7 tokens a step (portions of prompts beside decoded tokens),
+    temperature 0.8 with a seed per request: each request draws exactly the tokens it draws alone, and each
+    token is the one the plain distribution assigns to the generator's number."""
+    import forge_b200 as forge
+    d, plain = _literal_model(tmp_path, "B", seed=1)
+    prompts = [random_tokens(n, 384, seed=40 + n) for n in (5, 17, 33)]
+    seeds = [101, 202, 303]
+    model = forge.Model(d, dtype="float32", max_num_seqs=3, cache_tokens=256, max_tokens_per_step=7)
+    alone = [model.generate(p, max_new_tokens=12, temperature=0.8, seed=s)["token_ids"] for p, s in zip(prompts, seeds)]
+    sched = forge.RequestScheduler(model, max_num_seqs=3)
+    ids = [sched.submit(p, max_new_tokens=12, sampler_config=forge.SamplerConfig(temperature=0.8, seed=s))
+           for p, s in zip(prompts, seeds)]
+    beside = 0
+    while sched.has_pending():
+        sched.step()
+        kinds = {n == 1 and wants for _, _, n, wants in sched.last_step or []}
+        beside += kinds == {True, False}
+        assert sum(n for _, _, n, _ in sched.last_step or []) <= 7
+    assert beside >= 2, "portions of prompts were meant to run beside decoded tokens"
+    done = {r.request_id: r for r in sched.get_finished()}
+    for rid, p, s, want in zip(ids, prompts, seeds, alone):
+        assert done[rid].output_tokens == want, f"request {rid} draws other tokens in company than alone"
+        _interval_holds(plain, p, want, s, 0.8)
+
+
+def test_samplers_of_different_kinds_in_one_batch(tiny):
+    """One call of the device sampler with greedy, temperature, top-k and top-p rows (and a repeat penalty)
+    side by side: every row obeys its own options and its own generator."""
+    from plain.kernels_ref import sample_probabilities_ref as _sample_ref
+    from forge_b200.sampling import RequestSampler, SamplerConfig, XorShift64, sample_batch
+    V = 977
+    logits = (torch.randn(6, V, generator=torch.Generator().manual_seed(4)) * 3.0)
+    configs = [SamplerConfig(do_sample=False), SamplerConfig(temperature=0.8, seed=5), SamplerConfig(temperature=1.2, top_k=7, seed=6),
+               SamplerConfig(temperature=0.9, top_p=0.6, seed=7), SamplerConfig(temperature=0.0, seed=8),
+               SamplerConfig(temperature=0.7, top_k=30, top_p=0.85, repeat_penalty=1.4, seed=9)]
+    samplers = [RequestSampler(c) for c in configs]
+    samplers[5].record(int(logits[5].argmax()))            # the penalty pushes the best token of row 5 down
+    samplers[5].record(3)
+    want_logits = logits.clone()
+    for t in (int(logits[5].argmax()), 3):
+        v = want_logits[5, t]
+        want_logits[5, t] = v / 1.4 if v > 0 else v * 1.4
+    got = sample_batch(logits.to("cuda:0"), samplers)
+    for r, (c, tok) in enumerate(zip(configs, got)):
+        if c.greedy:
+            assert tok == int(want_logits[r].argmax())
+            continue
+        u = XorShift64(c.seed).uniform()
+        p = _sample_ref(want_logits[r], c.temperature, c.top_k, c.top_p)
+        cdf = torch.cumsum(p, 0)
+        assert p[tok] > 0, f"row {r}: a token outside the kept set was drawn"
+        lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+        assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5, f"row {r}"
+        assert samplers[r].history[tok] >= 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sixty_four_requests_decode_through_the_graph(tiny, dtype):
+    """64 requests, each decoding one token a step through the captured graph for several steps.  In 32-bit
+    such a step is large enough for the rotary part to use a table of angles per step; a graph that replayed
+    the captured step's table would rotate every later step by stale angles."""
+    from forge_b200.engine import ModelRunner, StepEntry
+    name, d, plain = tiny
+    V = TINY[name]["vocab_size"]
+    n_req, prompt_len, steps = 64, 3, 5
+    toks = [random_tokens(prompt_len + steps, V, seed=300 + i) for i in range(n_req)]
+    want = [plain.logits(t).float() for t in toks]
+    runner = ModelRunner(d, dtype=dtype, page_size=16, cache_tokens=64 * 16, max_requests=64)
+    assert runner.cuda_graphs
+    for i in range(n_req):
+        runner.admit(i)
+    runner.step([StepEntry(i, toks[i][:prompt_len], []) for i in range(n_req)])
+    for s in range(steps):
+        p = prompt_len + s
+        lg = runner.step([StepEntry(i, [toks[i][p]], [0]) for i in range(n_req)]).cpu()
+        ref = torch.stack([w[p] for w in want])
+        assert max_rel_err(lg, ref) <= TOL[dtype], f"decode step {s}"
+    runner.check_status()

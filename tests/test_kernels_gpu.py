@@ -161,23 +161,6 @@ def test_argmax_lowest_index_wins():
     assert got[0].item() == 17
 
 
-def _sample_ref(row, temperature, top_k, top_p):
-    """The reference's pipeline (src/inference/sampler.cpp:197-316) in float64; returns kept probabilities."""
-    p = torch.softmax(row.double() / temperature, dim=0)
-    if top_k > 0:
-        kth = torch.topk(p, top_k).values[-1]
-        p = torch.where(p >= kth, p, torch.zeros_like(p))
-        p = p / p.sum()
-    if top_p < 1.0:
-        sp, _ = torch.sort(p, descending=True)
-        c = torch.cumsum(sp, 0)
-        cutoff = int((c > top_p).nonzero()[0]) + 1 if bool((c > top_p).any()) else p.numel()
-        thr = sp[cutoff - 1]
-        p = torch.where(p >= thr, p, torch.zeros_like(p))
-        p = p / p.sum()
-    return p
-
-
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 1.0), (0.8, 40, 1.0), (1.3, 0, 0.9),
                                                       (0.7, 40, 0.9), (1.0, 1, 1.0)])
 def test_sample_picks_the_token_whose_interval_holds_u(temperature, top_k, top_p):
@@ -188,7 +171,7 @@ def test_sample_picks_the_token_whose_interval_holds_u(temperature, top_k, top_p
     got = k.sample(logits, torch.full((R_,), temperature, device=DEV), torch.full((R_,), top_k, dtype=torch.int32, device=DEV),
                    torch.full((R_,), top_p, device=DEV), us.to(DEV))
     for r in range(R_):
-        p = _sample_ref(logits[r].cpu(), temperature, top_k, top_p)
+        p = R.sample_probabilities_ref(logits[r].cpu(), temperature, top_k, top_p)
         cdf = torch.cumsum(p, 0)
         i = int(got[r])
         assert p[i] > 0, "a token outside the kept set was drawn"

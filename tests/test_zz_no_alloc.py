@@ -59,3 +59,26 @@ def test_static_scratch_entry_refuses_what_does_not_fit():
     plan = k.attention_plan(batch, nh // nkv, q.device)
     rc, _, msg = _call(fn, lib, q, cache, group, batch, plan, nh, nkv, hd, ps, 2000)   # 64*4*2000*16*66 floats
     assert rc != 0 and "scratch floats needed" in msg and "holds" in msg
+    # sizes whose product would wrap round 64 bits must not slip under the limit either (nothing is launched:
+    # the refusal comes before any pointer is looked at)
+    rc = fn(None, None, None, None, None, None, None, None, 2 ** 28, 16, nh, 2 ** 15, hd, ps, 4, 0, 2 ** 15, 0.125, None)
+    assert rc != 0
+
+
+def test_static_scratch_entry_with_prompt_portions():
+    """Requests that bring many rows (the four-warp layout of the scratch, 64 rows a tile) with their keys cut
+    into slices; and a long prompt in one slice, which needs no scratch at all and must not be refused for a
+    size it does not use."""
+    from forge_b200 import kernels as k
+    nh, nkv, hd, ps = 32, 4, 64, 16
+    lib, fn = _static_entry(hd)
+    for reqs, splits in (([(200, 9), (40, 3), (0, 7)], 3), ([(0, 2048)], 1), ([(100, 24), (700, 1)], 2)):
+        q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=5)
+        plan = k.attention_plan(batch, nh // nkv, q.device)
+        assert plan["max_rows"] > 16
+        want = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, num_splits=splits)
+        rc, got, msg = _call(fn, lib, q, cache, group, batch, plan, nh, nkv, hd, ps, splits)
+        assert rc == 0, msg
+        torch.cuda.synchronize()
+        assert not torch.isnan(got.float()).any()
+        assert (got.float() - want.float()).abs().max() <= 1e-2 * want.float().abs().max(), (reqs, splits)
