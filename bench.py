@@ -80,6 +80,73 @@ class ClockSampler:
                 "samples": len(s)}
 
 
+REF_DIR = os.environ.get("FORGE_REFERENCE_BUILD", os.path.join(ROOT, "baseline", "_ref", "cuda"))
+REF_SOURCE = os.environ.get("FORGE_REFERENCE_SOURCE", "/root/reference")
+
+
+def reference_arm(a):
+    """The UNMODIFIED reference on its CUDA backend, through its own engine API (baseline/ref_bench.cpp says how it
+    is driven, baseline/build_reference.py how it is built: by hand, because its pip/CMake build needs the
+    network).  The reference computes in FP32 and serves one sequence at a time on the GPU, so its line is batch 1 in
+    fp32 at the same layer sizes, prompt length and prefill length; `config.same_config` says so."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
+        return 0
+    if a.gpus != 1:
+        return unavailable("the reference's engine runs on one GPU; asked for %d" % a.gpus)
+    exe = os.path.join(REF_DIR, "ref_bench")
+    if not os.path.exists(exe):
+        if not os.path.isdir(REF_SOURCE):
+            return unavailable(f"baseline/_ref/cuda/ref_bench is not built and the reference's sources are not at {REF_SOURCE}")
+        b = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py"), "--reference", REF_SOURCE],
+                           capture_output=True, text=True)
+        if b.returncode != 0 or not os.path.exists(exe):
+            return unavailable("building the reference's CUDA backend by hand failed: " + (b.stdout + b.stderr)[-300:])
+    s = SHAPE
+    steps, warmup = a.steps, max(a.warmup, 3)
+    args = [s["num_hidden_layers"], s["hidden_size"], s["num_attention_heads"], s["num_key_value_heads"], s["head_dim"],
+            s["intermediate_size"], s["vocab_size"], s["rope_theta"], s["rms_norm_eps"], CONTEXT, PROMPT_LEN,
+            PREFILL_TOKENS, steps, warmup]
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        r = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=1500)
+    except subprocess.TimeoutExpired:
+        clocks.stop()
+        return unavailable("the reference's ref_bench did not finish within 1500 s")
+    clk = clocks.stop()
+    line = next((l for l in reversed(r.stdout.splitlines()) if l.startswith("{")), None)
+    if r.returncode != 0 or line is None:
+        return unavailable(f"the reference's ref_bench exited with {r.returncode}: " + (r.stderr or r.stdout)[-300:])
+    m = json.loads(line)
+    ms, e2e_ms = m["decode_ms_per_step"], m["e2e_ms_per_step"]
+    L, H, I, V = s["num_hidden_layers"], s["hidden_size"], s["intermediate_size"], s["vocab_size"]
+    qkv = (s["num_attention_heads"] + 2 * s["num_key_value_heads"]) * s["head_dim"]
+    T = PREFILL_TOKENS
+    flops = 2 * T * L * (qkv * H + H * s["num_attention_heads"] * s["head_dim"] + 3 * I * H) \
+        + L * 2 * T * T * s["head_dim"] * s["num_attention_heads"] + 2 * T * V * H      # its head runs on all T rows
+    print(json.dumps({
+        "metric": "decode tok/s at batch 8; also batch 1/64 and prefill tok/s at 2,048 tokens (TinyLlama-1.1B shape)",
+        "value": round(1e3 / ms, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic: random-init fp32 weights ~N(0,0.02), random token ids",
+        "impl": "reference",
+        "config": {"model": "TinyLlama-1.1B shape (arch llama, GenericEngine)", "layers": L, "layers_full": L, "hidden": H,
+                   "heads": s["num_attention_heads"], "kv_heads": s["num_key_value_heads"], "head_dim": s["head_dim"],
+                   "intermediate": I, "vocab": V, "global_batch": 1, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT,
+                   "parallelism": "1 GPU", "same_config": False,
+                   "why": "the reference has no bf16 path (fp32 weights and cache) and decodes one sequence at a time on "
+                          "the GPU: its batched path copies device memory with host memcpy "
+                          "(transformer_engine.cpp:236-240) and is not run; compare with points.decode_b1",
+                   "build": "by hand from unmodified sources, nvcc sm_100, cuBLAS on (baseline/build_reference.py)"},
+        "clocks": clk,
+        "e2e": {"value": round(1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+        "points": {"decode_b1": round(1e3 / ms, 1)},
+        "prefill": {"value": round(T / m["prefill_ms"] * 1e3, 1), "tokens": T, "ms": round(m["prefill_ms"], 3), "flops": flops},
+    }))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -92,12 +159,7 @@ def main():
     ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page (named in config)")
     a = ap.parse_args()
     if a.impl == "reference":
-        # Cyxuan0311/Forge is a C++/CUDA project whose build fetches pybind11 over the network and whose
-        # kernels target sm_86/89: an offline install fails in cmake, so there is nothing to import and run.
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "Forge's pip build needs CMake FetchContent (network) and has no sm_100 target; "
-                          "the offline install did not produce an importable module"}))
-        return 0
+        return reference_arm(a)
     if a.gpus != 1:
         print(json.dumps({"error": "forge_b200 is a single-GPU engine: bench.py runs at --gpus 1 only", "n_gpus": a.gpus}))
         return 2

@@ -3,6 +3,7 @@ mixer with state of its own and a toy architecture (different mixers in differen
 runs twice, a layer that reads another layer's cache, a windowed layer) are defined HERE, registered, built
 and stepped without touching the framework's files."""
 import json
+import math
 import os
 from dataclasses import asdict, dataclass
 
@@ -320,7 +321,7 @@ def _interleaved_rope(x, positions, theta):
     """Rotary encoding on neighbouring pairs (2d, 2d+1) instead of the half-split pairs; x [T, heads, HD]."""
     T, _, hd = x.shape
     d = torch.arange(hd // 2, dtype=x.dtype, device=x.device)
-    ang = positions.to(x.dtype)[:, None] * (1.0 / torch.pow(torch.tensor(float(theta), dtype=x.dtype, device=x.device), 2.0 * d / hd))
+    ang = positions.to(x.dtype)[:, None] * torch.exp(d * (-2.0 * math.log(float(theta)) / hd))    # 1 / theta^(2d/hd)
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x0, x1 = x[..., 0::2], x[..., 1::2]
     return torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1).reshape(x.shape)
