@@ -18,6 +18,7 @@
 
 #include "attention_no_alloc.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 #ifndef FORGE_ATT_HD
 #define FORGE_ATT_HD 64
@@ -25,14 +26,9 @@
 
 namespace {
 
+using namespace mma_sync;
 constexpr int HD = FORGE_ATT_HD;
 
-// 2^x by the special-function unit (2 ulp, ex2(-inf) = 0); the weights are rounded to bfloat16 right after
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 constexpr int BQ = 64;
 constexpr int LD = HD + 8;                    // padded row length in shared memory (bf16 elements)
 constexpr int CPR = HD / 8;                   // 16-byte chunks per row
@@ -52,30 +48,6 @@ struct AttnParams {
     int NH, NKV, page_size, max_pages, window, num_splits, part_rows;
     float scale_log2;
 };
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // Loads keys/values of token indices [t0, t0+BKV) of the request into one shared-memory buffer; rows
 // outside [lo, hi) are zero-filled (their scores are masked and their values must not be NaN).

@@ -28,6 +28,7 @@ class Model:
             if spec.cache_from is not None and not 0 <= spec.cache_from < n:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
         self.loaded = False
+        self._fused = None
 
     # ---------------------------------------------------------------------------------- tensors
     def _children(self):
@@ -90,13 +91,57 @@ class Model:
             out.append(earlier[-1])
         return out
 
+    # ---------------------------------------------------------------------------------- all layers in one kernel
+    def enable_fused_decode(self, position_caches, max_requests):
+        """Prepares the kernel that runs every layer of a decode step in one launch, if this model is one it
+        can run: every layer the stock arrangement of stock parts with equal sizes, each run once, in order, on
+        a cache of its own, all in one cache group.  Returns whether it is on."""
+        from .. import kernels
+        self._fused = None
+        sched = self.plan.schedule
+        if self.rt.full_precision or not sched or sched != list(range(len(self.blocks))):
+            return False
+        descs = [b.fused_decode() if hasattr(b, "fused_decode") else None for b in self.blocks]
+        if any(d is None for d in descs):
+            return False
+        keys = ("hidden", "intermediate", "num_heads", "num_kv_heads", "head_dim", "theta", "rotary", "eps", "window", "scale")
+        first = descs[0]
+        if any(d[k] != first[k] for d in descs for k in keys):
+            return False
+        caches = list(position_caches)
+        if any(c is None or c.kv is None or not c.writable or c.group != caches[0].group for c in caches):
+            return False
+        if not kernels.DecodeLayers.supports(first["hidden"], first["intermediate"], first["num_heads"], first["num_kv_heads"],
+                                             first["head_dim"]):
+            return False
+        layers = [dict(d["tensors"], kv=c.kv) for d, c in zip(descs, caches)]
+        self._fused = (kernels.DecodeLayers(layers, first["hidden"], first["intermediate"], first["num_heads"],
+                                            first["num_kv_heads"], first["head_dim"], caches[0].page_size, first["theta"],
+                                            first["rotary"], first["eps"], window=first["window"], scale=first["scale"],
+                                            max_tokens=min(max_requests, kernels.DecodeLayers.MAX_TOKENS)), caches[0].group)
+        return True
+
+    def _fused_decode_applies(self, batch):
+        fused = getattr(self, "_fused", None)
+        if fused is None or batch.num_tokens != batch.num_requests or batch.num_tokens > fused[0].max_tokens:
+            return False
+        # one CTA serves a (request, kv head) with four warps: with few requests and very long contexts the
+        # one-kernel-per-operation path, whose attention spreads a request's keys over several CTAs, is faster
+        max_ctx = getattr(batch, "max_context", None) or (max(batch.host_context_before) + 1)
+        return max_ctx <= 4096 or batch.num_requests * fused[0].dims[3] >= 128
+
     # ---------------------------------------------------------------------------------- forward
     def forward(self, batch, position_caches):
         """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run.
         Returns fp32 logits [R,V] at ``batch.logits_rows`` (None if no row is wanted)."""
         residual = self.embedding.forward(batch.token_ids, status=batch.status)
-        for pos, i in enumerate(self.plan.schedule):
-            self.blocks[i].forward(residual, batch, position_caches[pos])
+        if self._fused_decode_applies(batch):
+            fused, group = self._fused
+            g = batch.groups[group]
+            fused.run(residual, g.block_table, batch.positions, g.slot_mapping)
+        else:
+            for pos, i in enumerate(self.plan.schedule):
+                self.blocks[i].forward(residual, batch, position_caches[pos])
         if batch.num_logits == 0:
             return None
         x = self.final_norm.forward(residual, rows=batch.logits_rows)

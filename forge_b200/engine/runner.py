@@ -6,6 +6,8 @@ replay tool, tests) admit a request, feed it tokens over any number of steps, cu
 it; the runner makes no scheduling decision of its own.  (Reference counterparts:
 InferenceEngine::forward / forward_batch, include/forge/engine.h:65-90.)
 """
+import os
+
 import torch
 
 from ..cache import CacheStorage, OutOfPages, bytes_per_page
@@ -38,13 +40,14 @@ def resolve_dtype(dtype):
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
                  page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True,
-                 max_tokens_per_step=None, max_decode_graphs=16):
+                 max_tokens_per_step=None, max_decode_graphs=16, fused_decode=True):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
         ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the
         free device memory holds, capped by max_requests * max positions).  ``cuda_graphs``: replay decode
         steps as CUDA graphs where every part of the model allows it (``Part.graph_safe``); a model with a part
         that does not takes the ordinary step, whatever this says.  ``max_tokens_per_step``: a step with more
         tokens is refused (None: no limit); the step's activations live in a workspace of that many rows.
+        ``fused_decode``: run all layers of a decode step in one kernel where the model allows it.
         ``max_decode_graphs``: how many captured graphs (one per batch size and context bucket) are kept; the
         one used longest ago goes first."""
         if not torch.cuda.is_available():
@@ -86,6 +89,9 @@ class ModelRunner:
         if all(g.window is None for g in self.manager.groups.values()):
             self.max_pages_per_request = min(self.num_pages, self.max_pages_per_request)
         self.max_tokens_per_step = None if max_tokens_per_step is None else int(max_tokens_per_step)
+        # decode steps of stock layers run all their layers in one persistent kernel (FORGE_FUSED_DECODE=0: off)
+        self.fused_decode = fused_decode and os.environ.get("FORGE_FUSED_DECODE", "1") != "0" \
+            and self.model.enable_fused_decode(self.storage.layers, self.max_requests)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # decode steps replay a captured graph only if every part of the model says that it may be captured
         self.graph_safe = self.model.graph_safe()
@@ -202,7 +208,12 @@ class ModelRunner:
     def check_status(self):
         """Reads the device error word (synchronises); raises if a kernel flagged a problem."""
         from .. import kernels
-        kernels.check_kernel_status(self.device)          # tensor-core kernels: a bounded wait that ran out
+        try:
+            kernels.check_kernel_status(self.device)      # tensor-core kernels: a bounded wait that ran out
+        except kernels.KernelError:
+            if self.model._fused is not None:
+                self.model._fused[0].reset_after_error()
+            raise
         s = int(self.status.item())
         if s:
             self.status.zero_()

@@ -53,6 +53,13 @@ _SIGNATURES = {
     "attention_sm100": {
         "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
     },
+    "decode_layers": {
+        "forge_decode_layers_desc_bytes": [],
+        "forge_decode_layers_supports": [_I] * 6,
+        "forge_decode_layers_describe": [_P, _I] + [_P] * 8 + [_I] * 5,
+        "forge_decode_layers": [_P, _I] + [_P] * 10 + [_I] * 10 + [_F, _F, _F, _P],
+        "forge_decode_layers_barrier_probe": [_P, _P, ctypes.c_ulonglong, _P],
+    },
 }
 
 _libs = {}
@@ -440,6 +447,74 @@ def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, 
         int(window or 0), 1 if rotary else 0, float(theta), float(scale), int(max_context or 0), _stream()),
         "decode_attention_fused")
     return out
+
+
+class DecodeLayers:
+    """All layers of a decode step as one persistent kernel (csrc/decode_layers.cu).
+
+    Made once per model from the layers' device tensors; ``run`` then takes the residual stream of a step of
+    at most ``max_tokens`` single tokens through every layer, in place.  The object owns the kernel's scratch
+    (fp32 results of the projections, attention output, barrier words), so calls must not overlap on the GPU.
+    """
+    MAX_TOKENS = 64
+
+    @staticmethod
+    def supports(hidden, intermediate, n_heads, n_kv_heads, head_dim, tokens=1):
+        if not (_TENSOR_CORE_GEMM and _TENSOR_CORE_ATTENTION) or head_dim % 16 != 0 or not 16 <= head_dim <= 128:
+            return False
+        lib = library("decode_layers", {"FORGE_ATT_HD": head_dim})
+        return bool(lib.forge_decode_layers_supports(int(tokens), hidden, intermediate, n_heads, n_kv_heads, head_dim))
+
+    def __init__(self, layers, hidden, intermediate, n_heads, n_kv_heads, head_dim, page_size, theta, rotary, eps,
+                 window=0, scale=None, max_tokens=MAX_TOKENS):
+        """layers: per layer a dict of device tensors: wqkv bf16 [(NH+2NKV)*HD, H], wo [H, NH*HD], wgu [2I, H] (gate and
+        up rows interleaved), wdown [H, I], norm1 / norm2 fp32 [H], bias fp32 [(NH+2NKV)*HD] or None, kv (the layer's
+        cache [pages, 2, NKV, page_size, HD] bf16)."""
+        self.lib = lib = library("decode_layers", {"FORGE_ATT_HD": head_dim})
+        self.dims = (hidden, intermediate, n_heads, n_kv_heads, head_dim)
+        self.page_size, self.theta, self.rotary, self.eps, self.window = int(page_size), float(theta), bool(rotary), float(eps), int(window or 0)
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.max_tokens = min(int(max_tokens), self.MAX_TOKENS)
+        dev = layers[0]["wqkv"].device
+        self.num_layers = len(layers)
+        nbytes = lib.forge_decode_layers_desc_bytes()
+        self.descs = torch.zeros(self.num_layers * nbytes, dtype=torch.uint8, device=dev)
+        self._keep = layers                                    # the maps hold raw pointers into these tensors
+        with torch.cuda.device(dev):
+            for i, t in enumerate(layers):
+                rc = lib.forge_decode_layers_describe(
+                    self.descs.data_ptr(), i, _need(t["wqkv"], "wqkv", torch.bfloat16, 2), _need(t["wo"], "wo", torch.bfloat16, 2),
+                    _need(t["wgu"], "wgu", torch.bfloat16, 2), _need(t["wdown"], "wdown", torch.bfloat16, 2),
+                    _need(t["norm1"], "norm1", torch.float32), _need(t["norm2"], "norm2", torch.float32),
+                    _opt(t.get("bias"), "bias", torch.float32), _need(t["kv"], "kv", torch.bfloat16), hidden, intermediate,
+                    n_heads, n_kv_heads, head_dim)
+                if rc != 0:
+                    raise KernelError(f"decode_layers: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
+        B, qkv = self.max_tokens, (n_heads + 2 * n_kv_heads) * head_dim
+        self.qkv_acc = torch.zeros(B * qkv, dtype=torch.float32, device=dev)
+        self.gu_acc = torch.zeros(B * 2 * intermediate, dtype=torch.float32, device=dev)
+        self.ssq = torch.zeros(128, dtype=torch.float32, device=dev)
+        self.attn_out = torch.zeros(B * n_heads * head_dim, dtype=torch.bfloat16, device=dev)
+        self.barrier = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def run(self, residual, block_table, positions, slot_mapping):
+        """residual fp32 [B, H], updated in place; block_table int32 [B, max_pages]; positions, slot_mapping int32 [B]."""
+        H, I, NH, NKV, HD = self.dims
+        B = residual.shape[0]
+        if B > self.max_tokens or residual.shape[1] != H:
+            raise KernelError(f"decode_layers: residual {tuple(residual.shape)} does not fit ({self.max_tokens} tokens of {H})")
+        lib = self.lib
+        _check(lib, lib.forge_decode_layers(
+            self.descs.data_ptr(), self.num_layers, _need(residual, "residual", torch.float32, 2), self.qkv_acc.data_ptr(),
+            self.gu_acc.data_ptr(), self.ssq.data_ptr(), self.attn_out.data_ptr(), _need(block_table, "block_table", torch.int32, 2),
+            _need(positions, "positions", torch.int32), _need(slot_mapping, "slot_mapping", torch.int32), self.barrier.data_ptr(),
+            _need(_gemm_status(residual.device), "status", torch.int32), B, H, I, NH, NKV, HD, self.page_size,
+            block_table.shape[1], self.window, 1 if self.rotary else 0, self.theta, self.scale, self.eps, _stream()), "decode_layers")
+        return residual
+
+    def reset_after_error(self):
+        """After a wait ran out the barrier words are left as they were; clear them before the next step."""
+        self.barrier.zero_()
 
 
 def paged_attention(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=None,

@@ -28,6 +28,8 @@ LIBRARIES = {
     "attention_mma": ["attention_mma.cu"],
     # bf16 tcgen05/TMEM paged attention for prompt portions, head size 64
     "attention_sm100": ["attention_sm100.cu"],
+    # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)
+    "decode_layers": ["decode_layers.cu"],
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -136,7 +138,7 @@ COMMON_HEAD_DIMS = (64, 128)
 def build_all(force=False):
     out = {}
     for name in LIBRARIES:
-        if name == "attention_mma":
+        if name in ("attention_mma", "decode_layers"):
             for hd in COMMON_HEAD_DIMS:
                 out[f"{name}_hd{hd}"] = build_library(name, force=force, defines={"FORGE_ATT_HD": hd})
         else:

@@ -37,6 +37,28 @@ class PreNormBlock(Part):
         for prefix, part in self._children():
             part.bind({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
 
+    def fused_decode(self):
+        """What the kernel that runs all layers of a decode step at once needs of this layer, or None: the layer
+        must be exactly the stock arrangement of the stock parts (that kernel computes RMSNorm, rotary attention
+        over the paged cache and SwiGLU, and nothing else), in bfloat16 on the tensor-core products."""
+        from .attention import GQAAttention
+        from .feedforward import SwiGLU
+        from .norm import RMSNorm
+        m, f, n1, n2 = self.mixer, self.feed_forward, self.norm_in, self.norm_post
+        if type(self) is not PreNormBlock or type(m) is not GQAAttention or type(f) is not SwiGLU \
+                or type(n1) is not RMSNorm or type(n2) is not RMSNorm or self.rt.full_precision:
+            return None
+        pos = m.position.fused_decode() if hasattr(m.position, "fused_decode") else None
+        if pos is None or m.out_bias or n1.eps != n2.eps or m.qkv is None:
+            return None
+        if not all(lin.tensor_core for lin in (m.qkv, m.o, f.gate_up, f.down)):
+            return None
+        return {"hidden": m.hidden_size, "intermediate": f.intermediate_size, "num_heads": m.num_heads,
+                "num_kv_heads": m.num_kv_heads, "head_dim": m.head_dim, "theta": pos["theta"], "rotary": pos["rotary"],
+                "eps": n1.eps, "window": m.window or 0, "scale": m.scale,
+                "tensors": {"wqkv": m.qkv.weight, "wo": m.o.weight, "wgu": f.gate_up.weight, "wdown": f.down.weight,
+                            "norm1": n1.weight, "norm2": n2.weight, "bias": m.qkv.bias}}
+
     def forward(self, residual, batch, cache):
         x = self.norm_in.forward(residual)
         self.mixer.forward(x, batch, cache, residual)
