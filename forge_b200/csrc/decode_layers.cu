@@ -1,4 +1,4 @@
-// All layers of a decode step (one new token for each of up to 64 requests) in ONE persistent kernel.
+// All layers of a decode step (one new token for each of up to 16 requests) in ONE persistent kernel.
 //
 // A decode step of a dense decoder is a stream of weights through the SMs: every matrix is read once and
 // multiplied with a handful of token rows.  Launched as one kernel per operation (norm, qkv, attention, o,
@@ -11,29 +11,37 @@
 //    TMA (two [128 x 64] k-blocks of a matrix per instruction).  It never waits for data, only for a free
 //    stage: weights for the next operation, and the next layer, arrive while the current one is computed.
 //  * warp 1 issues the tcgen05 MMAs: the weight tile is the M operand (128 output features), the tokens are
-//    the N side (16, 32 or 64), the accumulator lives in tensor memory.
+//    the N side (16), the accumulator lives in tensor memory.
 //  * warps 2-9 (256 threads) prepare the token operand and finish the products.  Activations live in global
 //    memory in fp32 (they are a few hundred KB and stay in L2); the workers read the slice they need, apply
 //    what stands between two products (norm weight, SwiGLU), round to bfloat16 and write the 128-byte-swizzled
-//    tile the MMA reads.  After a tile's last MMA they add its accumulator into the result in global memory
-//    with `red.global.add.f32` (the L2 adds; nothing is read back).  They also run the attention.
+//    tile the MMA reads; the loads of the next units are in flight while the current ones are converted.  After
+//    a tile's last MMA they add its accumulator into the result in global memory with `red.global.add.f32` (the
+//    L2 adds; nothing is read back).  They also run the attention.
 //
 // A matrix is dealt to the CTAs in units of (128 output features) x (128 of K), the same number of units to
 // every CTA whatever the matrix's shape, so the partial sums of an output element come from several CTAs and
 // meet in L2.  What follows a product is applied by the consumer of its result:
 //     qkv_acc  += (x * w_norm1) . Wqkv^T           ssq1 += sum x^2
-//     attention reads qkv_acc / rms + bias, rotates, writes the cache, attends      -> attn_out (bf16)
-//     x        += attn_out . Wo^T
+//     attention reads qkv_acc / rms + bias, rotates, writes the cache, attends      -> parts of the result
+//     x        += merge(parts) . Wo^T
 //     gu_acc   += (x * w_norm2) . Wgu^T             ssq2 += sum x^2
 //     x        += (silu(g / rms) * (u / rms)) . Wd^T
 // (RMSNorm is linear up to the division by the row's rms, which commutes with the product.)
 // Between these five phases all CTAs meet at a barrier in global memory (an arrival counter that every CTA
 // increments and polls); the weight streamer does not take part, so the barrier costs latency but no
-// bandwidth.  Every wait (mbarrier, grid barrier) has a time limit; on expiry the CTA raises a status bit and
-// a flag that makes all other CTAs leave too.
+// bandwidth.
 //
-// The sums over K are made in an order that depends on timing (atomic adds), so results differ from run to
-// run in the last bits of fp32; the bfloat16 path makes no promise beyond rounding.
+// Attention: the keys of a (request, kv head) are dealt to up to 4 CTAs (tiles of 32 keys round the CTAs, then
+// round a CTA's 4 warps), so that with few requests most SMs have a share and a warp has one or two tiles.  The
+// tiles of earlier positions do not depend on this layer's projections: they are requested before the barrier
+// that ends the qkv product, so their trip from HBM is over when q arrives.  Each CTA leaves its un-normalised
+// partial result in global memory; the o-projection merges the parts (in part order) while it builds its token
+// operand.  Rotary angles come from a table that the kernel fills once at its start.
+//
+// Every wait (mbarrier, grid barrier) has a time limit; on expiry the CTA raises a status bit and a flag that
+// makes all other CTAs leave too.  The sums over K are made in an order that depends on timing (atomic adds),
+// so results differ from run to run in the last bits of fp32; the bfloat16 path makes no promise beyond rounding.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -59,7 +67,9 @@ constexpr int kStageW = kPair * BM * BK * 2;           // 32 KB of weights per s
 constexpr int kStages = 4;
 constexpr int kThreads = 320, kWorkers = 256;
 constexpr int kSmemLimit = 227 * 1024;
-constexpr int kMaxTokens = 64;
+constexpr int kMaxTokens = 16;                         // tokens of a step: the N side of every MMA
+constexpr int kSsqStride = 64;                          // ssq: [2][kSsqStride]
+constexpr int kMaxSplit = 4;                            // CTAs that share the keys of one (request, kv head)
 
 // attention inside the kernel: 4 warps (2 for head sizes above 64) take tiles of 32 keys in turn
 constexpr int DKV = 32;
@@ -69,7 +79,8 @@ constexpr int kAttWarps = HD <= 64 ? 4 : 2;
 constexpr int kAttBytes = (16 + kAttWarps * 4 * DKV) * LD * 2;
 static_assert((size_t)kAttWarps * 16 * (HD + 2) * 4 <= (size_t)kAttWarps * 4 * DKV * LD * 2, "merge area fits the tile buffers");
 
-enum { OP_NORMW = 0, OP_COPY = 1, OP_SWIGLU = 2 };
+enum { OP_NORMW = 0, OP_MERGE = 1, OP_SWIGLU = 2 };
+constexpr int kAccs = 4;                                // accumulators in tensor memory: tiles whose sums wait for their epilogue
 
 struct alignas(64) LayerDesc {
     CUtensorMap w_qkv, w_o, w_gu, w_down;              // k-block views {64, rows, K/64}, boxes {64, 128, 2}
@@ -85,8 +96,10 @@ struct Params {
     float* resid;                 // [B, H] fp32, in and out: the residual stream
     float* qkv_acc;               // [B, QKV] fp32 scratch
     float* gu_acc;                // [B, 2I] fp32 scratch (gate and up interleaved)
-    float* ssq;                   // [2][64] sums of squares of the rows before each norm
-    __nv_bfloat16* attn_out;      // [B, NH*HD]
+    float* ssq;                   // [2][64] sums of squares of the rows before each norm (first 16 of each used)
+    float2* rope_tab;             // [B, HD/2] (cos, sin) of the step's positions
+    float* part_o;                // [B*NKV, kMaxSplit, 16, HD] un-normalised attention outputs of the parts of the keys
+    float* part_ml;               // [B*NKV, kMaxSplit, 16, 2] their (maximum, sum of weights)
     const int32_t* block_table;   // [B, max_pages]
     const int32_t* positions;     // [B]
     const int32_t* slot_mapping;  // [B]
@@ -95,6 +108,8 @@ struct Params {
     int B, H, I, NH, NKV, QKV, page_size, max_pages, window, rotary;
     float theta, scale_log2, eps;
     unsigned long long wait_limit_ns;
+    int prefetch_units;            // how many units ahead of its ring loads the weight streamer asks L2 for
+    unsigned long long* timeline;  // null, or [CTAs][barriers][2]: when each CTA reached and left each barrier (ns)
 };
 
 struct PhaseInfo {
@@ -114,10 +129,10 @@ __device__ __forceinline__ PhaseInfo phase_info(const Params& p, const LayerDesc
         f.map = &L->w_qkv; f.n_out = p.QKV; f.K = p.H; f.op = OP_NORMW; f.out = p.qkv_acc; f.ldo = p.QKV;
         f.normw = L->norm1; f.ssq = p.ssq;
     } else if (ph == 1) {
-        f.map = &L->w_o; f.n_out = p.H; f.K = p.NH * HD; f.op = OP_COPY; f.out = p.resid; f.ldo = p.H;
+        f.map = &L->w_o; f.n_out = p.H; f.K = p.NH * HD; f.op = OP_MERGE; f.out = p.resid; f.ldo = p.H;
     } else if (ph == 2) {
         f.map = &L->w_gu; f.n_out = 2 * p.I; f.K = p.H; f.op = OP_NORMW; f.out = p.gu_acc; f.ldo = 2 * p.I;
-        f.normw = L->norm2; f.ssq = p.ssq + kMaxTokens;
+        f.normw = L->norm2; f.ssq = p.ssq + kSsqStride;
     } else {
         f.map = &L->w_down; f.n_out = p.H; f.K = p.I; f.op = OP_SWIGLU; f.out = p.resid; f.ldo = p.H;
     }
@@ -133,6 +148,31 @@ __device__ __forceinline__ void unit_range(const PhaseInfo& f, int& u0, int& u1)
     u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
 }
 
+// Walks the units of this CTA in the order of the step: layers, in each the four products, in each the CTA's share.
+struct UnitWalk {
+    int layer, ph, u, u1;
+    PhaseInfo f;
+    bool done;
+};
+__device__ __forceinline__ void walk_settle(const Params& p, UnitWalk& w) {
+    // moves on to the next product (or layer) until one has a unit for this CTA
+    while (!w.done && w.u >= w.u1) {
+        if (++w.ph == 4) { w.ph = 0; ++w.layer; }
+        if (w.layer >= p.num_layers) { w.done = true; break; }
+        w.f = phase_info(p, p.layers + w.layer, w.ph);
+        unit_range(w.f, w.u, w.u1);
+    }
+}
+__device__ __forceinline__ UnitWalk walk_begin(const Params& p) {
+    UnitWalk w;
+    w.layer = 0; w.ph = -1; w.u = 0; w.u1 = 0; w.done = p.num_layers <= 0;
+    walk_settle(p, w);
+    return w;
+}
+__device__ __forceinline__ void walk_next(const Params& p, UnitWalk& w) {
+    ++w.u;
+    walk_settle(p, w);
+}
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
@@ -146,10 +186,16 @@ __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
 __device__ __forceinline__ bool grid_barrier(const Params& p, unsigned int target, volatile int* abort, int tid) {
     workers_sync();
     if (tid == 0 && !*abort) {
+        unsigned long long* stamp = nullptr;
+        if (p.timeline) {
+            const unsigned int nb = target / gridDim.x - 1, per_cta = 1 + 5 * p.num_layers;
+            stamp = p.timeline + ((size_t)blockIdx.x * per_cta + nb) * 8;
+            stamp[0] = global_ns();
+        }
         __threadfence();
-        atomicAdd(p.barrier, 1u);
+        const unsigned int mine = atomicAdd(p.barrier, 1u) + 1u;     // the CTA that brings the count to `target` need not poll
         const unsigned long long t0 = global_ns();
-        while (ld_acquire_u32(p.barrier) < target) {
+        while (mine < target && ld_acquire_u32(p.barrier) < target) {
             if (ld_acquire_u32(p.barrier + 1) != 0u) { *abort = 1; break; }
             if (global_ns() - t0 > p.wait_limit_ns) {
                 *abort = 1;
@@ -159,12 +205,15 @@ __device__ __forceinline__ bool grid_barrier(const Params& p, unsigned int targe
             }
         }
         __threadfence();
+        if (stamp) stamp[1] = global_ns();
     }
     workers_sync();
     return *abort == 0;
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+// g / (1 + e^-g) with the special-function unit's exponential and division (relative error of a few fp32 ulp; the
+// result is rounded to bfloat16 right after)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
     uint4 o;
@@ -177,50 +226,48 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
 
 // The token operands of up to UG consecutive units (k-pairs pair0, pair0 + 1, ...) of one weight tile: rows =
 // tokens (NT of them, those beyond B are zero), 128 of K each, every unit as two 128-byte-swizzled [NT x 64] bf16
-// tiles in the stage of the ring that its turn `it` names.  A thread makes 16-byte chunks (8 elements).  All the
-// group's loads are issued before the first value is used: a unit's operand is one trip to L2 away, and a CTA has
-// dozens of units a layer, so the trips of several units have to overlap.
+// tiles in the stage of the ring that its turn names.  A thread makes 16-byte chunks (8 elements).  A unit's
+// operand is one trip to L2 away and a CTA has dozens of units a layer, so the work is cut in two: load_group only
+// issues a group's loads (into registers), store_group converts and stores them; the caller issues the loads of
+// the next group before it converts the current one.
+template <int NT, int UG> struct RawGroup { float4 v[UG][NT * 16 / kWorkers][4]; };
+
 template <int NT, int UG, int OP>
-__device__ __forceinline__ void convert_group(const Params& p, const PhaseInfo& f, int pair0, int n_units, uint8_t* x_ring,
-                                              uint32_t it, uint64_t* act_full, bool do_ssq, int tid) {
+__device__ __forceinline__ void load_group(const Params& p, const PhaseInfo& f, int pair0, int n_units, RawGroup<NT, UG>& raw, int tid) {
     constexpr int CH = NT * 16 / kWorkers;                 // chunks per thread and unit
-    constexpr int kXStage = kPair * NT * 128;
-    const int lane = tid & 31;
-    float4 raw[UG][CH][4];
-    float rinv[CH];
-#pragma unroll
-    for (int ci = 0; ci < CH; ++ci) {
-        const int row = (tid + ci * kWorkers) >> 4;
-        rinv[ci] = 1.f;
-        if (OP == OP_SWIGLU && row < p.B) rinv[ci] = 1.0f / sqrtf(__ldcg(p.ssq + kMaxTokens + row) / (float)p.H + p.eps);
-    }
 #pragma unroll
     for (int j = 0; j < UG; ++j) {
-        if (j >= n_units) break;
 #pragma unroll
         for (int ci = 0; ci < CH; ++ci) {
             const int idx = tid + ci * kWorkers;
             const int row = idx >> 4, chunk = idx & 15;
             const int k = (pair0 + j) * kPair * BK + chunk * 8;
             const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-            raw[j][ci][0] = raw[j][ci][1] = raw[j][ci][2] = raw[j][ci][3] = zero;
-            if (row < p.B && k < f.K) {
+            raw.v[j][ci][0] = raw.v[j][ci][1] = raw.v[j][ci][2] = raw.v[j][ci][3] = zero;
+            if (j < n_units && row < p.B && k < f.K) {
                 if (OP == OP_NORMW) {
                     const float4* src = reinterpret_cast<const float4*>(p.resid + (size_t)row * p.H + k);
                     const float4* wv = reinterpret_cast<const float4*>(f.normw + k);
-                    raw[j][ci][0] = __ldcg(src); raw[j][ci][1] = __ldcg(src + 1);
-                    raw[j][ci][2] = __ldg(wv); raw[j][ci][3] = __ldg(wv + 1);
-                } else if (OP == OP_COPY) {
-                    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.attn_out + (size_t)row * f.K + k));
-                    raw[j][ci][0] = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+                    raw.v[j][ci][0] = __ldcg(src); raw.v[j][ci][1] = __ldcg(src + 1);
+                    raw.v[j][ci][2] = __ldg(wv); raw.v[j][ci][3] = __ldg(wv + 1);
                 } else {
                     const float4* src = reinterpret_cast<const float4*>(p.gu_acc + (size_t)row * 2 * p.I + 2 * (size_t)k);
-                    raw[j][ci][0] = __ldcg(src); raw[j][ci][1] = __ldcg(src + 1);
-                    raw[j][ci][2] = __ldcg(src + 2); raw[j][ci][3] = __ldcg(src + 3);
+                    raw.v[j][ci][0] = __ldcg(src); raw.v[j][ci][1] = __ldcg(src + 1);
+                    raw.v[j][ci][2] = __ldcg(src + 2); raw.v[j][ci][3] = __ldcg(src + 3);
                 }
             }
         }
     }
+}
+
+// rinv: per chunk row of this thread, 1 / rms of the row (SwiGLU only)
+template <int NT, int UG, int OP>
+__device__ __forceinline__ void store_group(const Params& p, const PhaseInfo& f, int n_units, const RawGroup<NT, UG>& raw,
+                                            const float (&rinv)[NT * 16 / kWorkers], uint8_t* x_ring, uint32_t it,
+                                            uint64_t* act_full, bool do_ssq, int tid) {
+    constexpr int CH = NT * 16 / kWorkers;
+    constexpr int kXStage = kPair * NT * 128;
+    const int lane = tid & 31;
 #pragma unroll
     for (int j = 0; j < UG; ++j) {
         if (j >= n_units) break;
@@ -230,15 +277,13 @@ __device__ __forceinline__ void convert_group(const Params& p, const PhaseInfo& 
             const int idx = tid + ci * kWorkers;
             const int row = idx >> 4, chunk = idx & 15;
             const int kb = chunk >> 3, c = chunk & 7;
-            const float4 a = raw[j][ci][0], b = raw[j][ci][1], w0 = raw[j][ci][2], w1 = raw[j][ci][3];
+            const float4 a = raw.v[j][ci][0], b = raw.v[j][ci][1], w0 = raw.v[j][ci][2], w1 = raw.v[j][ci][3];
             uint4 packed;
             float sq = 0.f;
             if (OP == OP_NORMW) {
                 sq = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
                 const float v[8] = {a.x * w0.x, a.y * w0.y, a.z * w0.z, a.w * w0.w, b.x * w1.x, b.y * w1.y, b.z * w1.z, b.w * w1.w};
                 packed = pack8(v);
-            } else if (OP == OP_COPY) {
-                packed = make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w));
             } else {
                 const float r = rinv[ci];
                 const float v[8] = {silu_f(a.x * r) * (a.y * r), silu_f(a.z * r) * (a.w * r), silu_f(b.x * r) * (b.y * r),
@@ -261,6 +306,113 @@ __device__ __forceinline__ void convert_group(const Params& p, const PhaseInfo& 
     }
 }
 
+// The token operand of the o-projection is the attention's result, which exists as up to kMaxSplit un-normalised
+// parts per (request, kv head), each with the maximum and the sum of its weights: the parts are merged here, on their
+// way into the operand (so the attention needs no second round among its CTAs).  Two units at a time, all their loads
+// in flight together.
+template <int NT>
+__device__ __forceinline__ bool convert_segment_merge(const Params& p, const PhaseInfo& f, int u, int seg_end, uint8_t* x_ring, uint32_t& it,
+                                                      uint64_t* empty, uint64_t* act_full, int S, volatile int* abort, int tid) {
+    static_assert(NT * 16 == kWorkers, "one chunk per worker and unit");
+    constexpr int kXStage = kPair * NT * 128;
+    const int row = tid >> 4, chunk = tid & 15;
+    const int kb = chunk >> 3, c = chunk & 7;
+    const int G = p.NH / p.NKV;
+    while (u < seg_end) {
+        const int n = min(2, seg_end - u);
+        float4 o[2][kMaxSplit][2];
+        float2 ml[2][kMaxSplit];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int k = ((u + j) % f.kp) * kPair * BK + chunk * 8;
+            const int h = k / HD, d = k % HD;
+            const size_t part0 = ((size_t)(row * p.NKV + h / G) * kMaxSplit) * 16 + (h % G);
+            const bool live = j < n && row < p.B && k < f.K;
+#pragma unroll
+            for (int z = 0; z < kMaxSplit; ++z) {
+                o[j][z][0] = o[j][z][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                ml[j][z] = make_float2(-INFINITY, 0.f);
+                if (live && z < S) {
+                    const size_t r = part0 + (size_t)z * 16;
+                    ml[j][z] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + r * 2));
+                    const float4* src = reinterpret_cast<const float4*>(p.part_o + r * HD + d);
+                    o[j][z][0] = __ldcg(src);
+                    o[j][z][1] = __ldcg(src + 1);
+                }
+            }
+        }
+        for (int j = 0; j < n; ++j) {
+            const uint32_t t = it + j;
+            if (t >= (uint32_t)kStages && !mbar_wait(&empty[t % kStages], ((t / kStages) - 1) & 1, abort, p.status, 4)) return false;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (j >= n) break;
+            float M = -INFINITY;
+#pragma unroll
+            for (int z = 0; z < kMaxSplit; ++z) M = fmaxf(M, ml[j][z].x);
+            float L = 0.f, v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int z = 0; z < kMaxSplit; ++z) {
+                const float wt = ml[j][z].x == -INFINITY ? 0.f : exp2f(ml[j][z].x - M);
+                L += wt * ml[j][z].y;
+                v[0] += wt * o[j][z][0].x; v[1] += wt * o[j][z][0].y; v[2] += wt * o[j][z][0].z; v[3] += wt * o[j][z][0].w;
+                v[4] += wt * o[j][z][1].x; v[5] += wt * o[j][z][1].y; v[6] += wt * o[j][z][1].z; v[7] += wt * o[j][z][1].w;
+            }
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= inv;
+            uint8_t* xs = x_ring + ((it + j) % kStages) * kXStage;
+            *reinterpret_cast<uint4*>(xs + kb * (NT * 128) + row * 128 + ((c ^ (row & 7)) << 4)) = pack8(v);
+            fence_proxy_async();
+            mbar_arrive(&act_full[(it + j) % kStages]);
+        }
+        it += n;
+        u += n;
+    }
+    return true;
+}
+
+// The token operands of the units [u, seg_end) of one weight tile, in groups of UG, the next group's loads in flight
+// while the current one is converted.  Returns false if a wait ran out.
+template <int NT, int UG, int OP>
+__device__ __forceinline__ bool convert_segment(const Params& p, const PhaseInfo& f, int u, int seg_end, uint8_t* x_ring, uint32_t& it,
+                                                uint64_t* empty, uint64_t* act_full, bool do_ssq, volatile int* abort, int tid) {
+    constexpr int CH = NT * 16 / kWorkers;
+    float rinv[CH];
+#pragma unroll
+    for (int ci = 0; ci < CH; ++ci) {
+        const int row = (tid + ci * kWorkers) >> 4;
+        rinv[ci] = 1.f;
+        if (OP == OP_SWIGLU && row < p.B) rinv[ci] = 1.0f / sqrtf(__ldcg(p.ssq + kSsqStride + row) / (float)p.H + p.eps);
+    }
+    auto wait_stages = [&](int n) {
+        bool ok = true;
+        for (int j = 0; j < n && ok; ++j) {
+            const uint32_t t = it + j;
+            if (t >= (uint32_t)kStages) ok = mbar_wait(&empty[t % kStages], ((t / kStages) - 1) & 1, abort, p.status, 4);
+        }
+        return ok;
+    };
+    RawGroup<NT, UG> ra, rb;
+    int pair = u % f.kp;
+    load_group<NT, UG, OP>(p, f, pair, min(UG, seg_end - u), ra, tid);
+    while (u < seg_end) {
+        const int na = min(UG, seg_end - u), nb = min(UG, seg_end - u - na);
+        if (nb > 0) load_group<NT, UG, OP>(p, f, pair + na, nb, rb, tid);
+        if (!wait_stages(na)) return false;
+        store_group<NT, UG, OP>(p, f, na, ra, rinv, x_ring, it, act_full, do_ssq, tid);
+        it += na; u += na; pair += na;
+        if (nb == 0) break;
+        const int nc = min(UG, seg_end - u - nb);
+        if (nc > 0) load_group<NT, UG, OP>(p, f, pair + nb, nc, ra, tid);
+        if (!wait_stages(nb)) return false;
+        store_group<NT, UG, OP>(p, f, nb, rb, rinv, x_ring, it, act_full, do_ssq, tid);
+        it += nb; u += nb; pair += nb;
+    }
+    return true;
+}
+
 // this CTA's share of `n` floats at `ptr` becomes zero (n a multiple of 4, ptr 16-byte aligned)
 __device__ __forceinline__ void zero_slice(float* ptr, long long n, int tid) {
     const long long n4 = n / 4;
@@ -269,76 +421,139 @@ __device__ __forceinline__ void zero_slice(float* ptr, long long n, int tid) {
     for (long long i = a + tid; i < b; i += kWorkers) q[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-// Attention of request s, kv head kvh, by the workers (the first kAttWarps warps of them compute; all take part
-// in the barriers): the new token's q (G heads) and k are taken from qkv_acc (divided by the row's rms, plus
-// bias), rotated, k and v go into the cache, and the G heads attend over the request's keys.
-__device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc* L, int s, int kvh, uint8_t* scratch, int tid) {
+// Attention of a decode step.  Unit v of a layer is (request s, kv head kvh, part z of S): the keys of (s, kvh) are
+// dealt in tiles of 32, tile i to part i % S and there to warp (i / S) % kAttWarps.
+struct AttUnit { int s, kvh, z, S; };
+
+__device__ __forceinline__ int att_split(const Params& p) {
+    const int units = p.B * p.NKV;
+    int S = (int)gridDim.x / units;
+    return S < 1 ? 1 : (S > kMaxSplit ? kMaxSplit : S);
+}
+__device__ __forceinline__ AttUnit att_unit(const Params& p, int v, int S) {
+    AttUnit a;
+    a.S = S;
+    a.z = v % S;
+    a.kvh = (v / S) % p.NKV;
+    a.s = v / (S * p.NKV);
+    return a;
+}
+
+struct AttGeometry {
+    const int32_t* table;
+    int pos, kv_lo, kv_hi, t_begin, t_end;
+};
+__device__ __forceinline__ AttGeometry att_geometry(const Params& p, int s) {
+    AttGeometry g;
+    g.pos = p.positions[s];
+    g.table = p.block_table + (size_t)s * p.max_pages;
+    g.kv_hi = g.pos + 1;
+    g.kv_lo = (p.window > 0 && g.pos - p.window + 1 > 0) ? g.pos - p.window + 1 : 0;
+    g.t_begin = g.kv_lo / DKV;
+    g.t_end = (g.kv_hi + DKV - 1) / DKV;
+    return g;
+}
+
+// The row of the cache (page * 2 * NKV + kvh) * page_size + slot that holds key `lane` of tile t, or -1 outside
+// [kv_lo, kv_hi).  The same in every layer (the layers of a group share the block table).
+__device__ __forceinline__ int att_tile_row(const Params& p, const AttGeometry& g, int kvh, int t, int lane) {
+    const int tk = t * DKV + lane;
+    if (tk < g.kv_lo || tk >= g.kv_hi) return -1;
+    return (g.table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
+}
+
+// keys and values of a tile into buffer `buf` of this warp; ridx: att_tile_row of this lane (rows of -1: zeros)
+__device__ __forceinline__ void att_load_tile(const Params& p, const __nv_bfloat16* kv, __nv_bfloat16* my_k, int buf, int ridx, int lane) {
+    __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
+    const int v_rows = p.NKV * p.page_size;
+#pragma unroll 4
+    for (int c = lane; c < DKV * CPR; c += 32) {
+        const int r_row = c / CPR, ch = c % CPR;
+        const int r = __shfl_sync(0xffffffffu, ridx, r_row);
+        __nv_bfloat16* dk = kd + r_row * LD + ch * 8;
+        __nv_bfloat16* dv = dk + DKV * LD;
+        if (r >= 0) {
+            const __nv_bfloat16* src = kv + (size_t)r * HD + ch * 8;
+            cp_async16(dk, src);
+            cp_async16(dv, src + (size_t)v_rows * HD);
+        } else {
+            *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// What a warp needs to ask for its first two tiles of the CTA's first unit before q exists: worked out once per
+// step (it is the same for every layer).  n: how many of them hold only earlier positions (the tile with the new
+// token has to wait for this layer's key).
+struct AttPrefetch { int n; int ridx[2]; };
+__device__ __forceinline__ AttPrefetch att_prefetch_plan(const Params& p, const AttUnit& a, int tid) {
+    AttPrefetch pf;
+    pf.n = 0;
+    pf.ridx[0] = pf.ridx[1] = -1;
+    const int warp = tid >> 5, lane = tid & 31;
+    if (warp < kAttWarps) {
+        const AttGeometry g = att_geometry(p, a.s);
+        for (; pf.n < 2; ++pf.n) {
+            const int t = g.t_begin + a.z + a.S * (warp + kAttWarps * pf.n);
+            if (t >= g.t_end - 1) break;
+            pf.ridx[pf.n] = att_tile_row(p, g, a.kvh, t, lane);
+        }
+    }
+    return pf;
+}
+__device__ __forceinline__ int attention_prefetch(const Params& p, const LayerDesc* L, const AttPrefetch& pf, uint8_t* scratch, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    if (warp < kAttWarps) {
+        __nv_bfloat16* my_k = reinterpret_cast<__nv_bfloat16*>(scratch) + 16 * LD + (size_t)warp * 4 * DKV * LD;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (i < pf.n) {
+                att_load_tile(p, L->kv, my_k, i, pf.ridx[i], lane);
+                cp_async_commit();
+            }
+        }
+    }
+    return pf.n;
+}
+
+// The unit's share of the attention, by the workers (the first kAttWarps warps of them compute; all take part in
+// the barriers): the new token's q (G heads) and k are taken from qkv_acc (divided by the row's rms, plus bias),
+// rotated, k and v go into the cache (by the part that owns the last tile), and the G heads attend over the part's
+// keys.  The part leaves its un-normalised result with its maximum and sum; the o-projection's operand is made of
+// the parts (convert_segment_merge).
+__device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc* L, const AttUnit& a, uint8_t* scratch,
+                                               int issued, int tid, unsigned long long* trace = nullptr) {
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(scratch);          // [16][LD]  (G heads, zero-padded)
     __nv_bfloat16* kvs = qs + 16 * LD;                                      // [kAttWarps][2 buffers][K | V][DKV][LD]
     const int warp = tid >> 5, lane = tid & 31;
+    const int s = a.s, kvh = a.kvh, S = a.S;
     const int G = p.NH / p.NKV;
-    const int pos = p.positions[s];
     const int half = HD / 2;
+    const AttGeometry g = att_geometry(p, s);
+    const int pos = g.pos, t_begin = g.t_begin, t_end = g.t_end;
     const float* row = p.qkv_acc + (size_t)s * p.QKV;
     const float rms = 1.0f / sqrtf(__ldcg(p.ssq + s) / (float)p.H + p.eps);
     const int slot = p.slot_mapping[s];
     __nv_bfloat16* kv = L->kv;
     __nv_bfloat16* page_base = kv + ((size_t)(slot / p.page_size) * 2 * p.NKV + kvh) * p.page_size * HD + (size_t)(slot % p.page_size) * HD;
     const float* bias = L->qkv_bias;
-
-    const int32_t* table = p.block_table + (size_t)s * p.max_pages;
-    const int kv_hi = pos + 1;
-    const int kv_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int t_begin = kv_lo / DKV, t_end = (kv_hi + DKV - 1) / DKV;
     __nv_bfloat16* my_k = kvs + (size_t)warp * 4 * DKV * LD;               // [buffer][K | V]
-
-    auto load_tile = [&](int buf, int t) {
-        __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
-        const int tk = t * DKV + lane;                                     // lane = row of the tile
-        int ridx = -1;
-        if (tk >= kv_lo && tk < kv_hi) ridx = (table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
-        const int v_rows = p.NKV * p.page_size;
-#pragma unroll 4
-        for (int c = lane; c < DKV * CPR; c += 32) {
-            const int r_row = c / CPR, ch = c % CPR;
-            const int r = __shfl_sync(0xffffffffu, ridx, r_row);
-            __nv_bfloat16* dk = kd + r_row * LD + ch * 8;
-            __nv_bfloat16* dv = dk + DKV * LD;
-            if (r >= 0) {
-                const __nv_bfloat16* src = kv + (size_t)r * HD + ch * 8;
-                cp_async16(dk, src);
-                cp_async16(dv, src + (size_t)v_rows * HD);
-            } else {
-                *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
-            }
-        }
-    };
-
-    // 0. the tiles that hold only earlier positions can be on their way while q and k are rotated
-    int issued = 0;
-    if (warp < kAttWarps) {
-        for (; issued < 2; ++issued) {
-            const int t = t_begin + warp + issued * kAttWarps;
-            if (t >= t_end - 1) break;
-            load_tile(issued, t);
-            cp_async_commit();
-        }
-    }
+    const bool writes_kv = a.z == (t_end - 1 - t_begin) % S;               // the part that owns the tile with the new token
+    const int t_first = t_begin + a.z + S * warp, t_step = S * kAttWarps;  // this warp's tiles
 
     // 1. rotate q (G heads) and k (one head), copy v; q to shared memory, k and v to the cache
     for (int i = tid; i < 16 * CPR; i += kWorkers)
         if (i / CPR >= G) *reinterpret_cast<uint4*>(qs + (i / CPR) * LD + (i % CPR) * 8) = make_uint4(0, 0, 0, 0);
     for (int i = tid; i < (G + 2) * half; i += kWorkers) {
         const int h = i / half, d = i % half;                              // h < G: q head; G: k; G + 1: v
+        if (h >= G && !writes_kv) continue;
         const int src_head = h < G ? kvh * G + h : (h == G ? p.NH + kvh : p.NH + p.NKV + kvh);
         float x0 = __ldcg(row + src_head * HD + d) * rms, x1 = __ldcg(row + src_head * HD + d + half) * rms;
         if (bias) { x0 += bias[src_head * HD + d]; x1 += bias[src_head * HD + d + half]; }
         if (p.rotary && h <= G) {
-            const float freq = 1.0f / powf(p.theta, (2.0f * (float)d) / (float)HD);
-            float sn, cs;
-            sincosf((float)pos * freq, &sn, &cs);
-            const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+            const float2 cs = __ldcg(p.rope_tab + (size_t)s * half + d);
+            const float y0 = x0 * cs.x - x1 * cs.y, y1 = x0 * cs.y + x1 * cs.x;
             x0 = y0;
             x1 = y1;
         }
@@ -353,6 +568,7 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
     }
     __threadfence_block();        // the new key and value are read back below by whichever warp gets their tile
     workers_sync();
+    if (trace && tid == 0) trace[2] = global_ns();
 
     // 2. every computing warp walks its share of the key tiles
     const bool valid_a = (lane >> 2) < G, valid_b = (lane >> 2) + 8 < G;
@@ -363,10 +579,10 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
 
     if (warp < kAttWarps) {
         int n_done = 0;
-        for (int t = t_begin + warp; t < t_end; t += kAttWarps, ++n_done) {
+        for (int t = t_first; t < t_end; t += t_step, ++n_done) {
             const int buf = n_done & 1;
-            for (; issued < n_done + 2 && t_begin + warp + issued * kAttWarps < t_end; ++issued) {
-                load_tile(issued & 1, t_begin + warp + issued * kAttWarps);
+            for (; issued < n_done + 2 && t_first + issued * t_step < t_end; ++issued) {
+                att_load_tile(p, kv, my_k, issued & 1, att_tile_row(p, g, kvh, t_first + issued * t_step, lane), lane);
                 cp_async_commit();
             }
             if (issued == n_done + 2) cp_async_wait<1>(); else cp_async_wait<0>();
@@ -378,14 +594,14 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
             for (int i = 0; i < DKV / 8; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
-                uint32_t a[4];
-                ldmatrix_x4(a, qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+                uint32_t af[4];
+                ldmatrix_x4(af, qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
                 for (int nb = 0; nb < DKV / 16; ++nb) {
                     uint32_t b[4];
                     ldmatrix_x4(b, kb + (nb * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
-                    mma_bf16(sc[2 * nb], a, b[0], b[1]);
-                    mma_bf16(sc[2 * nb + 1], a, b[2], b[3]);
+                    mma_bf16(sc[2 * nb], af, b[0], b[1]);
+                    mma_bf16(sc[2 * nb + 1], af, b[2], b[3]);
                 }
             }
             float mx_a = m_a, mx_b = m_b;
@@ -449,6 +665,7 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
 
     // 3. merge the warps' partial results in shared memory (the tile buffers are free now), in warp order
     workers_sync();
+    if (trace && tid == 0) trace[3] = global_ns();
     float* mo = reinterpret_cast<float*>(kvs);                             // [kAttWarps][16][HD]
     float* ml = mo + kAttWarps * 16 * HD;                                  // [kAttWarps][16][2]
     if (warp < kAttWarps) {
@@ -464,6 +681,9 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
         }
     }
     workers_sync();
+    const size_t unit = (size_t)s * p.NKV + kvh;
+    float* my_po = p.part_o + (unit * kMaxSplit + a.z) * 16 * HD;
+    float* my_pml = p.part_ml + (unit * kMaxSplit + a.z) * 32;
     for (int i = tid; i < G * HD; i += kWorkers) {
         const int r = i / HD, d = i % HD;
         float M = -INFINITY;
@@ -477,17 +697,20 @@ __device__ __forceinline__ void attention_unit(const Params& p, const LayerDesc*
             Lsum += wt * ml[(w * 16 + r) * 2 + 1];
             acc += wt * mo[((size_t)w * 16 + r) * HD + d];
         }
-        p.attn_out[(size_t)s * p.NH * HD + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+        my_po[r * HD + d] = acc;
+        if (d == 0) { my_pml[r * 2] = M; my_pml[r * 2 + 1] = Lsum; }
     }
     workers_sync();               // the scratch is free for the next unit
+    if (trace && tid == 0) trace[6] = global_ns();
 }
 
 template <int NT>
 struct Cfg {
     static constexpr int kXStage = kPair * NT * 128;                       // two [NT x 64] bf16 tiles
-    static constexpr int kScratch = ((kStages * kXStage > kAttBytes ? kStages * kXStage : kAttBytes) + 1023) / 1024 * 1024;
-    static constexpr int kTmemCols = NT < 32 ? 32 : NT;
-    static constexpr int kSmemBytes = 1024 + kStages * kStageW + kScratch + 512;
+    static constexpr int kAttScratch = (kAttBytes + 1023) / 1024 * 1024;   // apart from the ring: filled during the qkv product
+    static constexpr int kTmemCols = kAccs * NT < 32 ? 32 : kAccs * NT;
+    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "tensor memory columns: a power of two");
+    static constexpr int kSmemBytes = 1024 + kStages * kStageW + kStages * kXStage + kAttScratch + 512;
     static_assert(kSmemBytes <= kSmemLimit, "shared memory");
 };
 
@@ -498,20 +721,21 @@ decode_layers_kernel(const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* w_ring = smem;                                    // [kStages][2][128 x 64] bf16
-    uint8_t* x_ring = smem + kStages * kStageW;                // [kStages][2][NT x 64] bf16; the attention's scratch too
-    uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + C::kScratch);
+    uint8_t* x_ring = smem + kStages * kStageW;                // [kStages][2][NT x 64] bf16
+    uint8_t* att_scratch = x_ring + kStages * C::kXStage;      // q, key and value tiles, the warps' partial results
+    uint64_t* bars = reinterpret_cast<uint64_t*>(att_scratch + C::kAttScratch);
     uint64_t* full = bars;                                     // TMA -> MMA
     uint64_t* empty = bars + kStages;                          // MMA -> TMA and workers
     uint64_t* act_full = bars + 2 * kStages;                   // workers -> MMA
-    uint64_t* acc_full = bars + 3 * kStages;                   // MMA -> workers
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+    uint64_t* acc_full = bars + 3 * kStages;                   // [kAccs] MMA -> workers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + kAccs);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         *abort = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&act_full[s], kWorkers); }
-        mbar_init(acc_full, 1);
+        for (int a = 0; a < kAccs; ++a) mbar_init(&acc_full[a], 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -528,19 +752,11 @@ decode_layers_kernel(const Params p) {
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int layer = 0; layer < p.num_layers && ok; ++layer) {
-                const LayerDesc* L = p.layers + layer;
-                for (int ph = 0; ph < 4 && ok; ++ph) {
-                    const PhaseInfo f = phase_info(p, L, ph);
-                    int u0, u1;
-                    unit_range(f, u0, u1);
-                    for (int u = u0; u < u1; ++u, ++it) {
-                        const int s = it % kStages;
-                        if (it >= (uint32_t)kStages && !(ok = mbar_wait(&empty[s], ((it / kStages) - 1) & 1, abort, p.status, 1))) break;
-                        mbar_arrive_expect_tx(&full[s], kStageW);
-                        tma_load_3d(w_ring + s * kStageW, f.map, &full[s], 0, (u / f.kp) * BM, (u % f.kp) * kPair);
-                    }
-                }
+            for (UnitWalk ld = walk_begin(p); !ld.done; walk_next(p, ld), ++it) {
+                const int s = it % kStages;
+                if (it >= (uint32_t)kStages && !(ok = mbar_wait(&empty[s], ((it / kStages) - 1) & 1, abort, p.status, 1))) break;
+                mbar_arrive_expect_tx(&full[s], kStageW);
+                tma_load_3d(w_ring + s * kStageW, ld.f.map, &full[s], 0, (ld.u / ld.f.kp) * BM, (ld.u % ld.f.kp) * kPair);
             }
             // the copies asked for last must have landed before the CTA's shared memory goes (after a normal run
             // they have: the MMAs that read them are done; after an abort this waits for them, with a limit)
@@ -554,54 +770,68 @@ decode_layers_kernel(const Params p) {
         // ---------------------------------------------------------------- the MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, NT);
-            uint32_t it = 0;
+            uint32_t it = 0, seg = 0;
             bool ok = true;
-            for (int layer = 0; layer < p.num_layers && ok; ++layer) {
-                const LayerDesc* L = p.layers + layer;
-                for (int ph = 0; ph < 4 && ok; ++ph) {
-                    const PhaseInfo f = phase_info(p, L, ph);
-                    int u0, u1;
-                    unit_range(f, u0, u1);
-                    for (int u = u0; u < u1 && ok;) {
-                        const int seg_end = min(u1, (u / f.kp + 1) * f.kp);
-                        bool fresh = true;
-                        for (; u < seg_end; ++u, ++it) {
-                            const int s = it % kStages;
-                            const uint32_t par = (it / kStages) & 1;
-                            if (!(ok = mbar_wait(&full[s], par, abort, p.status, 2))) break;
-                            if (!(ok = mbar_wait(&act_full[s], par, abort, p.status, 3))) break;
-                            tc_fence_after_sync();
-                            const uint64_t w_desc = umma_desc_k_sw128(smem_u32(w_ring + s * kStageW));
-                            const uint64_t x_desc = umma_desc_k_sw128(smem_u32(x_ring + s * C::kXStage));
+            for (UnitWalk w = walk_begin(p); !w.done && ok;) {
+                // a segment: this CTA's units of one weight tile; its sums gather in accumulator seg % kAccs
+                const int tile = w.u / w.f.kp, layer = w.layer, ph = w.ph;
+                const uint32_t d_tmem = tmem_base + (seg % kAccs) * NT;
+                bool fresh = true;
+                while (!w.done && w.layer == layer && w.ph == ph && w.u / w.f.kp == tile) {
+                    const int s = it % kStages;
+                    const uint32_t par = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(&full[s], par, abort, p.status, 2))) break;
+                    if (!(ok = mbar_wait(&act_full[s], par, abort, p.status, 3))) break;
+                    tc_fence_after_sync();
+                    const uint64_t w_desc = umma_desc_k_sw128(smem_u32(w_ring + s * kStageW));
+                    const uint64_t x_desc = umma_desc_k_sw128(smem_u32(x_ring + s * C::kXStage));
 #pragma unroll
-                            for (int j = 0; j < kPair; ++j) {
+                    for (int j = 0; j < kPair; ++j) {
 #pragma unroll
-                                for (int k = 0; k < BK / UMMA_K; ++k) {
-                                    umma_bf16(tmem_base, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
-                                              umma_desc_advance(x_desc, j * (NT * 128) + k * UMMA_K * 2), idesc, !(fresh && j == 0 && k == 0));
-                                }
-                            }
-                            fresh = false;
-                            umma_commit(&empty[s]);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            umma_bf16(d_tmem, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
+                                      umma_desc_advance(x_desc, j * (NT * 128) + k * UMMA_K * 2), idesc, !(fresh && j == 0 && k == 0));
                         }
-                        if (ok) umma_commit(acc_full);
                     }
+                    fresh = false;
+                    umma_commit(&empty[s]);
+                    walk_next(p, w);
+                    ++it;
                 }
+                if (ok) umma_commit(&acc_full[seg % kAccs]);
+                ++seg;
             }
         }
     } else {
         // ---------------------------------------------------------------- the workers
         const int tid = threadIdx.x - 64;
         const int quarter = warp & 3, col_half = (warp - 2) >> 2;   // two warps share a quarter of the lanes and split the tokens
-        constexpr int UG = 64 / NT;                           // units whose operands are fetched together
+        constexpr int UG = NT <= 16 ? 2 : 1;                        // units whose operands are fetched together
+        const int S = att_split(p), att_units = p.B * p.NKV * S;
+        const int half = HD / 2;
         forge::pdl_wait();                                   // the residual stream comes from the kernel before
         uint32_t it = 0, seg = 0, nbar = 0;
+        int att_issued = 0;
         bool ok = true;
-        // the first product adds into qkv_acc and ssq1
+        // (profiling) slot k of the record of the barrier that will end the current phase
+        auto mark = [&](int k) {
+            if (p.timeline && tid == 0) p.timeline[((size_t)blockIdx.x * (1 + 5 * p.num_layers) + nbar) * 8 + k] = global_ns();
+        };
+        // before the first layer: the first product adds into qkv_acc and ssq1; the step's rotary angles
         zero_slice(p.qkv_acc, (long long)p.B * p.QKV, tid);
-        if (blockIdx.x == 0 && tid < kMaxTokens) p.ssq[tid] = 0.f;
+        if (blockIdx.x == 0 && tid < kSsqStride) p.ssq[tid] = 0.f;
+        if (p.rotary) {
+            for (int i = blockIdx.x * kWorkers + tid; i < p.B * half; i += gridDim.x * kWorkers) {
+                const int d = i % half;
+                const float freq = 1.0f / powf(p.theta, (2.0f * (float)d) / (float)HD);
+                float sn, cs;
+                sincosf((float)p.positions[i / half] * freq, &sn, &cs);
+                p.rope_tab[i] = make_float2(cs, sn);
+            }
+        }
         ok = grid_barrier(p, ++nbar * gridDim.x, abort, tid);
         if (tid == 0) forge::pdl_launch_dependents();        // every CTA is resident: the next kernel may be set up
+        const AttPrefetch att_pf = (int)blockIdx.x < att_units ? att_prefetch_plan(p, att_unit(p, blockIdx.x, S), tid) : AttPrefetch{0, {-1, -1}};
         for (int layer = 0; layer < p.num_layers && ok; ++layer) {
             const LayerDesc* L = p.layers + layer;
             for (int ph = 0; ph < 4 && ok; ++ph) {
@@ -609,55 +839,64 @@ decode_layers_kernel(const Params p) {
                 int u0, u1;
                 unit_range(f, u0, u1);
                 for (int u = u0; u < u1 && ok;) {
-                    const int tile = u / f.kp;
-                    const int seg_end = min(u1, (tile + 1) * f.kp);
-                    while (u < seg_end) {
-                        const int n_units = min(UG, seg_end - u);
-                        for (int j = 0; j < n_units && ok; ++j) {
-                            const uint32_t t = it + j;
-                            if (t >= (uint32_t)kStages) ok = mbar_wait(&empty[t % kStages], ((t / kStages) - 1) & 1, abort, p.status, 4);
-                        }
-                        if (!ok) break;
+                    // up to kAccs tiles: first the token operands of all their units (so that no MMA waits for an
+                    // epilogue), then the tiles' sums
+                    int tiles[kAccs], n_tiles = 0;
+                    const uint32_t seg0 = seg;
+                    while (u < u1 && n_tiles < kAccs && ok) {
+                        const int tile = u / f.kp;
+                        const int seg_end = min(u1, (tile + 1) * f.kp);
                         const bool do_ssq = f.ssq != nullptr && tile == 0;
-                        if (f.op == OP_NORMW) convert_group<NT, UG, OP_NORMW>(p, f, u % f.kp, n_units, x_ring, it, act_full, do_ssq, tid);
-                        else if (f.op == OP_COPY) convert_group<NT, UG, OP_COPY>(p, f, u % f.kp, n_units, x_ring, it, act_full, false, tid);
-                        else convert_group<NT, UG, OP_SWIGLU>(p, f, u % f.kp, n_units, x_ring, it, act_full, false, tid);
-                        u += n_units;
-                        it += n_units;
+                        if (f.op == OP_NORMW) ok = convert_segment<NT, UG, OP_NORMW>(p, f, u, seg_end, x_ring, it, empty, act_full, do_ssq, abort, tid);
+                        else if (f.op == OP_MERGE) ok = convert_segment_merge<NT>(p, f, u, seg_end, x_ring, it, empty, act_full, S, abort, tid);
+                        else ok = convert_segment<NT, UG, OP_SWIGLU>(p, f, u, seg_end, x_ring, it, empty, act_full, false, abort, tid);
+                        tiles[n_tiles++] = tile;
+                        u = seg_end;
                     }
                     if (!ok) break;
-                    // the tile's (partial) sums: one output feature per thread, tokens along the columns
-                    if (!(ok = mbar_wait(acc_full, seg & 1, abort, p.status, 5))) break;
-                    ++seg;
-                    tc_fence_after_sync();
-                    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-                    const int n = tile * BM + quarter * 32 + lane;
+                    mark(2);
+                    for (int i = 0; i < n_tiles; ++i, ++seg) {
+                        // a tile's (partial) sums: one output feature per thread, tokens along the columns
+                        if (!(ok = mbar_wait(&acc_full[seg % kAccs], (seg / kAccs) & 1, abort, p.status, 5))) break;
+                        if (i == 0) mark(3);
+                        tc_fence_after_sync();
+                        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (seg % kAccs) * NT;
+                        const int n = tiles[i] * BM + quarter * 32 + lane;
 #pragma unroll
-                    for (int c = 16 * col_half; c < NT; c += 32) {
-                        if (c >= p.B) break;                 // uniform over the warp
-                        uint32_t r[16];
-                        tmem_ld_32x32b_x16(t_row + c, r);
-                        tmem_ld_wait();
-                        if (n < f.n_out) {
+                        for (int c = 16 * col_half; c < NT; c += 32) {
+                            if (c >= p.B) break;                 // uniform over the warp
+                            uint32_t r[16];
+                            tmem_ld_32x32b_x16(t_row + c, r);
+                            tmem_ld_wait();
+                            if (n < f.n_out) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (c + i < p.B) atomicAdd(f.out + (size_t)(c + i) * f.ldo + n, __uint_as_float(r[i]));
+                                for (int e = 0; e < 16; ++e)
+                                    if (c + e < p.B) atomicAdd(f.out + (size_t)(c + e) * f.ldo + n, __uint_as_float(r[e]));
+                            }
                         }
+                        tc_fence_before_sync();
                     }
-                    tc_fence_before_sync();
+                    if (!ok) seg = seg0 + n_tiles;
+                    mark(4);
                 }
                 if (!ok) break;
-                if (ph == 3) {
+                if (ph == 0) {
+                    // the keys of earlier positions do not wait for this layer's q: they travel during the barrier
+                    att_issued = attention_prefetch(p, L, att_pf, att_scratch, tid);
+                } else if (ph == 3) {
                     // nobody reads qkv_acc and ssq1 any more in this layer: clear them for the next one
                     zero_slice(p.qkv_acc, (long long)p.B * p.QKV, tid);
-                    if (blockIdx.x == 0 && tid < kMaxTokens) p.ssq[tid] = 0.f;
+                    if (blockIdx.x == 0 && tid < kSsqStride) p.ssq[tid] = 0.f;
                 }
                 if (!(ok = grid_barrier(p, ++nbar * gridDim.x, abort, tid))) break;
                 if (ph == 0) {
+                    for (int v = blockIdx.x; v < att_units; v += gridDim.x) {
+                        attention_unit(p, L, att_unit(p, v, S), att_scratch, att_issued, tid,
+                                       p.timeline ? p.timeline + ((size_t)blockIdx.x * (1 + 5 * p.num_layers) + nbar) * 8 : nullptr);
+                        att_issued = 0;
+                    }
                     zero_slice(p.gu_acc, (long long)p.B * 2 * p.I, tid);
-                    if (blockIdx.x == 0 && tid < kMaxTokens) p.ssq[kMaxTokens + tid] = 0.f;
-                    for (int unit = blockIdx.x; unit < p.B * p.NKV; unit += gridDim.x)
-                        attention_unit(p, L, unit / p.NKV, unit % p.NKV, x_ring, tid);
+                    if (blockIdx.x == 0 && tid < kSsqStride) p.ssq[kSsqStride + tid] = 0.f;
                     if (!(ok = grid_barrier(p, ++nbar * gridDim.x, abort, tid))) break;
                 }
             }
@@ -720,7 +959,7 @@ extern "C" int forge_decode_layers_max_tokens() { return kMaxTokens; }
 // Why these sizes cannot run here, or null.  (The caller falls back to one kernel per operation.)
 static const char* unsupported(int B, int H, int I, int NH, int NKV, int head_dim) {
     if (head_dim != HD) return "built for another head size";
-    if (B < 1 || B > kMaxTokens) return "more than 64 tokens";
+    if (B < 1 || B > kMaxTokens) return "more than 16 tokens";
     if (NH <= 0 || NKV <= 0 || NH % NKV != 0 || NH / NKV > 16) return "more than 16 query heads per kv head";
     if (H % 64 != 0 || I % 64 != 0 || (NH * HD) % 64 != 0) return "a reduction size that is not a multiple of 64";
     return nullptr;
@@ -754,24 +993,26 @@ extern "C" int forge_decode_layers_describe(void* descs, int layer, const void* 
 }
 
 // Runs `num_layers` layers on the residual stream resid [B, H] (fp32, in place).  Scratch, all the caller's:
-// qkv_acc fp32 [B, (NH+2NKV)*HD], gu_acc fp32 [B, 2I], ssq fp32 [128], attn_out bf16 [B, NH*HD], barrier uint32 [4]
-// (zero before the first call; the kernel leaves it zero unless a wait ran out).
-// Calls on one device must not overlap (they would share the scratch).
+// qkv_acc fp32 [B, (NH+2NKV)*HD], gu_acc fp32 [B, 2I], ssq fp32 [128], rope_tab fp32 [B, HD], part_o fp32
+// [B*NKV, 4, 16, HD], part_ml fp32 [B*NKV, 4, 16, 2] and barrier uint32 [4] (zero before the first call; the kernel
+// leaves it zero unless a wait ran out).
+// Calls on one device must not overlap (they would share the scratch).  prefetch_units: non-zero: weights are asked
+// into L2 two or three products before they are needed (a layer's matrices should fit the L2).  timeline: null, or uint64 [CTAs (one per SM)]
+// [1 + 5 * num_layers barriers][2] that receives the time (ns) at which each CTA reached and left each barrier.
 extern "C" int forge_decode_layers(const void* descs, int num_layers, float* resid, float* qkv_acc, float* gu_acc, float* ssq,
-                                   void* attn_out, const int32_t* block_table, const int32_t* positions,
+                                   void* rope_tab, float* part_o, float* part_ml,
+                                   const int32_t* block_table, const int32_t* positions,
                                    const int32_t* slot_mapping, unsigned int* barrier, int* status, int B, int H, int I, int NH,
                                    int NKV, int head_dim, int page_size, int max_pages, int window, int rotary, float theta,
-                                   float scale, float eps, cudaStream_t stream) {
+                                   float scale, float eps, int prefetch_units, unsigned long long* timeline, cudaStream_t stream) {
     const char* why = unsupported(B, H, I, NH, NKV, head_dim);
     if (why) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_layers: %s", why);
     if (num_layers < 0 || page_size <= 0 || max_pages <= 0) return forge::fail(FORGE_ERR_ARG, "decode_layers: bad sizes");
     if (num_layers == 0) return FORGE_OK;
-    Params p{static_cast<const LayerDesc*>(descs), num_layers, resid, qkv_acc, gu_acc, ssq, static_cast<__nv_bfloat16*>(attn_out),
-             block_table, positions, slot_mapping, barrier, status, B, H, I, NH, NKV, (NH + 2 * NKV) * HD, page_size, max_pages,
-             window, rotary, theta, scale * 1.4426950408889634f, eps, sm100::kWaitLimitNs};
-    if (B <= 16) return launch_layers<16>(p, stream);
-    if (B <= 32) return launch_layers<32>(p, stream);
-    return launch_layers<64>(p, stream);
+    Params p{static_cast<const LayerDesc*>(descs), num_layers, resid, qkv_acc, gu_acc, ssq,
+             static_cast<float2*>(rope_tab), part_o, part_ml, block_table, positions, slot_mapping, barrier, status, B, H, I, NH, NKV, (NH + 2 * NKV) * HD, page_size, max_pages,
+             window, rotary, theta, scale * 1.4426950408889634f, eps, sm100::kWaitLimitNs, prefetch_units < 0 ? 0 : prefetch_units, timeline};
+    return launch_layers<16>(p, stream);
 }
 
 // For the test of the bounded wait: one CTA arrives at a barrier that expects two; the wait must run out after

@@ -125,10 +125,7 @@ class Model:
         fused = getattr(self, "_fused", None)
         if fused is None or batch.num_tokens != batch.num_requests or batch.num_tokens > fused[0].max_tokens:
             return False
-        # one CTA serves a (request, kv head) with four warps: with few requests and very long contexts the
-        # one-kernel-per-operation path, whose attention spreads a request's keys over several CTAs, is faster
-        max_ctx = getattr(batch, "max_context", None) or (max(batch.host_context_before) + 1)
-        return max_ctx <= 4096 or batch.num_requests * fused[0].dims[3] >= 128
+        return True
 
     # ---------------------------------------------------------------------------------- forward
     def forward(self, batch, position_caches):

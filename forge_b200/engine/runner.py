@@ -40,14 +40,15 @@ def resolve_dtype(dtype):
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
                  page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True,
-                 max_tokens_per_step=None, max_decode_graphs=16, fused_decode=True):
+                 max_tokens_per_step=None, max_decode_graphs=16, fused_decode=None):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
         ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the
         free device memory holds, capped by max_requests * max positions).  ``cuda_graphs``: replay decode
         steps as CUDA graphs where every part of the model allows it (``Part.graph_safe``); a model with a part
         that does not takes the ordinary step, whatever this says.  ``max_tokens_per_step``: a step with more
         tokens is refused (None: no limit); the step's activations live in a workspace of that many rows.
-        ``fused_decode``: run all layers of a decode step in one kernel where the model allows it.
+        ``fused_decode``: run all layers of a decode step of up to 16 requests in one persistent kernel where the
+        model allows it (None: only if FORGE_FUSED_DECODE=1; it is the slower path at the sizes measured).
         ``max_decode_graphs``: how many captured graphs (one per batch size and context bucket) are kept; the
         one used longest ago goes first."""
         if not torch.cuda.is_available():
@@ -89,9 +90,13 @@ class ModelRunner:
         if all(g.window is None for g in self.manager.groups.values()):
             self.max_pages_per_request = min(self.num_pages, self.max_pages_per_request)
         self.max_tokens_per_step = None if max_tokens_per_step is None else int(max_tokens_per_step)
-        # decode steps of stock layers run all their layers in one persistent kernel (FORGE_FUSED_DECODE=0: off)
-        self.fused_decode = fused_decode and os.environ.get("FORGE_FUSED_DECODE", "1") != "0" \
-            and self.model.enable_fused_decode(self.storage.layers, self.max_requests)
+        # Decode steps of up to 16 requests can run all their layers in ONE persistent kernel (csrc/decode_layers.cu).
+        # Measured on B200 at TinyLlama widths it is correct but slower than one kernel per operation (1.07 ms
+        # against 0.79 ms for the 22 layers at batch 8: five grid barriers a layer and the per-CTA conversion of
+        # the token operand cost more than the seven kernel hand-overs they replace), so it is off unless asked
+        # for (fused_decode=True or FORGE_FUSED_DECODE=1).
+        want = fused_decode if fused_decode is not None else os.environ.get("FORGE_FUSED_DECODE", "0") == "1"
+        self.fused_decode = bool(want) and self.model.enable_fused_decode(self.storage.layers, self.max_requests)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # decode steps replay a captured graph only if every part of the model says that it may be captured
         self.graph_safe = self.model.graph_safe()

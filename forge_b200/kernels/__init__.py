@@ -6,6 +6,7 @@ library's message on a non-zero return.  There is no CPU or PyTorch fallback: if
 compiled or loaded the first call that needs it raises.
 """
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -57,7 +58,7 @@ _SIGNATURES = {
         "forge_decode_layers_desc_bytes": [],
         "forge_decode_layers_supports": [_I] * 6,
         "forge_decode_layers_describe": [_P, _I] + [_P] * 8 + [_I] * 5,
-        "forge_decode_layers": [_P, _I] + [_P] * 10 + [_I] * 10 + [_F, _F, _F, _P],
+        "forge_decode_layers": [_P, _I] + [_P] * 12 + [_I] * 10 + [_F, _F, _F, _I, _P, _P],
         "forge_decode_layers_barrier_probe": [_P, _P, ctypes.c_ulonglong, _P],
     },
 }
@@ -456,7 +457,7 @@ class DecodeLayers:
     at most ``max_tokens`` single tokens through every layer, in place.  The object owns the kernel's scratch
     (fp32 results of the projections, attention output, barrier words), so calls must not overlap on the GPU.
     """
-    MAX_TOKENS = 64
+    MAX_TOKENS = 16
 
     @staticmethod
     def supports(hidden, intermediate, n_heads, n_kv_heads, head_dim, tokens=1):
@@ -475,6 +476,9 @@ class DecodeLayers:
         self.page_size, self.theta, self.rotary, self.eps, self.window = int(page_size), float(theta), bool(rotary), float(eps), int(window or 0)
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.max_tokens = min(int(max_tokens), self.MAX_TOKENS)
+        # weights are asked into L2 two or three products ahead of their use (0: off); a layer's matrices must fit
+        # the L2 beside what is in use for that to pay
+        self.prefetch_units = int(os.environ.get("FORGE_DECODE_PREFETCH_UNITS", "1"))
         dev = layers[0]["wqkv"].device
         self.num_layers = len(layers)
         nbytes = lib.forge_decode_layers_desc_bytes()
@@ -494,11 +498,15 @@ class DecodeLayers:
         self.qkv_acc = torch.zeros(B * qkv, dtype=torch.float32, device=dev)
         self.gu_acc = torch.zeros(B * 2 * intermediate, dtype=torch.float32, device=dev)
         self.ssq = torch.zeros(128, dtype=torch.float32, device=dev)
-        self.attn_out = torch.zeros(B * n_heads * head_dim, dtype=torch.bfloat16, device=dev)
+        self.rope_tab = torch.zeros(B * head_dim, dtype=torch.float32, device=dev)
+        self.part_o = torch.zeros(B * n_kv_heads * 4 * 16 * head_dim, dtype=torch.float32, device=dev)
+        self.part_ml = torch.zeros(B * n_kv_heads * 4 * 16 * 2, dtype=torch.float32, device=dev)
         self.barrier = torch.zeros(4, dtype=torch.int32, device=dev)
 
-    def run(self, residual, block_table, positions, slot_mapping):
-        """residual fp32 [B, H], updated in place; block_table int32 [B, max_pages]; positions, slot_mapping int32 [B]."""
+    def run(self, residual, block_table, positions, slot_mapping, timeline=None):
+        """residual fp32 [B, H], updated in place; block_table int32 [B, max_pages]; positions, slot_mapping int32 [B].
+        ``timeline``: an int64 tensor [SMs, 1 + 5 * layers, 2] that receives when each CTA reached and left each of
+        the kernel's barriers (ns of the device's clock), for a look at where a step's time goes."""
         H, I, NH, NKV, HD = self.dims
         B = residual.shape[0]
         if B > self.max_tokens or residual.shape[1] != H:
@@ -506,10 +514,12 @@ class DecodeLayers:
         lib = self.lib
         _check(lib, lib.forge_decode_layers(
             self.descs.data_ptr(), self.num_layers, _need(residual, "residual", torch.float32, 2), self.qkv_acc.data_ptr(),
-            self.gu_acc.data_ptr(), self.ssq.data_ptr(), self.attn_out.data_ptr(), _need(block_table, "block_table", torch.int32, 2),
+            self.gu_acc.data_ptr(), self.ssq.data_ptr(), self.rope_tab.data_ptr(), self.part_o.data_ptr(),
+            self.part_ml.data_ptr(), _need(block_table, "block_table", torch.int32, 2),
             _need(positions, "positions", torch.int32), _need(slot_mapping, "slot_mapping", torch.int32), self.barrier.data_ptr(),
             _need(_gemm_status(residual.device), "status", torch.int32), B, H, I, NH, NKV, HD, self.page_size,
-            block_table.shape[1], self.window, 1 if self.rotary else 0, self.theta, self.scale, self.eps, _stream()), "decode_layers")
+            block_table.shape[1], self.window, 1 if self.rotary else 0, self.theta, self.scale, self.eps, self.prefetch_units,
+            _opt(timeline, "timeline", torch.int64), _stream()), "decode_layers")
         return residual
 
     def reset_after_error(self):

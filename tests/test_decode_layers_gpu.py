@@ -1,6 +1,6 @@
 """The persistent kernel that runs all layers of a decode step, alone, against plain functions: several layers,
 widths that are no powers of two, groups of 1 to 8 query heads, q/k/v bias, a window, contexts on and around page
-and tile edges, 1 to 64 tokens; and its grid barrier's time limit."""
+and tile edges, 1 to 16 tokens; and its grid barrier's time limit."""
 import math
 
 import pytest
@@ -58,7 +58,8 @@ def test_all_layers_of_a_decode_step(H, I, nh, nkv, hd, bias, window):
     ps, theta, eps, n_layers = 16, 30000.0, 1e-3, 3
     assert k.DecodeLayers.supports(H, I, nh, nkv, hd)
     layers = _layers(n_layers, H, I, nh, nkv, hd, bias, seed=H)
-    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 300, 700], [0], [5] * 40 + [129] + [64] * 23, [257, 1, 90, 31] * 5):
+    # 10 requests (keys of a request shared by several CTAs), one, 16 (the most), and three with many tiles a warp
+    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 300, 700], [0], [5] * 9 + [129] + [64] * 6, [1500, 1, 2100]):
         reqs = [(c, 1) for c in ctxs]
         S = len(reqs)
         _, cache0, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=S)
@@ -91,7 +92,7 @@ def test_sizes_it_does_not_take_are_refused():
     from forge_b200 import kernels as k
     assert not k.DecodeLayers.supports(96, 256, 3, 1, 32)        # a width that is not a multiple of 64
     assert not k.DecodeLayers.supports(2048, 5632, 34, 2, 64)    # 17 query heads per kv head
-    assert not k.DecodeLayers.supports(2048, 5632, 32, 4, 64, tokens=65)
+    assert not k.DecodeLayers.supports(2048, 5632, 32, 4, 64, tokens=17)
 
 
 def test_grid_barrier_gives_up_after_its_time_limit():
@@ -112,3 +113,26 @@ def test_grid_barrier_gives_up_after_its_time_limit():
     assert s & 2 and s & (1 << 20)
     assert barrier.tolist()[:2] == [1, 1]            # one arrival, and the word that tells other CTAs to leave
     assert torch.ones(4, device=DEV).sum().item() == 4.0
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_whole_model_with_all_layers_in_one_kernel(page_size, tmp_path_factory):
+    """The engine with the persistent kernel switched on (it is off by default): a model of head size 64 whose last
+    tokens are decoded one by one, alone and four requests at a time, through the CUDA graph, against the plain
+    implementation at every position."""
+    import schedules
+    from helpers import TINY, TOL, make_model_dir, random_tokens
+    from plain.llama import PlainLlama
+    from test_engine_gpu import first_bad, run_schedule
+    from forge_b200.engine import ModelRunner
+    d = make_model_dir(tmp_path_factory, "C")
+    plain = PlainLlama(d)
+    reqs = {f"r{i}": random_tokens(n, TINY["C"]["vocab_size"], seed=60 + i) for i, n in enumerate([150, 40, 300, 77, 64])}
+    want = {rid: plain.logits(t).float() for rid, t in reqs.items()}
+    for steps in (schedules.last_one_by_one(reqs), schedules.mixed(reqs, max_live=4, decode_tail=20)):
+        runner = ModelRunner(d, dtype="bfloat16", page_size=page_size, cache_tokens=schedules.peak_tokens(reqs, steps, round_to=page_size),
+                             max_requests=4, fused_decode=True)
+        assert runner.fused_decode
+        got = run_schedule(runner, reqs, steps)
+        msg = first_bad(got, want, TOL["bfloat16"])
+        assert msg is None, msg
