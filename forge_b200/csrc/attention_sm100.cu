@@ -1,45 +1,56 @@
-// Paged causal grouped-query attention for prompt portions on the 5th-generation tensor cores (head size 64).
+// Paged causal grouped-query attention for prompt portions on the 5th-generation tensor cores (head sizes 64 and
+// 128; the library is built per head size, -DFORGE_ATT_HD).
 //
-// One CTA = one tile of 128 query rows of one (request, kv head); a row is a (token, head of the kv head's
-// group) pair, row r <-> token r / G, head r % G, so a tile is 128 / G tokens and the G heads share every
-// key/value tile.  Per tile of 64 keys:
-//   S = Q K^T      tcgen05.mma M=128 N=64 K=64, Q and K in shared memory (TMA, 128-byte swizzle), S in TMEM
+// One CTA = one tile of up to 128 query rows of one (request, kv head); a row is a (token, head of the kv head's
+// group) pair, row r <-> token r / G, head r % G, so a tile is 128 / G tokens (rounded down: with a group that
+// does not divide 128 the last rows of the tile stay empty) and the G heads share every key/value tile.  Per tile
+// of 64 keys (HD = head size):
+//   S = Q K^T      tcgen05.mma M=128 N=64 K=HD, Q and K in shared memory (TMA, 128-byte swizzle), S in TMEM
 //                  (two buffers: the scores of tile it + 2 are computed while the rows work on tile it)
 //   softmax        128 threads, one row each, hold the row's 64 scores in registers, online max/sum in fp32
 //                  (exp2 domain, packed fp32 arithmetic), write P as bf16 into shared memory in the MMA's
 //                  layout (two buffers); the output accumulator in TMEM is rescaled only when a row's
 //                  reference exponent has to move (a maximum that grew by more than 2^8)
-//   O += P V       tcgen05.mma M=128 N=64 K=64, P K-major, V MN-major (keys are rows of 128 bytes), O in TMEM
+//   O += P V       tcgen05.mma M=128 N=64 K=64 per 64 columns of the head, P K-major, V MN-major (keys are rows of
+//                  128 bytes), O in TMEM
 // Warps 0-3 run one thread each: warp 0 feeds keys and values page by page through the request's block table
 // (one TMA box per page and operand; key and value tiles have rings of three slots each, keys run ahead),
 // warp 1 issues P V, warp 2 issues Q K^T; warps 4-7 are the softmax rows.  The first warpgroup hands most of
-// its registers to the second (setmaxnreg).  Two such CTAs fit an SM (99 KB of shared memory, 256 TMEM
-// columns each).  Tiles are listed longest first and the kv heads of a tile are neighbouring CTAs, so the
+// its registers to the second (setmaxnreg).  With head size 64 two such CTAs fit an SM (99 KB of shared memory,
+// 256 TMEM columns each); with 128 one does (163 KB).  Tiles are listed longest first and the kv heads of a tile are neighbouring CTAs, so the
 // long tiles of all heads start in the first wave.
-//   s_j = (q . k_j) / sqrt(64) for keys max(0, p - window + 1) <= j <= p of the row's position p;
+//   s_j = (q . k_j) * scale for keys max(0, p - window + 1) <= j <= p of the row's position p;
 //   o = sum_j softmax(s)_j v_j        (formulas of src/operators/cuda/cuda_flash_attn.cu:154-248)
-// Needs 128 % G == 0, 64 % page_size == 0 and page_size >= 8; everything else is served by attention_mma.cu.
+// Needs G <= 128, 64 % page_size == 0 and page_size >= 8; everything else is served by attention_mma.cu.
 #include "common.cuh"
 #include "sm100.cuh"
+
+#ifndef FORGE_ATT_HD
+#define FORGE_ATT_HD 64
+#endif
 
 namespace {
 
 using namespace sm100;
 
-constexpr int HD = 64, BQ = 128, BKV = 64, UMMA_K = 16;
+constexpr int HD = FORGE_ATT_HD, BQ = 128, BKV = 64, UMMA_K = 16;
+static_assert(HD == 64 || HD == 128, "head size 64 or 128");
+constexpr int KB = HD / 64;                       // 64-wide blocks of the head: Q, K and V tiles are KB swizzled blocks
 constexpr int kThreads = 256;                     // warps 0-3: copies, P V, Q K^T, (idle); warps 4-7: the softmax rows
 constexpr int kQkWarp = 2;
-constexpr int kCtasPerSm = 2;
+constexpr int kCtasPerSm = 2;                     // what the register budget is made for (head size 128: one fits, by shared memory)
 constexpr int kLaunchRegs = 65536 / (kThreads * kCtasPerSm) / 8 * 8;     // what the compiler gives every thread at launch
 constexpr int kRegsFew = 64, kRegsMany = 192;      // registers per thread of the two warpgroups after they trade
 // setmaxnreg only moves registers inside the CTA's allocation: asking for more than it holds waits for ever
 static_assert(kRegsFew + kRegsMany <= 2 * kLaunchRegs, "the two warpgroups cannot hold more registers than the CTA was given");
-constexpr int kTileBytes = BQ * 128;              // Q or P: 128 rows of 128 bytes
-constexpr int kKVBytes = BKV * 128;               // K or V tile: 64 rows of 128 bytes
+constexpr int kTileBytes = BQ * 128;              // P, or one block of Q: 128 rows of 128 bytes
+constexpr int kQBytes = KB * kTileBytes;
+constexpr int kKVBlock = BKV * 128;               // one block of a K or V tile: 64 keys of 128 bytes
+constexpr int kKVBytes = KB * kKVBlock;
 constexpr int kStages = 3;                        // ring slots for key tiles, and as many for value tiles
 constexpr int kPageWindow = 256;                  // block-table entries staged in shared memory at a time
-constexpr int kSmemBytes = kTileBytes * 3 + 2 * kStages * kKVBytes + 1024 + 1024 + kPageWindow * 4;
-constexpr int kTmemCols = 256;                    // S of even / odd tiles: columns 0..63 / 64..127, O: 128..191
+constexpr int kSmemBytes = kQBytes + 2 * kTileBytes + 2 * kStages * kKVBytes + 1024 + 1024 + kPageWindow * 4;
+constexpr int kTmemCols = 256;                    // S of even / odd tiles: columns 0..63 / 64..127, O: 128..128+HD-1
 
 struct AttnTcParams {
     __nv_bfloat16* out;           // [T, NH*HD]
@@ -99,10 +110,10 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                              const AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_s = smem;                                            // [128][64] bf16, K-major, swizzled
-    uint8_t* p_s = smem + kTileBytes;                               // [2][128][64 keys] bf16, K-major, swizzled
-    uint8_t* k_s = smem + 3 * kTileBytes;                           // [kStages][64 keys][64]
-    uint8_t* v_s = k_s + kStages * kKVBytes;                        // [kStages][64 keys][64]
+    uint8_t* q_s = smem;                                            // [KB][128][64] bf16, K-major, swizzled
+    uint8_t* p_s = smem + kQBytes;                                  // [2][128][64 keys] bf16, K-major, swizzled
+    uint8_t* k_s = p_s + 2 * kTileBytes;                            // [kStages][KB][64 keys][64]
+    uint8_t* v_s = k_s + kStages * kKVBytes;                        // [kStages][KB][64 keys][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kStages * kKVBytes);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;                  // [kStages]
@@ -145,6 +156,8 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     // key/value stages start as zeros: pages that are skipped (beyond the request, or released by the
     // window) leave their rows as they are, and those rows must hold finite numbers (their weights are 0)
     for (int i = threadIdx.x; i < 2 * kStages * kKVBytes / 16; i += kThreads) reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0, 0, 0, 0);
+    // so do the rows of Q that a tile of fewer than 128 rows leaves unwritten
+    for (int i = threadIdx.x; i < kQBytes / 16; i += kThreads) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     if (warp == 1) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -159,7 +172,8 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 
     const int s_req = p.tile_req[tile], row0 = p.tile_row0[tile];
     const int qs0 = p.q_start[s_req], qlen = p.q_start[s_req + 1] - qs0, ctx = p.ctx_before[s_req];
-    const int rows_here = min(BQ, qlen * G - row0);
+    const int tile_rows = (BQ / G) * G;                             // rows of a full tile: whole tokens only
+    const int rows_here = min(tile_rows, qlen * G - row0);
     const int pos_lo = ctx + row0 / G, pos_hi = ctx + (row0 + rows_here - 1) / G;
     const int kv_hi = pos_hi + 1;
     const int kv_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
@@ -179,8 +193,8 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         const int iters_per_win = kPageWindow / ppt;
         const uint32_t page_bytes = p.page_size * 128;
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, kTileBytes);
-            tma_load_3d(q_s, &tmap_q, q_full, 0, kvh * G, qs0 + row0 / G);
+            mbar_arrive_expect_tx(q_full, KB * tile_rows * 128);
+            for (int kb = 0; kb < KB; ++kb) tma_load_3d(q_s + kb * kTileBytes, &tmap_q, q_full, kb * 64, kvh * G, qs0 + row0 / G);
         }
         bool ok = true;
         int st = 0, ph = 0;                                              // ring slot and its phase
@@ -203,14 +217,18 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                     }
                     // keys first: Q K^T of a tile runs two tiles ahead of its P V
                     if (!(ok = mbar_wait<true>(&k_empty[st], ph ^ 1, abort, p.status, 1))) break;
-                    mbar_arrive_expect_tx(&k_full[st], n_valid * page_bytes);
-                    for (int i = 0; i < ppt; ++i)
-                        if (rows[i] >= 0) tma_load_2d(k_s + st * kKVBytes + i * page_bytes, &tmap_kv, &k_full[st], 0, rows[i]);
-                    if (!(ok = mbar_wait<true>(&v_empty[st], ph ^ 1, abort, p.status, 9))) break;
-                    mbar_arrive_expect_tx(&v_full[st], n_valid * page_bytes);
+                    mbar_arrive_expect_tx(&k_full[st], KB * n_valid * page_bytes);
                     for (int i = 0; i < ppt; ++i)
                         if (rows[i] >= 0)
-                            tma_load_2d(v_s + st * kKVBytes + i * page_bytes, &tmap_kv, &v_full[st], 0, rows[i] + p.NKV * p.page_size);
+                            for (int kb = 0; kb < KB; ++kb)
+                                tma_load_2d(k_s + st * kKVBytes + kb * kKVBlock + i * page_bytes, &tmap_kv, &k_full[st], kb * 64, rows[i]);
+                    if (!(ok = mbar_wait<true>(&v_empty[st], ph ^ 1, abort, p.status, 9))) break;
+                    mbar_arrive_expect_tx(&v_full[st], KB * n_valid * page_bytes);
+                    for (int i = 0; i < ppt; ++i)
+                        if (rows[i] >= 0)
+                            for (int kb = 0; kb < KB; ++kb)
+                                tma_load_2d(v_s + st * kKVBytes + kb * kKVBlock + i * page_bytes, &tmap_kv, &v_full[st], kb * 64,
+                                            rows[i] + p.NKV * p.page_size);
                     if (++st == kStages) { st = 0; ph ^= 1; }
                 }
             }
@@ -219,7 +237,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     } else if (warp == 1) {
         // ------------------------------------------------------------------ P V issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_pv = umma_idesc_bf16_f32_bmn(BQ, HD);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16_f32_bmn(BQ, 64);        // one product per 64 columns of the head
             const uint32_t p_addr = smem_u32(p_s), v_addr = smem_u32(v_s);
             bool ok = true;
             int vst = 0, vph = 0;
@@ -230,9 +248,11 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                 tc_fence_after_sync();
                 const uint32_t pa = p_addr + b * kTileBytes, va = v_addr + vst * kKVBytes;
 #pragma unroll
-                for (int k = 0; k < BKV / UMMA_K; ++k)
-                    umma_bf16(tmem_base + 2 * BKV, umma_desc_k_sw128(pa + k * 32), umma_desc_mn_sw128(va + k * 2048, 0),
-                              idesc_pv, (it | k) != 0);
+                for (int nb = 0; nb < KB; ++nb)
+#pragma unroll
+                    for (int k = 0; k < BKV / UMMA_K; ++k)
+                        umma_bf16(tmem_base + 2 * BKV + nb * 64, umma_desc_k_sw128(pa + k * 32),
+                                  umma_desc_mn_sw128(va + nb * kKVBlock + k * 2048, 0), idesc_pv, (it | k) != 0);
                 umma_commit(&o_done[b]);
                 umma_commit(&v_empty[vst]);
                 if (++vst == kStages) { vst = 0; vph ^= 1; }
@@ -255,8 +275,11 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                 tc_fence_after_sync();
                 const uint32_t ka = k_addr + kst * kKVBytes;
 #pragma unroll
-                for (int k = 0; k < HD / UMMA_K; ++k)
-                    umma_bf16(tmem_base + b * BKV, umma_desc_k_sw128(q_addr + k * 32), umma_desc_k_sw128(ka + k * 32), idesc_qk, k != 0);
+                for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                    for (int k = 0; k < 64 / UMMA_K; ++k)
+                        umma_bf16(tmem_base + b * BKV, umma_desc_k_sw128(q_addr + kb * kTileBytes + k * 32),
+                                  umma_desc_k_sw128(ka + kb * kKVBlock + k * 32), idesc_qk, (kb | k) != 0);
                 umma_commit(&s_full[b]);
                 umma_commit(&k_empty[kst]);
                 if (++kst == kStages) { kst = 0; kph ^= 1; }
@@ -401,16 +424,16 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 
 }  // namespace
 
-// q [T, NH*64] bf16, kv cache [pages, 2, NKV, page_size, 64] bf16, out [T, NH*64] bf16.  tile_req / tile_row0
-// list tiles of 128 query rows (rows = tokens * G); q_start / ctx_before as for forge_paged_attention_mma.
+// q [T, NH*HD] bf16, kv cache [pages, 2, NKV, page_size, HD] bf16, out [T, NH*HD] bf16.  tile_req / tile_row0
+// list tiles of (128 / G) * G query rows (rows = tokens * G); q_start / ctx_before as for forge_paged_attention_mma.
 extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* out, const int32_t* block_table,
                                            const int32_t* tile_req, const int32_t* tile_row0, const int32_t* q_start,
                                            const int32_t* ctx_before, int* status, int num_tiles, int T, int num_pages,
                                            int NH, int NKV, int head_dim, int page_size, int max_pages, int window,
                                            float scale, cudaStream_t stream) {
-    if (head_dim != HD) return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: head_dim %d (only 64)", head_dim);
-    if (NH <= 0 || NKV <= 0 || NH % NKV != 0 || BQ % (NH / NKV) != 0 || NH / NKV > BQ)
-        return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: group size %d/%d must divide 128", NH, NKV);
+    if (head_dim != HD) return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: this library was built for head_dim %d, got %d", HD, head_dim);
+    if (NH <= 0 || NKV <= 0 || NH % NKV != 0 || NH / NKV > BQ)
+        return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: %d query heads per kv head (at most 128)", NKV > 0 ? NH / NKV : 0);
     if (page_size < 8 || BKV % page_size != 0)
         return forge::fail(FORGE_ERR_UNSUPPORTED, "paged_attention_sm100: page size %d must be 8, 16, 32 or 64", page_size);
     if (!(scale > 0.f)) return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: scale %g must be positive", (double)scale);

@@ -333,18 +333,20 @@ def attention_plan(batch, group, device, only_below=None):
 
 
 def attention_plan_tc(batch, group, device):
-    """Tiles of 128 rows for the requests that bring at least TC_MIN_ROWS rows, heaviest (most keys) first."""
+    """Tiles of (128 // group) whole tokens, that is up to 128 rows, for the requests that bring at least TC_MIN_ROWS
+    rows, heaviest (most keys) first."""
     key = ("tc", group)
     plan = batch.attention_plan.get(key)
     if plan is not None:
         return plan
     tiles, qs = [], batch.host_q_start
+    tile_rows = (TC_ROWS // group) * group
     for s in range(batch.num_requests):
         rows = (qs[s + 1] - qs[s]) * group
         if rows < TC_MIN_ROWS:
             continue
-        for r0 in range(0, rows, TC_ROWS):
-            tiles.append((batch.host_context_before[s] + min(rows, r0 + TC_ROWS) // group, s, r0))
+        for r0 in range(0, rows, tile_rows):
+            tiles.append((batch.host_context_before[s] + min(rows, r0 + tile_rows) // group, s, r0))
     tiles.sort(reverse=True)
     plan = {"tile_req": torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=device),
             "tile_row0": torch.tensor([t[2] for t in tiles], dtype=torch.int32, device=device), "num_tiles": len(tiles)}
@@ -353,14 +355,15 @@ def attention_plan_tc(batch, group, device):
 
 
 def attention_sm100_supports(head_dim, group, page_size):
-    return _TENSOR_CORE_ATTENTION and head_dim == 64 and TC_ROWS % group == 0 and page_size in (8, 16, 32, 64)
+    """Head sizes 64 and 128, any group of up to 128 query heads per kv head, pages of 8 to 64 tokens."""
+    return _TENSOR_CORE_ATTENTION and head_dim in (64, 128) and 1 <= group <= TC_ROWS and page_size in (8, 16, 32, 64)
 
 
 def paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=0,
                           scale=None, out=None):
     """tcgen05/TMEM attention for the requests of the step that bring many rows (prompt portions).  Writes
     only those requests' rows of ``out``.  Returns (out, number of tiles run)."""
-    lib = library("attention_sm100")
+    lib = library("attention_sm100", {"FORGE_ATT_HD": head_dim})
     plan = attention_plan_tc(batch, n_heads // n_kv_heads, q.device)
     if out is None:
         out = torch.empty_like(q)

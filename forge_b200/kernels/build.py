@@ -26,7 +26,7 @@ LIBRARIES = {
     "gemm_sm100": ["gemm_sm100.cu"],
     # bf16 tensor-core paged attention (mma.sync) for any head size, prompt portions and decode
     "attention_mma": ["attention_mma.cu"],
-    # bf16 tcgen05/TMEM paged attention for prompt portions, head size 64
+    # bf16 tcgen05/TMEM paged attention for prompt portions, head sizes 64 and 128 (built per head size)
     "attention_sm100": ["attention_sm100.cu"],
     # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)
     "decode_layers": ["decode_layers.cu"],
@@ -138,7 +138,7 @@ COMMON_HEAD_DIMS = (64, 128)
 def build_all(force=False):
     out = {}
     for name in LIBRARIES:
-        if name in ("attention_mma", "decode_layers"):
+        if name in ("attention_mma", "attention_sm100", "decode_layers"):
             for hd in COMMON_HEAD_DIMS:
                 out[f"{name}_hd{hd}"] = build_library(name, force=force, defines={"FORGE_ATT_HD": hd})
         else:

@@ -1,5 +1,6 @@
-"""The tcgen05/TMEM attention kernel for prompt portions (head size 64) against a plain fp64 restatement,
-alone and through the dispatcher that sends requests with few rows to the mma.sync kernel."""
+"""The tcgen05/TMEM attention kernel for prompt portions (head sizes 64 and 128, groups that do and do not divide
+the tile's 128 rows) against a plain fp64 restatement, alone and through the dispatcher that sends requests with few
+rows to the mma.sync kernel."""
 import pytest
 import torch
 
@@ -8,7 +9,12 @@ from test_attention_mma_gpu import make_case
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(32, 4, 64, 16), (8, 8, 64, 16), (16, 1, 64, 8), (4, 2, 64, 64), (6, 3, 64, 32)]
+SHAPES = [(32, 4, 64, 16), (8, 8, 64, 16), (16, 1, 64, 8), (4, 2, 64, 64), (6, 3, 64, 32),
+          (32, 8, 128, 16),      # head size 128, group of 4 (the Llama-3-8B shape)
+          (28, 4, 128, 64),      # head size 128, group of 7: a tile holds 18 tokens = 126 rows (the Qwen2.5-7B shape)
+          (6, 2, 64, 16),        # group of 3: 42 tokens = 126 rows
+          (5, 1, 128, 8),        # group of 5: 25 tokens = 125 rows
+          (40, 2, 64, 16)]       # group of 20: 6 tokens = 120 rows
 PORTIONS = [(0, 100), (130, 17), (0, 300), (63, 65), (500, 16), (64, 64)]
 
 
@@ -37,7 +43,14 @@ def test_prompt_portions(nh, nkv, hd, ps, window):
     assert len(bad) == 0, f"first wrong token {int(big[bad[0]])} (request {int(tok_req[big[bad[0]]])}, position {int(positions[big[bad[0]]])})"
 
 
-@pytest.mark.parametrize("nh,nkv,hd,ps", SHAPES[:3])
+def test_shapes_it_takes():
+    from forge_b200 import kernels as k
+    for hd, g in ((128, 4), (128, 7), (64, 3), (64, 8), (128, 128)):
+        assert k.attention_sm100_supports(hd, g, 16), (hd, g)
+    assert not k.attention_sm100_supports(96, 4, 16) and not k.attention_sm100_supports(64, 4, 128)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", SHAPES[:3] + SHAPES[5:8])
 def test_dispatcher_covers_every_token(nh, nkv, hd, ps):
     """Portions of prompts beside decode tokens: big requests by tcgen05, small ones by mma.sync, no row missed."""
     from forge_b200 import kernels as k
@@ -59,6 +72,14 @@ def test_long_causal_prompt_heaviest_tiles_first():
     got, n = k.paged_attention_sm100(q, cache, group, batch, nh, nkv, hd, ps)
     k.check_kernel_status()
     assert n == -(-1100 * 8 // 128)
+    # the same with head size 128 and 7 query heads per kv head
+    nh, nkv, hd, ps = 14, 2, 128, 32
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, [(0, 700)], seed=8)
+    ref = R.paged_attention_ref(q[-40:], cache, group.block_table, tok_req[-40:], positions[-40:], nh, nkv, hd, ps)
+    got, n = k.paged_attention_sm100(q, cache, group, batch, nh, nkv, hd, ps)
+    k.check_kernel_status()
+    assert n == -(-700 // 18)
+    assert (got.float()[-40:] - ref).abs().max() <= 1e-2 * ref.abs().max()
     assert (got.float()[-40:] - ref).abs().max() <= 1e-2 * ref.abs().max()
 
 
