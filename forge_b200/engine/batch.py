@@ -119,7 +119,9 @@ def build_step_batch(entries, manager, device, max_pages, status=None):
             table[s, :len(t)] = t
         group_spans[g] = (off, off + T)
         off += T + S * max_pages
-    dev = torch.from_numpy(buf).to(device)
+    from .. import kernels
+    dev = kernels.new_tensor((total,), torch.int32, device)      # from the step's workspace, if one is open
+    dev.copy_(torch.from_numpy(buf))
 
     def view(i):
         o, n = spans[i]

@@ -128,18 +128,26 @@ class Model:
         return True
 
     # ---------------------------------------------------------------------------------- forward
-    def forward(self, batch, position_caches):
+    def forward(self, batch, position_caches, workspace=None):
         """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run.
-        Returns fp32 logits [R,V] at ``batch.logits_rows`` (None if no row is wanted)."""
+        Returns fp32 logits [R,V] at ``batch.logits_rows`` (None if no row is wanted).  ``workspace``: the open
+        StepWorkspace that the kernels' outputs are cut from; a layer's share of it is given back after the layer."""
         residual = self.embedding.forward(batch.token_ids, status=batch.status)
         if self._fused_decode_applies(batch):
             fused, group = self._fused
             g = batch.groups[group]
             fused.run(residual, g.block_table, batch.positions, g.slot_mapping)
         else:
+            ws = workspace
             for pos, i in enumerate(self.plan.schedule):
+                m = ws.mark() if ws is not None else 0
                 self.blocks[i].forward(residual, batch, position_caches[pos])
+                if ws is not None:
+                    ws.release(m)              # a layer's intermediates are dead: the residual stream carries on
         if batch.num_logits == 0:
             return None
         x = self.final_norm.forward(residual, rows=batch.logits_rows)
-        return self.lm_head.forward(x)
+        if workspace is None:
+            return self.lm_head.forward(x)
+        with workspace.paused():               # the logits are the caller's to keep
+            return self.lm_head.forward(x)

@@ -98,6 +98,11 @@ class ModelRunner:
         want = fused_decode if fused_decode is not None else os.environ.get("FORGE_FUSED_DECODE", "0") == "1"
         self.fused_decode = bool(want) and self.model.enable_fused_decode(self.storage.layers, self.max_requests)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # Outputs of a step's kernels are views into one buffer that is as large as the largest step so far needed
+        # (one layer's intermediates at max_tokens_per_step, if that is given, plus the step's integers): after the
+        # first step of the largest size no step asks the allocator for anything but the logits it hands out.
+        from .. import kernels
+        self.workspace = kernels.StepWorkspace(self.device)
         # decode steps replay a captured graph only if every part of the model says that it may be captured
         self.graph_safe = self.model.graph_safe()
         self.cuda_graphs = bool(cuda_graphs) and self.graph_safe
@@ -152,9 +157,10 @@ class ModelRunner:
         if self.cuda_graphs and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             # the graph's own logits buffer is rewritten by the next replay: hand out a copy
             return self.decode_step(entries)[0].clone()
-        batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
-        self.storage.zero_state_slots(self.manager.take_fresh_slots())
-        logits = self.model.forward(batch, self.storage.layers)
+        with self.workspace.step() as ws:
+            batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
+            self.storage.zero_state_slots(self.manager.take_fresh_slots())
+            logits = self.model.forward(batch, self.storage.layers, workspace=ws)
         for e in entries:
             self.manager.release_out_of_window(e.req_id)
         return logits

@@ -130,6 +130,115 @@ def _opt(t, name, dtype=None):
     return None if t is None else _need(t, name, dtype)
 
 
+# ----------------------------------------------------------------------------------- step workspace
+
+class StepWorkspace:
+    """One device buffer that the outputs of a step's kernels are cut from, instead of one trip to the allocator per
+    kernel output (the reference allocates device memory for every operator output, src/core/tensor.cpp:86-107).
+
+    While a step is open (``with ws.step():``) every tensor that the functions of this module would allocate is a
+    view into the buffer, handed out front to back; ``mark`` / ``release`` give a layer's intermediates back when the
+    layer is done, so the buffer holds one layer's worth plus what lives for the whole step.  The buffer is as large
+    as the largest step so far needed: a step that outgrows it gets ordinary allocations for the overflow, and the
+    buffer is enlarged after that step.  ``reserve(nbytes)`` sizes it ahead of time.  Tensors cut from it are dead
+    when the next step opens; what a caller keeps (logits) must not come from here (``paused``)."""
+    ALIGN = 256
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.buf = None
+        self.capacity = 0
+        self.offset = 0          # next free byte (may run past capacity: then it only measures)
+        self.high = 0
+        self.open = False
+        self.hold = 0            # > 0: paused
+        self.allocations = 0     # outputs that had to come from the allocator while a step was open
+
+    def reserve(self, nbytes):
+        nbytes = -(-int(nbytes) // self.ALIGN) * self.ALIGN
+        if nbytes > self.capacity:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self.capacity = nbytes
+
+    def step(self):
+        return _OpenStep(self)
+
+    def paused(self):
+        return _Paused(self)
+
+    def mark(self):
+        return self.offset
+
+    def release(self, mark):
+        self.offset = mark
+
+    def take(self, shape, dtype):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = self.offset
+        self.offset = start + -(-nbytes // self.ALIGN) * self.ALIGN
+        self.high = max(self.high, self.offset)
+        if self.offset > self.capacity:
+            self.allocations += 1
+            return None
+        return self.buf[start:start + nbytes].view(dtype).view(tuple(int(d) for d in shape))
+
+
+class _OpenStep:
+    def __init__(self, ws):
+        self.ws = ws
+
+    def __enter__(self):
+        ws = self.ws
+        ws.offset, ws.high, ws.open = 0, 0, True
+        _active_workspace[0] = ws
+        return ws
+
+    def __exit__(self, *exc):
+        ws = self.ws
+        ws.open = False
+        _active_workspace[0] = None
+        if ws.high > ws.capacity:          # the next step of this size fits
+            ws.reserve(ws.high + ws.high // 8)
+        return False
+
+
+class _Paused:
+    def __init__(self, ws):
+        self.ws = ws
+
+    def __enter__(self):
+        self.ws.hold += 1
+
+    def __exit__(self, *exc):
+        self.ws.hold -= 1
+        return False
+
+
+_active_workspace = [None]
+
+
+def new_tensor(shape, dtype, device):
+    """An uninitialised tensor for a kernel's output: from the open step's workspace if there is one (and it is
+    not paused, and lives on this device), else from the allocator."""
+    ws = _active_workspace[0]
+    if ws is not None and ws.hold == 0 and torch.device(device) == ws.device and not torch.cuda.is_current_stream_capturing():
+        t = ws.take(shape, dtype)
+        if t is not None:
+            return t
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
+def new_ints(values, device):
+    """int32 device tensor of a host list (a step's tile lists and the like), its memory from the workspace."""
+    host = torch.tensor(values, dtype=torch.int32)
+    out = new_tensor(host.shape, torch.int32, device)
+    out.copy_(host)
+    return out
+
+
 # ---------------------------------------------------------------------------------------------- core
 
 def embedding(ids, table, out=None, status=None):
@@ -137,7 +246,7 @@ def embedding(ids, table, out=None, status=None):
     lib = library("core")
     T, (V, H) = ids.numel(), table.shape
     if out is None:
-        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        out = new_tensor((T, H), torch.float32, table.device)
     _check(lib, lib.forge_embedding(_need(ids, "ids", torch.int32), _need(table, "table", ndim=2),
                                     dtype_code(table.dtype), _need(out, "out", torch.float32), T, H, V,
                                     _opt(status, "status", torch.int32), _stream()), "embedding")
@@ -152,7 +261,7 @@ def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
     if weight.numel() != H:
         raise KernelError(f"rmsnorm: weight has {weight.numel()} elements, rows have {H}")
     if out is None:
-        out = torch.empty((R, H), dtype=out_dtype, device=x.device)
+        out = new_tensor((R, H), out_dtype, x.device)
     _check(lib, lib.forge_rmsnorm(_need(x, "x", torch.float32, 2), _need(weight, "weight", torch.float32),
                                   _need(out, "out", out_dtype), dtype_code(out_dtype),
                                   _opt(rows, "rows", torch.int32), R, H, float(eps), _stream()), "rmsnorm")
@@ -164,7 +273,7 @@ def rope_table(positions, head_dim, theta):
     per step and shared by every head of every layer with the same head size and base."""
     lib = library("core")
     T = positions.numel()
-    table = torch.empty((T, head_dim // 2, 2), dtype=torch.float32, device=positions.device)
+    table = new_tensor((T, head_dim // 2, 2), torch.float32, positions.device)
     _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
                                      float(theta), _stream()), "rope_table")
     return table
@@ -180,7 +289,7 @@ def rope_kv_write(qkv, positions, slot_mapping, kv_cache, n_heads, n_kv_heads, h
     if qkv.shape[1] != width:
         raise KernelError(f"rope_kv_write: qkv has width {qkv.shape[1]}, expected {width}")
     if q_out is None:
-        q_out = torch.empty((T, n_heads * head_dim), dtype=act_dtype, device=qkv.device)
+        q_out = new_tensor((T, n_heads * head_dim), act_dtype, qkv.device)
     if kv_cache is not None and kv_cache.dtype != act_dtype:
         raise KernelError("rope_kv_write: cache and activation dtypes differ")
     if kv_cache is None:
@@ -199,7 +308,7 @@ def silu_mul_interleaved(gu, out_dtype, out=None):
     lib = library("core")
     T, two_i = gu.shape
     if out is None:
-        out = torch.empty((T, two_i // 2), dtype=out_dtype, device=gu.device)
+        out = new_tensor((T, two_i // 2), out_dtype, gu.device)
     _check(lib, lib.forge_silu_mul_interleaved(_need(gu, "gu", torch.float32, 2), _need(out, "out", out_dtype),
                                                dtype_code(out_dtype), T, two_i // 2, _stream()), "silu_mul_interleaved")
     return out
@@ -214,7 +323,7 @@ def gemm_simt(a, w, bias=None, out=None, accumulate=False):
     if out is None:
         if accumulate:
             raise KernelError("gemm_simt: accumulate needs an output tensor")
-        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        out = new_tensor((M, N), torch.float32, a.device)
     elif tuple(out.shape) != (M, N):
         raise KernelError(f"gemm_simt: out has shape {tuple(out.shape)}, expected {(M, N)}")
     _check(lib, lib.forge_gemm_simt(_need(a, "a", ndim=2), _need(w, "w", ndim=2), _opt(bias, "bias", torch.float32),
@@ -230,7 +339,7 @@ def paged_attention_simt(q, kv_cache, block_table, tok_req, positions, n_heads, 
     lib = library("core")
     T = q.shape[0]
     if out is None:
-        out = torch.empty_like(q)
+        out = new_tensor(q.shape, q.dtype, q.device)
     if kv_cache.dtype != q.dtype:
         raise KernelError("paged_attention_simt: q and cache dtypes differ")
     scale = head_dim ** -0.5 if scale is None else scale
@@ -247,7 +356,7 @@ def argmax(logits, out=None):
     lib = library("core")
     R, V = logits.shape
     if out is None:
-        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        out = new_tensor((R,), torch.int32, logits.device)
     _check(lib, lib.forge_argmax(_need(logits, "logits", torch.float32, 2), _need(out, "out", torch.int32), R, V,
                                  _stream()), "argmax")
     return out
@@ -268,7 +377,7 @@ def sample(logits, temperature, top_k, top_p, u, out=None):
     lib = library("core")
     R, V = logits.shape
     if out is None:
-        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        out = new_tensor((R,), torch.int32, logits.device)
     _check(lib, lib.forge_sample(_need(logits, "logits", torch.float32, 2), _need(temperature, "temperature", torch.float32),
                                  _need(top_k, "top_k", torch.int32), _need(top_p, "top_p", torch.float32),
                                  _need(u, "u", torch.float32), _need(out, "out", torch.int32), R, V, _stream()), "sample")
@@ -325,8 +434,7 @@ def attention_plan(batch, group, device, only_below=None):
     max_ctx = getattr(batch, "max_context", None)
     if max_ctx is None:
         max_ctx = max(c + qs[s + 1] - qs[s] for s, c in enumerate(batch.host_context_before))
-    plan = {"tile_req": torch.tensor(tile_req, dtype=torch.int32, device=device),
-            "tile_row0": torch.tensor(tile_row0, dtype=torch.int32, device=device),
+    plan = {"tile_req": new_ints(tile_req, device), "tile_row0": new_ints(tile_row0, device),
             "num_tiles": len(tile_req), "max_rows": max_rows, "max_kv_tiles": -(-max_ctx // KV_TILE), "scratch": {}}
     batch.attention_plan[key] = plan
     return plan
@@ -348,8 +456,8 @@ def attention_plan_tc(batch, group, device):
         for r0 in range(0, rows, tile_rows):
             tiles.append((batch.host_context_before[s] + min(rows, r0 + tile_rows) // group, s, r0))
     tiles.sort(reverse=True)
-    plan = {"tile_req": torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=device),
-            "tile_row0": torch.tensor([t[2] for t in tiles], dtype=torch.int32, device=device), "num_tiles": len(tiles)}
+    plan = {"tile_req": new_ints([t[1] for t in tiles], device), "tile_row0": new_ints([t[2] for t in tiles], device),
+            "num_tiles": len(tiles)}
     batch.attention_plan[key] = plan
     return plan
 
@@ -366,7 +474,7 @@ def paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, 
     lib = library("attention_sm100", {"FORGE_ATT_HD": head_dim})
     plan = attention_plan_tc(batch, n_heads // n_kv_heads, q.device)
     if out is None:
-        out = torch.empty_like(q)
+        out = new_tensor(q.shape, q.dtype, q.device)
     if plan["num_tiles"] == 0:
         return out, 0
     scale = head_dim ** -0.5 if scale is None else scale
@@ -387,7 +495,7 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
     plan = attention_plan(batch, n_heads // n_kv_heads, q.device, only_below)
     if out is None:
-        out = torch.empty_like(q)
+        out = new_tensor(q.shape, q.dtype, q.device)
     if plan["num_tiles"] == 0:
         return out
     if num_splits is None:
@@ -403,11 +511,10 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
         sk = (num_splits, head_dim, pr)
         if sk not in plan["scratch"]:
             n = plan["num_tiles"] * n_kv_heads * num_splits * pr
-            plan["scratch"][sk] = (torch.empty(n * head_dim, dtype=torch.float32, device=q.device),
-                                   torch.empty(n * 2, dtype=torch.float32, device=q.device))
+            plan["scratch"][sk] = (new_tensor((n * head_dim,), torch.float32, q.device), new_tensor((n * 2,), torch.float32, q.device))
         part_o, part_ml = plan["scratch"][sk]
     if out is None:
-        out = torch.empty_like(q)
+        out = new_tensor(q.shape, q.dtype, q.device)
     scale = head_dim ** -0.5 if scale is None else scale
     _check(lib, lib.forge_paged_attention_mma(
         _need(q, "q", torch.bfloat16, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
@@ -442,7 +549,7 @@ def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, 
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
     S = qkv.shape[0]
     if out is None:
-        out = torch.empty((S, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+        out = new_tensor((S, n_heads * head_dim), torch.bfloat16, qkv.device)
     scale = head_dim ** -0.5 if scale is None else scale
     _check(lib, lib.forge_decode_attention_fused(
         _need(qkv, "qkv", torch.float32, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
@@ -562,14 +669,14 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
         if accumulate_into is not None:
             out, code = accumulate_into, EPILOGUES["accumulate"]
         else:
-            out = torch.empty((M, N), dtype=torch.float32, device=x.device) if out is None else out
+            out = new_tensor((M, N), torch.float32, x.device) if out is None else out
             code = EPILOGUES["none"]
         want_shape, want_dtype = (M, N), torch.float32
     elif epilogue == "cast":
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if out is None else out
+        out = new_tensor((M, N), torch.bfloat16, x.device) if out is None else out
         code, want_shape, want_dtype = EPILOGUES["cast"], (M, N), torch.bfloat16
     elif epilogue == "swiglu":
-        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device) if out is None else out
+        out = new_tensor((M, N // 2), torch.bfloat16, x.device) if out is None else out
         code, want_shape, want_dtype = EPILOGUES["swiglu"], (M, N // 2), torch.bfloat16
     else:
         raise KernelError(f"gemm_sm100: unknown epilogue {epilogue!r}")

@@ -203,3 +203,33 @@ def test_trace_run_program(tiny, dtype, tmp_path):
             assert max_rel_err(arr[o:o + n], want[rid][p:p + n]) <= TOL[dtype], (s, rid, p)
             o += n
         assert o == arr.shape[0]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_steps_do_not_go_through_the_allocator(tiny, dtype):
+    """The outputs of a step's kernels are views into the runner's workspace: after a first step of some size, a
+    step of that size asks the allocator for the logits it hands out and for nothing else, and a step beyond
+    max_tokens_per_step is refused before anything is touched."""
+    from forge_b200.engine import ModelRunner, StepEntry, StepError
+    name, d, plain, reqs, want = tiny
+    runner = ModelRunner(d, dtype=dtype, page_size=16, cache_tokens=512, max_requests=4, max_tokens_per_step=96)
+    toks = reqs["r0"][:64]
+    got = []
+    for rep in range(3):
+        runner.admit("a"), runner.admit("b")
+        torch.cuda.synchronize()
+        before, misses = torch.cuda.memory_stats()["allocation.all.allocated"], runner.workspace.allocations
+        lg = runner.step([StepEntry("a", toks[:40], [39]), StepEntry("b", toks[:24], [0, 23])])
+        torch.cuda.synchronize()
+        if rep > 0:
+            assert runner.workspace.allocations == misses, "a kernel output did not fit the workspace"
+            assert torch.cuda.memory_stats()["allocation.all.allocated"] - before <= 1, "more than the logits was allocated"
+        got.append(lg.cpu())
+        runner.release("a"), runner.release("b")
+    assert torch.equal(got[0], got[1]) and torch.equal(got[1], got[2])
+    assert max_rel_err(got[2][0:1], want["r0"][39:40]) <= TOL[dtype]
+    assert runner.workspace.capacity > 0 and runner.workspace.high <= runner.workspace.capacity
+    runner.admit("c")
+    with pytest.raises(StepError, match="96"):
+        runner.step([StepEntry("c", toks + toks[:33], [])])
+    assert runner.manager.num_tokens("c") == 0
