@@ -137,8 +137,10 @@ class StepWorkspace:
     kernel output (the reference allocates device memory for every operator output, src/core/tensor.cpp:86-107).
 
     While a step is open (``with ws.step():``) every tensor that the functions of this module would allocate is a
-    view into the buffer, handed out front to back; ``mark`` / ``release`` give a layer's intermediates back when the
-    layer is done, so the buffer holds one layer's worth plus what lives for the whole step.  The buffer is as large
+    view into the buffer.  What lives for one layer is handed out front to back, and ``mark`` / ``release`` give a
+    layer's intermediates back when the layer is done; what lives for the whole step (a step's tile lists, its table
+    of rotary angles: made inside the first layer that needs them, used by all) is handed out from the back and
+    stays until the step closes.  So the buffer holds one layer's worth plus the step's own.  The buffer is as large
     as the largest step so far needed: a step that outgrows it gets ordinary allocations for the overflow, and the
     buffer is enlarged after that step.  ``reserve(nbytes)`` sizes it ahead of time.  Tensors cut from it are dead
     when the next step opens; what a caller keeps (logits) must not come from here (``paused``)."""
@@ -148,7 +150,8 @@ class StepWorkspace:
         self.device = torch.device(device)
         self.buf = None
         self.capacity = 0
-        self.offset = 0          # next free byte (may run past capacity: then it only measures)
+        self.offset = 0          # next free byte at the front (may run past capacity: then it only measures)
+        self.back = 0            # bytes handed out from the back
         self.high = 0
         self.open = False
         self.hold = 0            # > 0: paused
@@ -172,15 +175,20 @@ class StepWorkspace:
     def release(self, mark):
         self.offset = mark
 
-    def take(self, shape, dtype):
+    def take(self, shape, dtype, whole_step=False):
         n = 1
         for d in shape:
             n *= int(d)
         nbytes = n * torch.empty((), dtype=dtype).element_size()
-        start = self.offset
-        self.offset = start + -(-nbytes // self.ALIGN) * self.ALIGN
-        self.high = max(self.high, self.offset)
-        if self.offset > self.capacity:
+        padded = -(-nbytes // self.ALIGN) * self.ALIGN
+        if whole_step:
+            self.back += padded
+            start = self.capacity - self.back
+        else:
+            start = self.offset
+            self.offset += padded
+        self.high = max(self.high, self.offset + self.back)
+        if self.offset + self.back > self.capacity:
             self.allocations += 1
             return None
         return self.buf[start:start + nbytes].view(dtype).view(tuple(int(d) for d in shape))
@@ -192,7 +200,7 @@ class _OpenStep:
 
     def __enter__(self):
         ws = self.ws
-        ws.offset, ws.high, ws.open = 0, 0, True
+        ws.offset, ws.back, ws.high, ws.open = 0, 0, 0, True
         _active_workspace[0] = ws
         return ws
 
@@ -220,21 +228,22 @@ class _Paused:
 _active_workspace = [None]
 
 
-def new_tensor(shape, dtype, device):
+def new_tensor(shape, dtype, device, whole_step=False):
     """An uninitialised tensor for a kernel's output: from the open step's workspace if there is one (and it is
-    not paused, and lives on this device), else from the allocator."""
+    not paused, and lives on this device), else from the allocator.  ``whole_step``: the tensor is kept for the rest
+    of the step (in the batch's plan, say), not only for the layer that makes it."""
     ws = _active_workspace[0]
     if ws is not None and ws.hold == 0 and torch.device(device) == ws.device and not torch.cuda.is_current_stream_capturing():
-        t = ws.take(shape, dtype)
+        t = ws.take(shape, dtype, whole_step)
         if t is not None:
             return t
     return torch.empty(tuple(shape), dtype=dtype, device=device)
 
 
 def new_ints(values, device):
-    """int32 device tensor of a host list (a step's tile lists and the like), its memory from the workspace."""
+    """int32 device tensor of a host list (a step's tile lists and the like), kept for the whole step."""
     host = torch.tensor(values, dtype=torch.int32)
-    out = new_tensor(host.shape, torch.int32, device)
+    out = new_tensor(host.shape, torch.int32, device, whole_step=True)
     out.copy_(host)
     return out
 
@@ -273,7 +282,7 @@ def rope_table(positions, head_dim, theta):
     per step and shared by every head of every layer with the same head size and base."""
     lib = library("core")
     T = positions.numel()
-    table = new_tensor((T, head_dim // 2, 2), torch.float32, positions.device)
+    table = new_tensor((T, head_dim // 2, 2), torch.float32, positions.device, whole_step=True)
     _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
                                      float(theta), _stream()), "rope_table")
     return table
@@ -511,7 +520,8 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
         sk = (num_splits, head_dim, pr)
         if sk not in plan["scratch"]:
             n = plan["num_tiles"] * n_kv_heads * num_splits * pr
-            plan["scratch"][sk] = (new_tensor((n * head_dim,), torch.float32, q.device), new_tensor((n * 2,), torch.float32, q.device))
+            plan["scratch"][sk] = (new_tensor((n * head_dim,), torch.float32, q.device, whole_step=True),
+                                   new_tensor((n * 2,), torch.float32, q.device, whole_step=True))
         part_o, part_ml = plan["scratch"][sk]
     if out is None:
         out = new_tensor(q.shape, q.dtype, q.device)

@@ -33,7 +33,7 @@ class RotaryEmbedding(Part):
         table: the table of the captured step would be replayed with every later step's positions."""
         table = None
         if self.rotary and batch is not None and qkv.shape[0] >= 64 and not getattr(batch, "decode_only", False):
-            key = ("rope", self.head_dim, self.theta)
+            key = ("rope", self.head_dim, self.theta, positions.data_ptr())
             table = batch.attention_plan.get(key)
             if table is None:
                 table = batch.attention_plan[key] = kernels.rope_table(positions, self.head_dim, self.theta)
