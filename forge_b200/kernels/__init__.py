@@ -110,7 +110,16 @@ def _check(lib, rc, what):
         raise KernelError(f"{what}: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
 
 
+# The current stream's handle, asked for once per kernel launch: torch's two C entry points answer in a fraction of a
+# microsecond, torch.cuda.current_stream() takes several (a prompt step of a 22-layer model launches 180 kernels and
+# is as long on the host as on the device).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -148,7 +157,10 @@ class StepWorkspace:
 
     def __init__(self, device):
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.buf = None
+        self.typed = {}
         self.capacity = 0
         self.offset = 0          # next free byte at the front (may run past capacity: then it only measures)
         self.back = 0            # bytes handed out from the back
@@ -157,11 +169,14 @@ class StepWorkspace:
         self.hold = 0            # > 0: paused
         self.allocations = 0     # outputs that had to come from the allocator while a step was open
 
+    ITEMSIZE = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.float16: 2, torch.int64: 8, torch.uint8: 1}
+
     def reserve(self, nbytes):
         nbytes = -(-int(nbytes) // self.ALIGN) * self.ALIGN
         if nbytes > self.capacity:
             self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
             self.capacity = nbytes
+            self.typed = {dt: self.buf.view(dt) for dt in self.ITEMSIZE}     # one view per element type to slice from
 
     def step(self):
         return _OpenStep(self)
@@ -178,8 +193,9 @@ class StepWorkspace:
     def take(self, shape, dtype, whole_step=False):
         n = 1
         for d in shape:
-            n *= int(d)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+            n *= d
+        size = self.ITEMSIZE[dtype]
+        nbytes = n * size
         padded = -(-nbytes // self.ALIGN) * self.ALIGN
         if whole_step:
             self.back += padded
@@ -191,7 +207,8 @@ class StepWorkspace:
         if self.offset + self.back > self.capacity:
             self.allocations += 1
             return None
-        return self.buf[start:start + nbytes].view(dtype).view(tuple(int(d) for d in shape))
+        first = start // size                        # start is a multiple of ALIGN, so of every element size
+        return self.typed[dtype][first:first + n].view(shape)
 
 
 class _OpenStep:
@@ -233,7 +250,7 @@ def new_tensor(shape, dtype, device, whole_step=False):
     not paused, and lives on this device), else from the allocator.  ``whole_step``: the tensor is kept for the rest
     of the step (in the batch's plan, say), not only for the layer that makes it."""
     ws = _active_workspace[0]
-    if ws is not None and ws.hold == 0 and torch.device(device) == ws.device and not torch.cuda.is_current_stream_capturing():
+    if ws is not None and ws.hold == 0 and device == ws.device:      # (a step is never open during a graph capture)
         t = ws.take(shape, dtype, whole_step)
         if t is not None:
             return t
