@@ -32,7 +32,7 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int kSmemLimit = 227 * 1024;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACCUM_F32 = 1, EPI_STORE_BF16 = 2, EPI_SWIGLU_BF16 = 3 };
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACCUM_F32 = 1, EPI_STORE_BF16 = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_ROPE = 4 };
 
 struct GemmParams {
     void* C;
@@ -41,6 +41,11 @@ struct GemmParams {
     int epilogue;
     int* status;
     int tma_out;        // fp32 results leave through shared memory and TMA stores / adds (the kernels that take a map of C)
+    // EPI_QKV_ROPE: the product is a step's q, k, v; its epilogue rotates q and k and puts k and v into the paged cache
+    const float* rope_table;         // [M, head_dim / 2, 2] (cos, sin) of each row's position, or null: no rotation
+    const int32_t* slot_mapping;     // [M] page * page_size + offset of each row's token (negative or null: no cache write)
+    __nv_bfloat16* kv_cache;         // [pages, 2, NKV, page_size, head_dim]
+    int NH, NKV, head_dim, page_size;
 };
 
 template <int BN> struct Cfg {
@@ -120,6 +125,62 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, const uint3
                 for (int i = 0; i < 16; ++i)
                     if (2 * i + 1 < width) dst[i] = __float2bfloat16_rn(silu(v[2 * i]) * v[2 * i + 1]);
             }
+        }
+    }
+}
+
+// EPI_QKV_ROPE for one row (token m) of a tile whose columns n0 .. n0 + BN - 1 are whole heads of the fused
+// [q heads | k heads | v heads] projection: per head, the HD sums leave tensor memory, get their bias, q and k heads
+// are rotated by the row's angles (half-split pairs d, d + HD/2, in fp32, as rope_cache.cu does), everything is
+// rounded once to bfloat16, and q goes to C [M, NH*HD], k and v into the cache at the row's slot.  The product never
+// exists in global memory in fp32.  (Formulas: src/operators/cuda/cuda_rope.cu:8-34; order of rotation and cache
+// update: src/inference/engines/generic_engine.cpp:961-973.)  Control flow is the same for all lanes of a warp.
+template <int BN, int HD>
+__device__ __forceinline__ void qkv_rope_row(const GemmParams& p, uint32_t t_row, int m, int n0) {
+    constexpr int half = HD / 2;
+    const bool row_ok = m < p.M;
+    const int slot = (row_ok && p.slot_mapping && p.kv_cache) ? p.slot_mapping[m] : -1;
+    const float2* tab = p.rope_table ? reinterpret_cast<const float2*>(p.rope_table) + (size_t)(row_ok ? m : 0) * half : nullptr;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += HD) {
+        const int n = n0 + c0;
+        if (n >= p.N) break;
+        uint32_t r[HD / 32][32];
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32b_x32(t_row + c0 + 32 * c, r[c]);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        const int head = n / HD;
+        const bool is_q = head < p.NH, is_v = head >= p.NH + p.NKV;
+        float v[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) v[i] = __uint_as_float(r[i / 32][i % 32]) + (p.bias ? __ldg(p.bias + n + i) : 0.f);
+        if (!is_v && tab) {
+#pragma unroll
+            for (int d = 0; d < half; ++d) {
+                const float2 cs = __ldg(tab + d);
+                const float x0 = v[d], x1 = v[d + half];
+                v[d] = x0 * cs.x - x1 * cs.y;
+                v[d + half] = x0 * cs.y + x1 * cs.x;
+            }
+        }
+        __nv_bfloat16* dst;
+        if (is_q) {
+            dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.NH * HD + (size_t)head * HD;
+        } else {
+            if (slot < 0) continue;
+            const int kvh = is_v ? head - p.NH - p.NKV : head - p.NH;
+            dst = p.kv_cache + (((size_t)(slot / p.page_size) * 2 + (is_v ? 1 : 0)) * p.NKV + kvh) * p.page_size * HD +
+                  (size_t)(slot % p.page_size) * HD;
+        }
+#pragma unroll
+        for (int i = 0; i < HD; i += 8) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[i], v[i + 1]), h1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), h3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+            uint4 o;
+            o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+            o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + i) = o;
         }
     }
 }
@@ -270,6 +331,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             bulk_commit_group();
                         }
                     }
+                    tc_fence_before_sync();
+                    mbar_arrive(&acc_empty[a]);
+                    continue;
+                }
+            }
+            if constexpr (BN % 128 == 0) {
+                if (p.epilogue == EPI_QKV_ROPE) {
+                    if (p.head_dim == 64) qkv_rope_row<BN, 64>(p, t_row, m, n0);
+                    else qkv_rope_row<BN, 128>(p, t_row, m, n0);
                     tc_fence_before_sync();
                     mbar_arrive(&acc_empty[a]);
                     continue;
@@ -1392,6 +1462,42 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         case 16: return launch<16>(ta, tw, p, stream);
         default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224, 256 or 512 (two CTAs on 256 x 256), got %d", bn);
     }
+}
+
+// The fused projection of a prompt step: x [M, K] . [Wq; Wk; Wv]^T (+ bias), whose epilogue rotates q and k by the rows'
+// angles (rope_table [M, head_dim/2, 2] of (cos, sin); null: no rotation), writes q [M, NH*head_dim] in bf16 and puts k
+// and v into the paged cache at slot_mapping (null or negative: not written).  Head sizes 64 and 128; for more than 128
+// rows (fewer go through forge_gemm_sm100 and the separate rotary kernel).
+extern "C" int forge_gemm_sm100_qkv_rope(const void* A, const void* W, const float* bias, void* q_out, void* kv_cache,
+                                         const float* rope_table, const int32_t* slot_mapping, int* status, int M, int K,
+                                         int NH, int NKV, int head_dim, int page_size, cudaStream_t stream) {
+    if (head_dim != 64 && head_dim != 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: head_dim %d (64 or 128)", head_dim);
+    if (M <= BM) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: for more than %d rows, got %d", BM, M);
+    if (K <= 0 || K % 8 != 0 || NH <= 0 || NKV <= 0 || page_size <= 0)
+        return forge::fail(FORGE_ERR_ARG, "gemm_sm100_qkv_rope: bad sizes K=%d NH=%d NKV=%d page=%d", K, NH, NKV, page_size);
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    const int N = (NH + 2 * NKV) * head_dim;
+    // tiles hold whole heads: 128 or 256 columns, whichever wastes less of the last wave (the cost model of forge_gemm_sm100)
+    const long tm = (M + BM - 1) / BM, ksteps = (K + UMMA_K - 1) / UMMA_K;
+    int bn = 128;
+    long best = -1;
+    for (int cand : {256, 128}) {
+        const long tiles = tm * ((N + cand - 1) / cand);
+        const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * ksteps * (64 + cand / 2) + 36L * cand;
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
+    const char* err = nullptr;
+    CUtensorMap ta, tw;
+    if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: A: %s", err);
+    if (!bf16_tile_map(W, N, K, bn, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: W: %s", err);
+    GemmParams p{q_out, bias, M, N, K, EPI_QKV_ROPE, status, 0, rope_table, slot_mapping, static_cast<__nv_bfloat16*>(kv_cache),
+                 NH, NKV, head_dim, page_size};
+    return bn == 256 ? launch<256>(ta, tw, p, stream) : launch<128>(ta, tw, p, stream);
 }
 
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }

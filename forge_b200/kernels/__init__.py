@@ -46,6 +46,7 @@ _SIGNATURES = {
     "gemm_sm100": {
         "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "forge_gemm_sm100_set_workspace": [_P, ctypes.c_longlong],
+        "forge_gemm_sm100_qkv_rope": [_P] * 8 + [_I] * 6 + [_P],
     },
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
@@ -717,6 +718,31 @@ def gemm_sm100(x, w, bias=None, accumulate_into=None, epilogue="none", tile_n=0,
                                      _need(status, "status", torch.int32), M, N, K, code, int(tile_n), None, _stream()),
            "gemm_sm100")
     return out
+
+
+def gemm_sm100_qkv_rope_supports(rows, head_dim, k):
+    """The projection whose epilogue rotates and stores: prompt portions (more than 128 rows), head sizes 64 and 128."""
+    return _TENSOR_CORE_GEMM and rows > 128 and head_dim in (64, 128) and k % 8 == 0
+
+
+def gemm_sm100_qkv_rope(x, w, bias, rope_table, slot_mapping, kv_cache, n_heads, n_kv_heads, head_dim, page_size, q_out=None):
+    """bf16 x [M,K] . w [(NH+2NKV)*HD, K]^T (+ bias) on the tensor cores; the epilogue rotates q and k by ``rope_table``
+    (fp32 [M, HD/2, 2] of (cos, sin); None: no rotation), returns q bf16 [M, NH*HD] and writes k and v into ``kv_cache``
+    at ``slot_mapping`` (None: not written).  The fp32 product never reaches global memory."""
+    lib = library("gemm_sm100")
+    (M, K), (N, K2) = x.shape, w.shape
+    if K != K2 or N != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"gemm_sm100_qkv_rope: x {tuple(x.shape)}, w {tuple(w.shape)} do not fit {n_heads}+2*{n_kv_heads} heads of {head_dim}")
+    if q_out is None:
+        q_out = new_tensor((M, n_heads * head_dim), torch.bfloat16, x.device)
+    if kv_cache is None:
+        slot_mapping = None
+    _check(lib, lib.forge_gemm_sm100_qkv_rope(
+        _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _opt(bias, "bias", torch.float32),
+        _need(q_out, "q_out", torch.bfloat16, 2), _opt(kv_cache, "kv_cache", torch.bfloat16), _opt(rope_table, "rope_table", torch.float32),
+        _opt(slot_mapping, "slot_mapping", torch.int32), _need(_gemm_status(x.device), "status", torch.int32), M, K, n_heads,
+        n_kv_heads, head_dim, page_size, _stream()), "gemm_sm100_qkv_rope")
+    return q_out
 
 
 _status_words = {}

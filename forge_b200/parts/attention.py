@@ -73,6 +73,18 @@ class GQAAttention(Part):
     def forward(self, x, batch, cache, residual):
         """x [T,H] normed input; cache: the layer's KV cache view; adds the output projection into residual."""
         g = batch.groups[cache.group]
+        offer = getattr(self.position, "fused_projection", None)
+        if offer is not None and self.qkv.tensor_core and kernels.gemm_sm100_qkv_rope_supports(x.shape[0], self.head_dim, self.hidden_size):
+            fused = offer(batch.positions, batch)
+            if fused is not None:
+                # prompt portions: the projection's epilogue rotates q and k and writes k and v into the pages
+                q = kernels.gemm_sm100_qkv_rope(x, self.qkv.weight, self.qkv.bias, fused["table"],
+                                                g.slot_mapping if cache.writable else None, cache.kv if cache.writable else None,
+                                                self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size)
+                o = kernels.paged_attention(q, cache.kv, g, batch, self.num_heads, self.num_kv_heads, self.head_dim,
+                                            cache.page_size, window=self.window, scale=self.scale)
+                self.o.forward(o, accumulate_into=residual)
+                return
         qkv = self.qkv.forward(x)                                           # fp32 [T,(NH+2NKV)*HD]
         fused = self._decode_in_one_kernel(batch, cache)
         if fused is not None:

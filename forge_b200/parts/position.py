@@ -27,16 +27,29 @@ class RotaryEmbedding(Part):
             return None
         return {"theta": self.theta, "rotary": self.rotary}
 
+    def _table(self, positions, batch):
+        """The step's cos/sin table, computed once per step (kept in the batch's ``attention_plan``), not once per
+        layer.  A batch that a CUDA graph replays keeps no table: the table of the captured step would be replayed
+        with every later step's positions."""
+        if not self.rotary or batch is None or getattr(batch, "decode_only", False):
+            return None
+        key = ("rope", self.head_dim, self.theta, positions.data_ptr())
+        table = batch.attention_plan.get(key)
+        if table is None:
+            table = batch.attention_plan[key] = kernels.rope_table(positions, self.head_dim, self.theta)
+        return table
+
+    def fused_projection(self, positions, batch):
+        """For the q/k/v product whose epilogue encodes and stores by itself (prompt portions): {"table": the step's
+        (cos, sin) table or None for no rotation}, or None if this part does not offer it.  As with ``fused_decode``
+        only the stock classes do: that epilogue computes the half-split rotation of the whole head."""
+        if type(self) not in (RotaryEmbedding, NoPosition) or batch is None or getattr(batch, "decode_only", False):
+            return None
+        return {"table": self._table(positions, batch)}
+
     def encode_and_store(self, qkv, positions, slot_mapping, kv_cache, num_heads, num_kv_heads, page_size, batch=None):
-        """``batch`` (optional): the step's batch; its ``attention_plan`` dict keeps the step's cos/sin table so
-        that it is computed once per step, not once per layer.  A batch that a CUDA graph replays keeps no
-        table: the table of the captured step would be replayed with every later step's positions."""
-        table = None
-        if self.rotary and batch is not None and qkv.shape[0] >= 64 and not getattr(batch, "decode_only", False):
-            key = ("rope", self.head_dim, self.theta, positions.data_ptr())
-            table = batch.attention_plan.get(key)
-            if table is None:
-                table = batch.attention_plan[key] = kernels.rope_table(positions, self.head_dim, self.theta)
+        """``batch`` (optional): the step's batch, which keeps the step's table of angles."""
+        table = self._table(positions, batch) if qkv.shape[0] >= 64 else None
         return kernels.rope_kv_write(qkv, positions, slot_mapping, kv_cache, num_heads, num_kv_heads, self.head_dim,
                                      page_size, self.theta, self.rt.dtype, rotary=self.rotary, table=table)
 

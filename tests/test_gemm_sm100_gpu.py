@@ -159,3 +159,37 @@ def test_refuses_what_it_cannot_do():
     with pytest.raises(k.KernelError, match="even"):
         k.gemm_sm100(_rand(4, 16), _rand(7, 16), epilogue="swiglu")
     assert not k.gemm_sm100_supports(64, 12) and k.gemm_sm100_supports(64, 16)
+
+
+@pytest.mark.parametrize("M,K,nh,nkv,hd,ps,bias,rotary", [
+    (300, 512, 8, 2, 64, 16, False, True),      # a tile of 128 columns holds two heads
+    (2048, 2048, 32, 4, 64, 64, False, True),   # the benchmark's prompt: 2560 columns
+    (257, 3584 // 7, 7, 1, 128, 8, True, True),  # head size 128, bias, columns that are no multiple of 256
+    (513, 192, 5, 5, 64, 16, True, False),      # no rotation (keys are stored as projected)
+])
+def test_projection_whose_epilogue_rotates_and_stores(M, K, nh, nkv, hd, ps, bias, rotary):
+    """x . [Wq; Wk; Wv]^T with rotary encoding and the paged cache write in the product's epilogue, against the plain
+    product followed by the plain rotate-and-store; some rows have no slot (their keys must not be written)."""
+    from forge_b200 import kernels as k
+    from plain import kernels_ref as R
+    g = torch.Generator().manual_seed(M + K)
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    b = torch.randn(N, generator=g) * 0.3 if bias else None
+    positions = torch.randint(0, 5000, (M,), generator=g, dtype=torch.int32)
+    pages = -(-M // ps) + 3
+    slots = torch.randperm(pages * ps, generator=g)[:M].to(torch.int32)
+    slots[5] = -1
+    slots[M - 1] = -1
+    cache0 = torch.randn(pages, 2, nkv, ps, hd, generator=g).to(torch.bfloat16)
+    qkv = R.gemm_ref(x, w, b)
+    q_ref, cache_ref = R.rope_kv_write_ref(qkv, positions, slots, cache0, nh, nkv, hd, ps, 10000.0, rotary)
+    dev = "cuda:0"
+    cache = cache0.clone().to(dev)
+    table = k.rope_table(positions.to(dev), hd, 10000.0) if rotary else None
+    q = k.gemm_sm100_qkv_rope(x.to(dev), w.to(dev), None if b is None else b.to(dev), table, slots.to(dev), cache, nh, nkv, hd, ps)
+    k.check_kernel_status()
+    assert (q.float().cpu() - q_ref).abs().max() <= 2e-2 * q_ref.abs().max()
+    assert (cache.float().cpu() - cache_ref).abs().max() <= 2e-2 * cache_ref.abs().max()
+    assert torch.equal(cache.cpu()[cache_ref == cache0.float()], cache0[cache_ref == cache0.float()])
