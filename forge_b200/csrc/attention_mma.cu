@@ -18,6 +18,7 @@
 
 #include "attention_no_alloc.h"
 #include "common.cuh"
+#include "checks.cuh"
 #include "mma_sync.cuh"
 
 #ifndef FORGE_ATT_HD
@@ -63,8 +64,10 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
     for (int i = 0; i < (BKV + 31) / 32; ++i) {
         const int t = t0 + lane + 32 * i;
         ridx[i] = -1;
-        if (lane + 32 * i < BKV && t >= lo && t < hi)
-            ridx[i] = (table[t / p.page_size] * 2 * p.NKV + kvh) * p.page_size + t % p.page_size;
+        if (lane + 32 * i < BKV && t >= lo && t < hi) {
+            const int page = table[t / p.page_size];
+            if (FORGE_PAGE_OK(page)) ridx[i] = (page * 2 * p.NKV + kvh) * p.page_size + t % p.page_size;      // (checks build) else: zeros
+        }
     }
     const int v_rows = p.NKV * p.page_size;                 // a page's values follow its keys
 #pragma unroll 4
@@ -408,7 +411,10 @@ decode_attention_fused_kernel(const DecodeParams p) {
         __nv_bfloat16* kd = my_k + (size_t)buf * 2 * DKV * LD;
         const int tk = t * DKV + lane;                                   // lane = row of the tile
         int ridx = -1;
-        if (tk >= kv_lo && tk < kv_hi) ridx = (table[tk / p.page_size] * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
+        if (tk >= kv_lo && tk < kv_hi) {
+            const int page = table[tk / p.page_size];
+            if (FORGE_PAGE_OK(page)) ridx = (page * 2 * p.NKV + kvh) * p.page_size + tk % p.page_size;
+        }
         const int v_rows = p.NKV * p.page_size;
 #pragma unroll 4
         for (int c = lane; c < DKV * CPR; c += 32) {
@@ -458,7 +464,7 @@ decode_attention_fused_kernel(const DecodeParams p) {
         if (h < G) {
             qs[h * LD + d] = __float2bfloat16_rn(x0);
             qs[h * LD + d + half] = __float2bfloat16_rn(x1);
-        } else if (writes_kv) {
+        } else if (writes_kv && FORGE_SLOT_OK(slot)) {
             __nv_bfloat16* dst = page_base + (h == G ? 0 : (size_t)p.NKV * p.page_size * HD);
             dst[d] = __float2bfloat16_rn(x0);
             dst[d + half] = __float2bfloat16_rn(x1);
@@ -784,4 +790,6 @@ extern "C" int forge_decode_attention_fused(const float* qkv, void* kv, void* ou
 }
 
 extern "C" int forge_attention_head_dim() { return HD; }
+// (checks build) the bounds that this library's kernels test page ids and slots against
+FORGE_DEFINE_CHECKS_ENTRY(attention_mma)
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }

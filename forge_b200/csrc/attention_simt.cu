@@ -8,6 +8,7 @@
 // request was cut into steps or on what else is in the batch.  This kernel serves the true 32-bit path
 // and any shape the tensor-core kernel refuses: any HD <= 256, any NH/NKV ratio, any page size.
 #include "common.cuh"
+#include "checks.cuh"
 
 namespace {
 
@@ -26,6 +27,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ kv_ca
     const int kvh = h / (NH / NKV);
     const int pos = positions[t];
     const int32_t* table = block_table + (size_t)tok_req[t] * max_pages;
+    if (!FORGE_TOKEN_OK(t)) return;
 
     float qr[DPL], acc[DPL];
 #pragma unroll
@@ -40,6 +42,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ kv_ca
         const int page_idx = j / page_size, off0 = j % page_size;
         const int page = table[page_idx];
         const int n_here = min(page_size - off0, pos - j + 1);
+        if (!FORGE_PAGE_OK(page)) { j += n_here; continue; }          // (checks build) a page outside the pool is skipped
         const T* kp = kv_cache + (((size_t)page * 2 + 0) * NKV + kvh) * page_size * HD;
         const T* vp = kv_cache + (((size_t)page * 2 + 1) * NKV + kvh) * page_size * HD;
         for (int o = off0; o < off0 + n_here; ++o) {
@@ -111,3 +114,6 @@ extern "C" int forge_paged_attention_simt(const void* q, const void* kv_cache, c
     if (dtype == FORGE_BF16) return launch<__nv_bfloat16>(q, kv_cache, block_table, tok_req, positions, out, T, NH, NKV, HD, page_size, max_pages, window, scale, stream);
     return forge::fail(FORGE_ERR_ARG, "paged_attention_simt: unknown dtype %d", dtype);
 }
+
+// (checks build) the bounds that this file's kernel tests page ids and token indices against
+FORGE_DEFINE_CHECKS_ENTRY(attention_simt)

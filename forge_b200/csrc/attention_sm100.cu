@@ -23,6 +23,7 @@
 //   o = sum_j softmax(s)_j v_j        (formulas of src/operators/cuda/cuda_flash_attn.cu:154-248)
 // Needs G <= 128, 64 % page_size == 0 and page_size >= 8; everything else is served by attention_mma.cu.
 #include "common.cuh"
+#include "checks.cuh"
 #include "sm100.cuh"
 
 #ifndef FORGE_ATT_HD
@@ -211,7 +212,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                     int rows[8], n_valid = 0;
                     for (int i = 0; i < ppt; ++i) {
                         const int tp = t0 + i * p.page_size, page = page_win[(it - it0) * ppt + i];
-                        const bool live = tp < kv_hi && tp + p.page_size > kv_lo && page >= 0;
+                        const bool live = tp < kv_hi && tp + p.page_size > kv_lo && page >= 0 && FORGE_PAGE_OK(page);
                         rows[i] = live ? (page * 2 * p.NKV + kvh) * p.page_size : -1;
                         n_valid += live;
                     }
@@ -469,3 +470,6 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
 }
 
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }
+
+// (checks build) the bounds that this library's kernel tests page ids against
+FORGE_DEFINE_CHECKS_ENTRY(attention_sm100)

@@ -22,6 +22,7 @@
 // and silu-multiply launches (src/operators/cuda/cuda_quant.cu:582-599, cuda_gemm.cu:7-55,
 // cuda_elementwise.cu:8-48).
 #include "common.cuh"
+#include "checks.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -139,7 +140,8 @@ template <int BN, int HD>
 __device__ __forceinline__ void qkv_rope_row(const GemmParams& p, uint32_t t_row, int m, int n0) {
     constexpr int half = HD / 2;
     const bool row_ok = m < p.M;
-    const int slot = (row_ok && p.slot_mapping && p.kv_cache) ? p.slot_mapping[m] : -1;
+    int slot = (row_ok && p.slot_mapping && p.kv_cache) ? p.slot_mapping[m] : -1;
+    if (slot >= 0 && !FORGE_SLOT_OK(slot)) slot = -1;             // (checks build) a slot outside the pool is not written
     const float2* tab = p.rope_table ? reinterpret_cast<const float2*>(p.rope_table) + (size_t)(row_ok ? m : 0) * half : nullptr;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += HD) {
@@ -1499,5 +1501,8 @@ extern "C" int forge_gemm_sm100_qkv_rope(const void* A, const void* W, const flo
                  NH, NKV, head_dim, page_size};
     return bn == 256 ? launch<256>(ta, tw, p, stream) : launch<128>(ta, tw, p, stream);
 }
+
+// (checks build) the bounds that this library's projection tests slots against
+FORGE_DEFINE_CHECKS_ENTRY(gemm_sm100)
 
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }

@@ -9,6 +9,7 @@
 // [num_pages, 2 (k,v), NKV, page_size, HD].  A negative slot skips the cache write (layers that read
 // another layer's cache).  `rotary == 0` copies without rotating (a model without rotary encoding).
 #include "common.cuh"
+#include "checks.cuh"
 
 namespace {
 
@@ -64,7 +65,7 @@ rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ 
         return;
     }
     const int slot = slot_mapping ? slot_mapping[t] : -1;
-    if (slot < 0) return;
+    if (slot < 0 || !FORGE_SLOT_OK(slot)) return;
     const int page = slot / page_size, off = slot % page_size;
     const int is_v = h >= NH + NKV, kvh = h - NH - (is_v ? NKV : 0);
     TCache* dst = kv_cache + (((size_t)page * 2 + is_v) * NKV + kvh) * page_size * HD + (size_t)off * HD;
@@ -121,7 +122,7 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const int32_t* __restric
             continue;
         }
         const int slot = slot_mapping ? slot_mapping[t] : -1;
-        if (slot < 0) continue;
+        if (slot < 0 || !FORGE_SLOT_OK(slot)) continue;
         const int page = slot / page_size, off = slot % page_size;
         const int is_v = h >= NH + NKV, kvh = h - NH - (is_v ? NKV : 0);
         TCache* dst = kv_cache + (((size_t)page * 2 + is_v) * NKV + kvh) * page_size * HD + (size_t)off * HD;
@@ -165,3 +166,6 @@ extern "C" int forge_rope_kv_write(const float* qkv, const int32_t* positions, c
                           reinterpret_cast<const float2*>(table)));
     return forge::check_launch("rope_kv_write", e);
 }
+
+// (checks build) the bounds that this library's kernels test page ids, slots and token indices against
+FORGE_DEFINE_CHECKS_ENTRY(rope)

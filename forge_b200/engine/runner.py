@@ -103,6 +103,8 @@ class ModelRunner:
         # first step of the largest size no step asks the allocator for anything but the logits it hands out.
         from .. import kernels
         self.workspace = kernels.StepWorkspace(self.device)
+        # FORGE_CHECKS=1: kernels test every page id, slot and token index before use (csrc/checks.cuh)
+        self.first_bad = torch.zeros(3, dtype=torch.int32, device=self.device) if kernels.checks_enabled() else None
         # decode steps replay a captured graph only if every part of the model says that it may be captured
         self.graph_safe = self.model.graph_safe()
         self.cuda_graphs = bool(cuda_graphs) and self.graph_safe
@@ -157,6 +159,9 @@ class ModelRunner:
         if self.cuda_graphs and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             # the graph's own logits buffer is rewritten by the next replay: hand out a copy
             return self.decode_step(entries)[0].clone()
+        if self.first_bad is not None:
+            from .. import kernels
+            kernels.configure_checks(self.num_pages, self.page_size, sum(len(e.tokens) for e in entries), self.status, self.first_bad)
         with self.workspace.step() as ws:
             batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
             self.storage.zero_state_slots(self.manager.take_fresh_slots())
@@ -188,6 +193,9 @@ class ModelRunner:
                 self._last_greedy = None
             g = DecodeGraph(self, S, max_context=bucket)
         self._decode_graphs[(S, bucket)] = g                               # most recently used last
+        if self.first_bad is not None:
+            from .. import kernels
+            kernels.configure_checks(self.num_pages, self.page_size, S, self.status, self.first_bad)
         hs = layout_step(entries, self.manager)
         self.storage.zero_state_slots(self.manager.take_fresh_slots())
         prev = self._last_greedy if tokens_on_device else None
@@ -230,7 +238,14 @@ class ModelRunner:
             self.status.zero_()
             raise RuntimeError(f"a kernel reported an error (status word {s:#x}): "
                                + ("token id outside the vocabulary; " if s & 1 else "")
-                               + ("a bounded wait ran out; " if s & 2 else ""))
+                               + ("a bounded wait ran out; " if s & 2 else "")
+                               + (self._bad_index() if s & 16 else ""))
+
+    def _bad_index(self):
+        kind, value, limit = self.first_bad.tolist() if self.first_bad is not None else (0, 0, 0)
+        self.first_bad.zero_() if self.first_bad is not None else None
+        what = {1: "page id", 2: "cache slot", 3: "token index"}.get(kind, "index")
+        return f"a kernel was given a {what} outside its range: {value} (limit {limit}); "
 
 
 class PendingTokens:

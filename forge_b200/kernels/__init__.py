@@ -66,10 +66,49 @@ _SIGNATURES = {
 
 _libs = {}
 
+# FORGE_CHECKS=1: every library is built with index checks (csrc/checks.cuh): page ids, slots and token indices are
+# tested before use, a bad one raises bit 4 of the step's status word and is skipped.  The entries that tell a
+# library the bounds, per library (one per source file that checks):
+_CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
+                  "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
+                  "attention_mma": ["forge_checks_configure_attention_mma"],
+                  "attention_sm100": ["forge_checks_configure_attention_sm100"]}
+_check_bounds = [None]          # (num_pages, page_size, num_tokens, status tensor, first_bad tensor) of the current step
+
+
+def checks_enabled():
+    return os.environ.get("FORGE_CHECKS", "0") == "1"
+
+
+def _configure_library_checks(name, lib):
+    b = _check_bounds[0]
+    if b is None:
+        return
+    for fn in _CHECK_ENTRIES.get(name, []):
+        f = getattr(lib, fn)
+        f.argtypes = [_I, _I, _I, _P, _P, _P]
+        f.restype = c_int
+        rc = f(b[0], b[1], b[2], b[3].data_ptr(), b[4].data_ptr(), _stream())
+        if rc != 0:
+            raise KernelError(f"{fn}: {lib.forge_last_error().decode(errors='replace')}")
+
+
+def configure_checks(num_pages, page_size, num_tokens, status, first_bad):
+    """(checks build) Gives every loaded library the bounds of the step that is about to run; libraries loaded later
+    get them when they load.  ``status``: int32 [1]; ``first_bad``: int32 [3] (kind, value, limit of the first offender)."""
+    if not checks_enabled():
+        return
+    _check_bounds[0] = (int(num_pages), int(page_size), int(num_tokens), status, first_bad)
+    for (name, defines), lib in _libs.items():
+        if ("FORGE_CHECKS", 1) in defines:
+            _configure_library_checks(name, lib)
+
 
 def library(name, defines=None):
     """Loads (building first if needed) kernel library ``name`` (variant ``defines``) and returns its
     ctypes handle."""
+    if checks_enabled() and name in _CHECK_ENTRIES:
+        defines = dict(defines or {}, FORGE_CHECKS=1)
     key = (name, tuple(sorted((defines or {}).items())))
     lib = _libs.get(key)
     if lib is not None:
@@ -90,6 +129,8 @@ def library(name, defines=None):
         f.restype = c_int
     lib.forge_last_error.restype = ctypes.c_char_p
     _libs[key] = lib
+    if defines and defines.get("FORGE_CHECKS") == 1:
+        _configure_library_checks(name, lib)
     return lib
 
 

@@ -233,3 +233,21 @@ def test_prompt_steps_do_not_go_through_the_allocator(tiny, dtype):
     with pytest.raises(StepError, match="96"):
         runner.step([StepEntry("c", toks + toks[:33], [])])
     assert runner.manager.num_tokens("c") == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_schedules_under_the_checks_build(tiny, dtype, monkeypatch):
+    """FORGE_CHECKS=1: the kernels are built with a test of every page id, slot and token index before it is used.
+    The four schedules (valid tables only) must run as before and leave the status word at zero."""
+    from forge_b200 import kernels
+    name, d, plain, reqs, want = tiny
+    monkeypatch.setenv("FORGE_CHECKS", "1")
+    for schedule in ("whole", "last_one_by_one", "changing_portions", "mixed"):
+        steps = getattr(schedules, schedule)(reqs)
+        runner = make_runner(d, dtype, schedules.peak_tokens(reqs, steps, round_to=16))
+        assert runner.first_bad is not None
+        got = run_schedule(runner, reqs, steps)             # ends with check_status(): raises if a check fired
+        assert int(runner.status.item()) == 0 and runner.first_bad.tolist() == [0, 0, 0]
+        assert first_bad(got, want, TOL[dtype]) is None, (schedule, first_bad(got, want, TOL[dtype]))
+    built = [n for (n, defines) in kernels._libs if ("FORGE_CHECKS", 1) in defines]
+    assert "core" in built and (dtype == "float32" or "attention_mma" in built), built
