@@ -7,10 +7,13 @@ from a model folder (config.json + safetensors, or seeded random weights) to gen
 """
 from .api import GenerateRequest, InferenceContext, Model, RequestScheduler, RequestStatus, SamplerConfig
 from .config import ConfigError, load_config, register_architecture, registered_architectures
+from .kernels import (profiler_disable, profiler_enable, profiler_enabled, profiler_print, profiler_reset,
+                      profiler_summary)
 from .weights import WeightError, write_random_model
 
 __version__ = "0.1.0"
 
 __all__ = ["Model", "InferenceContext", "RequestScheduler", "SamplerConfig", "GenerateRequest", "RequestStatus",
            "ConfigError", "WeightError", "load_config", "register_architecture", "registered_architectures",
-           "write_random_model", "__version__"]
+           "write_random_model", "profiler_enable", "profiler_disable", "profiler_enabled", "profiler_reset",
+           "profiler_summary", "profiler_print", "__version__"]

@@ -45,8 +45,47 @@ def build_parser():
                  "--image", "--system-prompt"):
         ap.add_argument(flag, dest="unsupported_" + flag.strip("-").replace("-", "_"), default=None)
     ap.add_argument("-i", "--interactive", action="store_true")
-    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--bench", action="store_true", help="prefill of 32/128/512 tokens and 128 decode steps, timed")
     return ap
+
+
+def run_benchmark(model, verbose=False):
+    """The reference's built-in benchmark (src/cli/forge_cli.cpp:242-321): prefill of 32, 128 and 512 dummy tokens
+    (three runs each from an empty cache, mean), then 128 single-token decode steps; wall-clock around device work."""
+    import torch
+    cfg = model.config
+    print("\n  Forge - Benchmark\n")
+    print(f"  Model: {cfg.architecture} ({cfg.num_hidden_layers} layers, {cfg.hidden_size}d)")
+    print("  Warming up...")
+    ctx = model.create_context()
+    ctx.forward([0] * 8, 0)
+    ctx.reset_kv()
+    print("  Warmup done\n")
+    limit = model.runner.plan.max_positions
+    for ps in (32, 128, 512):
+        if ps + 130 > limit or ps > model.runner.num_pages * model.runner.page_size:
+            continue
+        runner = model.runner
+        from .engine import StepEntry
+        runner.admit("bench"); runner.step([StepEntry("bench", [0] * ps, [ps - 1])]); runner.release("bench")   # kernels for this size
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            runner.admit("bench")
+            runner.step([StepEntry("bench", [0] * ps, [ps - 1])])
+            runner.release("bench")
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / 3
+        print(f"  Prefill {ps:4d} tokens: {ms:7.2f} ms  ({ps / ms * 1e3:8.1f} tok/s)")
+    steps = 128
+    out = model.generate([0], max_new_tokens=8, do_sample=False)                     # captures the decode graph
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = model.generate([0], max_new_tokens=steps + 1, do_sample=False)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3
+    print(f"  Decode  {out['num_generated_tokens'] - 1:4d} tokens: {ms:7.2f} ms  ({(out['num_generated_tokens'] - 1) / ms * 1e3:8.1f} tok/s)")
+    print("\n  Benchmark complete")
 
 
 def main(argv=None):
@@ -56,8 +95,6 @@ def main(argv=None):
             raise SystemExit(f"Error: option --{k[12:].replace('_', '-')} selects a feature this engine does not have")
     if a.interactive:
         raise SystemExit("Error: interactive chat is not part of this engine; give a prompt with -p")
-    if a.bench:
-        raise SystemExit("Error: use bench.py at the repository root for measurements")
     from . import Model, load_config, write_random_model
     from .config import config_from_dict
     model_dir = a.model
@@ -73,6 +110,10 @@ def main(argv=None):
         for k, v in cfg.to_dict().items():
             print(f"  {k}: {v}")
         return 0
+    if a.bench:
+        model = Model(model_dir, dtype=a.dtype, block_size=a.page_size, max_num_seqs=1, max_tokens_per_step=a.max_tokens_per_step)
+        run_benchmark(model, a.verbose)
+        return 0
     if a.prompt is None and a.prompt_file is None:
         raise SystemExit("Error: no prompt (-p); interactive mode is not part of this engine")
     prompt = parse_ids(a.prompt if a.prompt is not None else open(a.prompt_file).read())
@@ -80,6 +121,9 @@ def main(argv=None):
     model = Model(model_dir, dtype=a.dtype, block_size=a.page_size, max_num_seqs=1,
                   max_tokens_per_step=a.max_tokens_per_step)
     times = []
+    if a.verbose:                      # per-kernel timing table at the end (decode steps are launched one by one meanwhile)
+        from . import kernels
+        kernels.profiler_enable()
 
     def on_token(tok, step):
         times.append(time.perf_counter())
@@ -101,6 +145,7 @@ def main(argv=None):
           f"{out['num_generated_tokens'] / max(total_ms, 1e-9) * 1e3:.1f} tok/s]")
     if a.verbose:
         print(f"  finish_reason: {out['finish_reason']}", file=sys.stderr)
+        kernels.profiler_print(sys.stderr)
     return 0
 
 

@@ -107,11 +107,22 @@ class ModelRunner:
         self.first_bad = torch.zeros(3, dtype=torch.int32, device=self.device) if kernels.checks_enabled() else None
         # decode steps replay a captured graph only if every part of the model says that it may be captured
         self.graph_safe = self.model.graph_safe()
-        self.cuda_graphs = bool(cuda_graphs) and self.graph_safe
+        self._cuda_graphs = bool(cuda_graphs) and self.graph_safe
         self.max_decode_graphs = max(1, int(max_decode_graphs))
         self._decode_graphs = {}
         self._last_greedy = None
         self._token_rings = {}
+
+    @property
+    def cuda_graphs(self):
+        """Whether decode steps replay a captured graph now: the runner was made so, the model allows it, and the
+        per-kernel timing (kernels.profiler_enable) is off."""
+        from .. import kernels
+        return self._cuda_graphs and not kernels.profiler_enabled()
+
+    @cuda_graphs.setter
+    def cuda_graphs(self, on):
+        self._cuda_graphs = bool(on) and self.graph_safe
 
     # ---------------------------------------------------------------------------------- requests
     def admit(self, req_id):
@@ -162,6 +173,8 @@ class ModelRunner:
         if self.first_bad is not None:
             from .. import kernels
             kernels.configure_checks(self.num_pages, self.page_size, sum(len(e.tokens) for e in entries), self.status, self.first_bad)
+        from .. import kernels as _k
+        _k.profiler_step_begin()
         with self.workspace.step() as ws:
             batch = build_step_batch(entries, self.manager, self.device, self.max_pages_per_request, status=self.status)
             self.storage.zero_state_slots(self.manager.take_fresh_slots())

@@ -150,6 +150,76 @@ def _check(lib, rc, what):
     _launches[0] += 1
     if rc != 0:
         raise KernelError(f"{what}: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
+    if _profile["on"]:
+        _profile_mark(what)
+
+
+# ------------------------------------------------------------------------------------------ timing
+# A per-kernel-class timing table in the manner of the reference's PerfProfiler (include/forge/perf_profiler.h:28-218,
+# src/bindings/profiler.cpp): while it is enabled an event is recorded after every launch, and a kernel's time is the
+# time from the end of its predecessor on the stream to its own end (so it includes the hand-over between the two).
+# Decode steps are launched kernel by kernel meanwhile (a CUDA graph replay has no launches to put events between).
+_profile = {"on": False, "last": None, "pending": [], "records": {}}
+
+
+def profiler_enable():
+    _profile["on"] = True
+    _profile["last"] = None
+
+
+def profiler_disable():
+    _profile["on"] = False
+
+
+def profiler_enabled():
+    return _profile["on"]
+
+
+def profiler_reset():
+    _profile["pending"].clear()
+    _profile["records"].clear()
+    _profile["last"] = None
+
+
+def profiler_step_begin():
+    """The time before a step's first kernel belongs to nobody."""
+    if _profile["on"]:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        _profile["last"] = e
+
+
+def _profile_mark(what):
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    if _profile["last"] is not None:
+        _profile["pending"].append((what, _profile["last"], e))
+    _profile["last"] = e
+
+
+def profiler_summary():
+    """{kernel class: {count, total_ms, avg_ms, min_ms, max_ms, last_ms}} (the reference's field names)."""
+    if _profile["pending"]:
+        torch.cuda.synchronize()
+        for what, e0, e1 in _profile["pending"]:
+            ms = e0.elapsed_time(e1)
+            r = _profile["records"].setdefault(what, {"count": 0, "total_ms": 0.0, "min_ms": float("inf"), "max_ms": 0.0, "last_ms": 0.0})
+            r["count"] += 1
+            r["total_ms"] += ms
+            r["min_ms"], r["max_ms"], r["last_ms"] = min(r["min_ms"], ms), max(r["max_ms"], ms), ms
+        _profile["pending"].clear()
+    return {k: dict(v, avg_ms=v["total_ms"] / v["count"]) for k, v in _profile["records"].items()}
+
+
+def profiler_print(file=None):
+    import sys
+    rows = sorted(profiler_summary().items(), key=lambda kv: -kv[1]["total_ms"])
+    total = sum(r["total_ms"] for _, r in rows) or 1.0
+    out = file or sys.stderr
+    print(f"{'kernel':<28}{'count':>8}{'total ms':>12}{'avg us':>10}{'min us':>10}{'max us':>10}{'share':>8}", file=out)
+    for name, r in rows:
+        print(f"{name:<28}{r['count']:>8}{r['total_ms']:>12.3f}{1e3 * r['avg_ms']:>10.1f}{1e3 * r['min_ms']:>10.1f}"
+              f"{1e3 * r['max_ms']:>10.1f}{100 * r['total_ms'] / total:>7.1f}%", file=out)
 
 
 # The current stream's handle, asked for once per kernel launch: torch's two C entry points answer in a fraction of a

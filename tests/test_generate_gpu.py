@@ -265,3 +265,39 @@ def test_sixty_four_requests_decode_through_the_graph(tiny, dtype):
         ref = torch.stack([w[p] for w in want])
         assert max_rel_err(lg, ref) <= TOL[dtype], f"decode step {s}"
     runner.check_status()
+
+
+def test_per_kernel_timing_table(tiny):
+    """profiler_enable / profiler_summary in the reference's manner (src/bindings/profiler.cpp): while it is on, decode
+    steps are launched kernel by kernel, every kernel class gets counts and times, and the tokens are what they are
+    with it off."""
+    import forge_b200 as forge
+    name, d, plain = tiny
+    prompt = random_tokens(9, TINY[name]["vocab_size"], seed=5)
+    model = forge.Model(d, dtype="bfloat16", max_num_seqs=2, cache_tokens=256)
+    want = model.generate(prompt, max_new_tokens=8, do_sample=False)["token_ids"]
+    forge.profiler_reset()
+    forge.profiler_enable()
+    try:
+        assert forge.profiler_enabled() and not model.runner.cuda_graphs
+        got = model.generate(prompt, max_new_tokens=8, do_sample=False)["token_ids"]
+        table = forge.profiler_summary()
+    finally:
+        forge.profiler_disable()
+    assert model.runner.cuda_graphs
+    assert_greedy_follows_plain(plain.logits, prompt, got, TOL["bfloat16"], "with the timing on")
+    assert len(got) == len(want)
+    layers = TINY[name]["num_hidden_layers"]
+    assert table["rmsnorm"]["count"] == 8 * (2 * layers + 1)
+    for row in table.values():
+        assert row["count"] > 0 and 0 < row["min_ms"] <= row["avg_ms"] <= row["max_ms"] and row["total_ms"] > 0
+    assert {"embedding", "rmsnorm", "argmax"} <= set(table)
+
+
+def test_command_line_benchmark(tiny):
+    name, d, plain = tiny
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "--bench", "--dtype", "bfloat16"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "Prefill   32 tokens" in proc.stdout and "Prefill  512 tokens" in proc.stdout and "Decode   128 tokens" in proc.stdout
+    assert "Benchmark complete" in proc.stdout
