@@ -8,7 +8,8 @@ from types import SimpleNamespace
 
 import torch
 
-from forge_b200.kernels import decode_attention_fused, gemm_sm100, paged_attention, paged_attention_mma
+from forge_b200.kernels import (decode_attention_fused, gemm_sm100, gemm_sm100_qkv_rope, paged_attention, paged_attention_mma,
+                                rope_table)
 
 DEV = "cuda:0"
 H, I, NH, NKV, HD, PS = 2048, 5632, 32, 4, 64, 16
@@ -18,7 +19,7 @@ def _bf16(*shape, scale=1.0):
     return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
 
 
-def _attention_inputs(reqs):
+def _attention_inputs(reqs, NH=NH, NKV=NKV, HD=HD):
     """reqs: [(context_before, q_len)]; pages laid out in order."""
     pages = sum(-(-(c + q) // PS) for c, q in reqs)
     max_pages = max(-(-(c + q) // PS) for c, q in reqs)
@@ -67,12 +68,22 @@ def case(name):
     if name == "attention_prefill":          # one request, 2048 tokens, causal: 17.2 GFLOP
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
+    if name == "attention_prefill_hd128":    # the Llama-3-8B heads: 32 / 8 kv heads of 128, one request of 2048 tokens: 34.4 GFLOP
+        q, kv, g, b = _attention_inputs([(0, 2048)], 32, 8, 128)
+        return (lambda: paged_attention(q, kv, g, b, 32, 8, 128, PS)), 0, 2 * 2048 * 2048 * 32 * 128
+    if name == "gemm_prefill_qkv_rope":      # 2048 tokens x [2560, 2048]; the epilogue rotates q, k and writes q (bf16) and the cache
+        x, w = _bf16(2048, H), _bf16((NH + 2 * NKV) * HD, H, scale=0.02)
+        pos = torch.arange(2048, dtype=torch.int32, device=DEV)
+        table, kv = rope_table(pos, HD, 1e4), _bf16(2048 // PS, 2, NKV, PS, HD)
+        return (lambda: gemm_sm100_qkv_rope(x, w, None, table, pos, kv, NH, NKV, HD, PS)), \
+            (x.numel() + w.numel()) * 2 + 2048 * w.shape[0] * 2, 2 * 2048 * w.numel()
     if name == "attention_prefill_mma":      # the same through the mma.sync kernel, for comparison
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
     raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
-                     "gemm_prefill_down attention_decode attention_decode_fused attention_prefill attention_prefill_mma")
+                     "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_prefill "
+                     "attention_prefill_hd128 attention_prefill_mma")
 
 
 def main(argv):
