@@ -31,9 +31,12 @@ def _ids(prompt_ids):
 
 
 class Model:
-    def __init__(self, path=None, device="cuda", dtype="bfloat16", *, config=None, tensors=None, block_size=16,
+    def __init__(self, path=None, device="cuda", dtype="bfloat16", *, config=None, tensors=None, block_size=64,
                  max_num_seqs=4, cache_tokens=None, max_tokens_per_step=2048, memory_fraction=0.6):
-        """path: model folder (config.json + model.safetensors[.index.json]); or ``config`` + ``tensors``."""
+        """path: model folder (config.json + model.safetensors[.index.json]); or ``config`` + ``tensors``.
+        ``block_size``: tokens per cache page.  64 (the default) is what the prompt attention is fastest with (a key
+        tile of 64 is then one TMA box; 43 us a layer at 2,048 tokens against 54 us with pages of 16) and what the
+        benchmark uses; 8, 16 and 32 give the same results with finer-grained memory."""
         dev = "cuda:0" if device in ("cuda", "gpu") else device
         if not str(dev).startswith("cuda"):
             raise ValueError(f"forge_b200 runs on CUDA devices only, not {device!r}")

@@ -39,7 +39,7 @@ def build_parser():
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
     ap.add_argument("--random-weights", metavar="CONFIG.json", help="make a random model from this config")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page (8, 16, 32 or 64)")
     ap.add_argument("--max-tokens-per-step", type=int, default=2048)
     for flag in ("-ngl", "--n-gpu-layers", "-t", "--threads", "-b", "--batch-size", "--kv-cache-dtype", "--mmproj",
                  "--image", "--system-prompt"):

@@ -17,7 +17,7 @@ from .runner import ModelRunner, StepEntry
 DEFAULT_MAX_LIVE = 4
 
 
-def replay(model_dir, dtype, out_dir, max_tokens, lines, page_size=16, stdout=None, max_live=DEFAULT_MAX_LIVE):
+def replay(model_dir, dtype, out_dir, max_tokens, lines, page_size=64, stdout=None, max_live=DEFAULT_MAX_LIVE):
     stdout = stdout or sys.stdout
     os.makedirs(out_dir, exist_ok=True)
     # the pool holds max_tokens tokens, each live request rounded up to a multiple of 64
@@ -55,7 +55,7 @@ def main(argv=None):
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-requests", type=int, default=DEFAULT_MAX_LIVE, help="most requests live at a time")
     a = ap.parse_args(argv)
     return replay(a.model, a.dtype, a.out, a.max_tokens, sys.stdin, page_size=a.page_size, max_live=a.max_requests)

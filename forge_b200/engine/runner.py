@@ -39,7 +39,7 @@ def resolve_dtype(dtype):
 
 class ModelRunner:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", device="cuda:0",
-                 page_size=16, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True,
+                 page_size=64, cache_tokens=None, max_requests=8, memory_fraction=0.6, cuda_graphs=True,
                  max_tokens_per_step=None, max_decode_graphs=16, fused_decode=None):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors`` ({file name: tensor}).
         ``cache_tokens``: capacity of every cache group in tokens (default: what ``memory_fraction`` of the

@@ -107,7 +107,7 @@ def test_scheduler_many_requests_few_pages(tiny, dtype):
     name, d, plain = tiny
     V = TINY[name]["vocab_size"]
     prompts = [random_tokens(n, V, seed=20 + i) for i, n in enumerate([5, 17, 33, 9, 40, 3, 26, 12])]
-    model = forge.Model(d, dtype=dtype, max_num_seqs=4, cache_tokens=160, max_tokens_per_step=24)
+    model = forge.Model(d, dtype=dtype, max_num_seqs=4, cache_tokens=160, max_tokens_per_step=24, block_size=16)
     alone = [model.generate(p, max_new_tokens=20, do_sample=False)["token_ids"] for p in prompts]
     sched = forge.RequestScheduler(model, max_num_seqs=4)
     ids = [sched.submit(p, max_new_tokens=20, sampler_config=forge.SamplerConfig(do_sample=False)) for p in prompts]
