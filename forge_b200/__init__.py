@@ -9,6 +9,7 @@ from .api import GenerateRequest, InferenceContext, Model, RequestScheduler, Req
 from .config import ConfigError, load_config, register_architecture, registered_architectures
 from .kernels import (profiler_disable, profiler_enable, profiler_enabled, profiler_print, profiler_reset,
                       profiler_summary)
+from .log import Logger
 from .weights import WeightError, write_random_model
 
 __version__ = "0.1.0"
@@ -16,4 +17,4 @@ __version__ = "0.1.0"
 __all__ = ["Model", "InferenceContext", "RequestScheduler", "SamplerConfig", "GenerateRequest", "RequestStatus",
            "ConfigError", "WeightError", "load_config", "register_architecture", "registered_architectures",
            "write_random_model", "profiler_enable", "profiler_disable", "profiler_enabled", "profiler_reset",
-           "profiler_summary", "profiler_print", "__version__"]
+           "profiler_summary", "profiler_print", "Logger", "__version__"]

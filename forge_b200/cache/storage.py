@@ -78,16 +78,17 @@ class CacheStorage:
         self.page_size, self.max_requests, self.dtype, self.device = page_size, max_requests, dtype, device
         self.layers = []
         self._state_tensors = []
+        self._guarded = []              # (what, whole allocation): one page (or row) of canary words before and after
         for i, spec in enumerate(cache_specs):
             if cache_from[i] is not None:
                 self.layers.append(None)       # filled below
                 continue
             if isinstance(spec, KVCacheSpec):
-                kv = torch.zeros((pages_per_group[self.layer_group[i]], 2, spec.num_kv_heads, page_size, spec.head_dim),
-                                 dtype=dtype, device=device)
+                kv = self._guarded_zeros(f"keys/values of run {i}", (pages_per_group[self.layer_group[i]], 2, spec.num_kv_heads,
+                                                                     page_size, spec.head_dim), dtype)
                 self.layers.append(LayerCache(self.layer_group[i], page_size, kv=kv))
             elif isinstance(spec, StateSpec):
-                st = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=device)
+                st = self._guarded_zeros(f"state of run {i}", (max_requests, *spec.shape), spec.dtype)
                 self._state_tensors.append(st)
                 self.layers.append(LayerCache(None, page_size, state=st))
             elif spec is None:
@@ -98,6 +99,27 @@ class CacheStorage:
             if src is not None:
                 s = self.layers[src]
                 self.layers[i] = LayerCache(s.group, page_size, kv=s.kv, state=s.state, writable=False)
+
+    # Canary words: every cache tensor is allocated with one more page (or state row) in front and one behind, filled
+    # with a fixed bit pattern that nothing ever writes.  A kernel that follows a page id of -1 or num_pages (or a slot
+    # past the pool) writes there instead of into a neighbour's memory, and check_canaries() says which tensor it was.
+    CANARY_BYTE = 0x5A
+
+    def _guarded_zeros(self, what, shape, dtype):
+        whole = torch.zeros((shape[0] + 2, *shape[1:]), dtype=dtype, device=self.device)
+        whole[0].view(torch.uint8).fill_(self.CANARY_BYTE)
+        whole[-1].view(torch.uint8).fill_(self.CANARY_BYTE)
+        self._guarded.append((what, whole))
+        return whole[1:-1]
+
+    def check_canaries(self):
+        """Names of the cache tensors whose guard words were overwritten (synchronises)."""
+        bad = []
+        for what, whole in self._guarded:
+            for edge, name in ((whole[0], "before"), (whole[-1], "behind")):
+                if not bool((edge.view(torch.uint8) == self.CANARY_BYTE).all()):
+                    bad.append(f"{what} (the guard {name} it)")
+        return bad
 
     def zero_state_slots(self, slots):
         """Clears the state rows of newly admitted requests."""

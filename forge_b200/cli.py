@@ -95,7 +95,9 @@ def main(argv=None):
             raise SystemExit(f"Error: option --{k[12:].replace('_', '-')} selects a feature this engine does not have")
     if a.interactive:
         raise SystemExit("Error: interactive chat is not part of this engine; give a prompt with -p")
-    from . import Model, load_config, write_random_model
+    from . import Logger, Model, load_config, write_random_model
+    if a.verbose:
+        Logger.set_level(3)
     from .config import config_from_dict
     model_dir = a.model
     if a.random_weights:

@@ -71,6 +71,9 @@ class ModelRunner:
             check_tensors("tensors", self.model.tensor_specs(), {n: (tuple(t.shape), t.dtype) for n, t in tensors.items()})
         self.model.load(tensors, where=str(model_dir or "tensors"))
         del tensors
+        from .. import log
+        log.info(f"model loaded: {type(config).__name__}, {len(self.plan.layers)} layers, hidden {self.plan.hidden_size}, "
+                 f"vocabulary {self.plan.vocab_size}, {self.dtype}")
 
         self.page_size, self.max_requests = int(page_size), int(max_requests)
         specs, cfrom = self.model.cache_specs(), self.model.cache_from()
@@ -246,6 +249,9 @@ class ModelRunner:
             if self.model._fused is not None:
                 self.model._fused[0].reset_after_error()
             raise
+        overrun = self.storage.check_canaries() + ([] if self.workspace.canary_intact() else ["the step workspace (behind it)"])
+        if overrun:
+            raise RuntimeError("canary words were overwritten, a kernel wrote outside its tensor: " + "; ".join(overrun))
         s = int(self.status.item())
         if s:
             self.status.zero_()

@@ -25,6 +25,7 @@ from dataclasses import dataclass, field
 from enum import Enum
 from typing import Callable, List, Optional
 
+from .. import log
 from ..cache import OutOfPages
 from ..sampling import RequestSampler, SamplerConfig
 from .batch import StepEntry
@@ -271,6 +272,11 @@ class RequestScheduler:
                 self._finish(r, RequestStatus.Failed, f"error:{type(e).__name__}")
             raise
         self.num_steps += 1
+        if log.Logger.enabled(log.DEBUG):
+            decodes = sum(1 for _, _, n, w in plan if n == 1 and w)
+            log.debug(f"step {self.num_steps}: {sum(n for _, _, n, _ in plan)} tokens ({decodes} decodes, {len(plan) - decodes} portions), "
+                      f"{len(self.active)} running, {len(self.waiting)} waiting, free pages {self.manager.num_free_pages()}, "
+                      f"{self.num_preemptions} preemptions, {'graph' if (ahead or decode_only) else 'eager'}")
         if self.num_steps % 256 == 0 and hasattr(self.runner, "check_status"):
             self.runner.check_status()                    # device error words, read now and then
         for r, start, n, wants in plan:
@@ -379,4 +385,5 @@ class RequestScheduler:
         r.status, r.current_pos = RequestStatus.Waiting, 0
         r.num_preemptions += 1
         self.num_preemptions += 1
+        log.info(f"request {rid} preempted ({len(r.output_tokens)} tokens generated so far): pages ran out")
         self.waiting.appendleft(rid)

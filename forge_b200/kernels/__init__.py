@@ -283,12 +283,20 @@ class StepWorkspace:
 
     ITEMSIZE = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.float16: 2, torch.int64: 8, torch.uint8: 1}
 
+    CANARY_BYTE = 0xA5
+
     def reserve(self, nbytes):
         nbytes = -(-int(nbytes) // self.ALIGN) * self.ALIGN
         if nbytes > self.capacity:
-            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            whole = torch.empty(nbytes + self.ALIGN, dtype=torch.uint8, device=self.device)
+            whole[nbytes:].fill_(self.CANARY_BYTE)              # canary words behind the buffer: nothing ever writes them
+            self._whole, self.buf = whole, whole[:nbytes]
             self.capacity = nbytes
             self.typed = {dt: self.buf.view(dt) for dt in self.ITEMSIZE}     # one view per element type to slice from
+
+    def canary_intact(self):
+        """False if a kernel wrote past the end of the buffer (synchronises)."""
+        return self.capacity == 0 or bool((self._whole[self.capacity:] == self.CANARY_BYTE).all())
 
     def step(self):
         return _OpenStep(self)

@@ -71,6 +71,7 @@ def _digest(files):
 
 
 def _say(msg):
+    # compilation takes seconds to a minute: said whatever the log level, so that a first call does not look hung
     print(f"[forge_b200] {msg}", file=sys.stderr, flush=True)
 
 

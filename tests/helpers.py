@@ -24,12 +24,19 @@ TINY = {
     "C": dict(architectures=["LlamaForCausalLM"], vocab_size=1000, hidden_size=512, intermediate_size=1408,
               num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64, rope_theta=20000.0,
               rms_norm_eps=1e-2, attention_bias=False, tie_word_embeddings=False, max_position_embeddings=1536),
+    # head size 128 with 7 query heads on one kv head and q/k/v bias (the Qwen2.5-7B kind of layer): the tcgen05 prompt
+    # attention with two blocks per head and tiles of 18 tokens = 126 rows, the projection whose epilogue rotates heads
+    # of 128, a q width (896) that is not the hidden width (448)
+    "D": dict(architectures=["Qwen2ForCausalLM"], vocab_size=777, hidden_size=448, intermediate_size=1216,
+              num_hidden_layers=2, num_attention_heads=7, num_key_value_heads=1, head_dim=128, rope_theta=1000000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1280),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 # weights are drawn so that attention is far from uniform and the logits are of order 10 at every width
 STDS = {"A": dict(std=0.12, embed_std=0.6, norm_std=0.15, bias_std=0.2),
         "B": dict(std=0.12, embed_std=0.6, norm_std=0.15, bias_std=0.2),
-        "C": dict(std=0.07, embed_std=0.6, norm_std=0.15, bias_std=0.2)}
+        "C": dict(std=0.07, embed_std=0.6, norm_std=0.15, bias_std=0.2),
+        "D": dict(std=0.07, embed_std=0.6, norm_std=0.15, bias_std=0.3)}
 
 # max |engine - plain| allowed, as a fraction of max |plain logits| of the compared rows.
 # float32: the engine rounds every product and sum to fp32 (the oracle is float64) and takes rotary

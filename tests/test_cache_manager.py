@@ -109,3 +109,23 @@ def test_random_orders_keep_every_page_accounted(seed, pages, page_size, window)
         m.free(rid)
     m.check()
     assert m.num_free_pages() == {"g": pages, "h": pages + 2}
+
+
+def test_canary_words_around_cache_tensors():
+    """Every cache tensor has a guard page in front and behind; a write there (what a kernel following page id -1 or
+    num_pages would do) is reported by name.  On the CPU: the storage is plain torch."""
+    import torch
+    from forge_b200.cache import CacheStorage
+    from forge_b200.parts.base import KVCacheSpec, StateSpec
+    st = CacheStorage([KVCacheSpec(2, 8), StateSpec((5,))], [None, None], page_size=4, pages_per_group=3, max_requests=2,
+                      dtype=torch.float32, device=torch.device("cpu"))
+    assert st.layers[0].kv.shape == (3, 2, 2, 4, 8) and st.layers[0].kv.is_contiguous() and not st.layers[0].kv.any()
+    assert st.check_canaries() == []
+    st.layers[0].kv[2, 1, 1, 3, 7] = 1.0                       # the last element inside: fine
+    assert st.check_canaries() == []
+    whole = st._guarded[0][1]
+    whole[4, 0, 0, 0, 0] = 3.0                                  # "page 3" of 3: the guard behind
+    assert st.check_canaries() == ["keys/values of run 0 (the guard behind it)"]
+    whole[4].view(torch.uint8).fill_(st.CANARY_BYTE)
+    st._guarded[1][1][0, 2] = 1.0                               # "slot -1" of the state rows
+    assert st.check_canaries() == ["state of run 1 (the guard before it)"]

@@ -17,10 +17,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
 # C: with 4 query heads per kv head a request brings 128 rows from 32 tokens on; its lengths lie on both sides
-LENGTHS = {"A": [70, 129, 33, 200, 64, 97], "B": [150, 47, 16, 240, 81], "C": [300, 20, 131, 700, 45, 257]}
+LENGTHS = {"A": [70, 129, 33, 200, 64, 97], "B": [150, 47, 16, 240, 81], "C": [300, 20, 131, 700, 45, 257],
+           "D": [210, 9, 95, 400, 37]}
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def tiny(request, tmp_path_factory):
     name = request.param
     d = make_model_dir(tmp_path_factory, name)
@@ -98,7 +99,7 @@ def test_page_size_does_not_matter(tiny, dtype):
 def test_long_decoding(tiny, dtype):
     """A 3-token prompt, then hundreds of tokens one by one."""
     name, d, plain, reqs, want = tiny
-    n = {"A": 400, "B": 520, "C": 330}[name]
+    n = {"A": 400, "B": 520, "C": 330, "D": 300}[name]
     toks = random_tokens(n, TINY[name]["vocab_size"], seed=77)
     ref = plain.logits(toks).float()
     runner = make_runner(d, dtype, -(-n // 16) * 16)

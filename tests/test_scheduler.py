@@ -267,3 +267,23 @@ def test_abort_while_a_step_is_in_flight():
     done = {x.request_id: x for x in s.run()}
     assert done[a].finish_reason == "aborted" and done[b].output_tokens == [31, 32, 33, 34, 35, 36]
     assert r.manager.num_free_pages("g") == 16
+
+
+def test_logger_gets_a_line_per_step_at_debug_level():
+    """forge.Logger in the reference's manner: levels 0..5, a Python sink; at debug the scheduler reports each step."""
+    import forge_b200 as forge
+    lines = []
+    forge.Logger.set_python_sink(lambda level, msg: lines.append((level, msg)))
+    forge.Logger.set_level(4)
+    try:
+        runner, sched = make(pages=64, budget=16)
+        sched.submit([1] * 20, max_new_tokens=3)
+        sched.run()
+    finally:
+        forge.Logger.set_level(2)
+        forge.Logger.reset_sink()
+    steps = [m for lv, m in lines if lv == 4 and m.startswith("step ")]
+    assert len(steps) == sched.num_steps and "16 tokens (0 decodes, 1 portions)" in steps[0] and "free pages" in steps[0]
+    assert forge.Logger.level() == 2
+    with pytest.raises(ValueError):
+        forge.Logger.set_level(9)
