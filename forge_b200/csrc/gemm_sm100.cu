@@ -43,7 +43,7 @@ struct GemmParams {
     int* status;
     int tma_out;        // fp32 results leave through shared memory and TMA stores / adds (the kernels that take a map of C)
     // EPI_QKV_ROPE: the product is a step's q, k, v; its epilogue rotates q and k and puts k and v into the paged cache
-    const float* rope_table;         // [M, head_dim / 2, 2] (cos, sin) of each row's position, or null: no rotation
+    const float* rope_table;         // [head_dim / 2, M, 2] (cos, sin) of each row's position, or null: no rotation
     const int32_t* slot_mapping;     // [M] page * page_size + offset of each row's token (negative or null: no cache write)
     __nv_bfloat16* kv_cache;         // [pages, 2, NKV, page_size, head_dim]
     int NH, NKV, head_dim, page_size;
@@ -142,7 +142,8 @@ __device__ __forceinline__ void qkv_rope_row(const GemmParams& p, uint32_t t_row
     const bool row_ok = m < p.M;
     int slot = (row_ok && p.slot_mapping && p.kv_cache) ? p.slot_mapping[m] : -1;
     if (slot >= 0 && !FORGE_SLOT_OK(slot)) slot = -1;             // (checks build) a slot outside the pool is not written
-    const float2* tab = p.rope_table ? reinterpret_cast<const float2*>(p.rope_table) + (size_t)(row_ok ? m : 0) * half : nullptr;
+    // pair d of row m is at tab[d * M]: the 32 rows of a warp read 256 consecutive bytes per pair
+    const float2* tab = p.rope_table ? reinterpret_cast<const float2*>(p.rope_table) + (row_ok ? m : 0) : nullptr;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += HD) {
         const int n = n0 + c0;
@@ -160,7 +161,7 @@ __device__ __forceinline__ void qkv_rope_row(const GemmParams& p, uint32_t t_row
         if (!is_v && tab) {
 #pragma unroll
             for (int d = 0; d < half; ++d) {
-                const float2 cs = __ldg(tab + d);
+                const float2 cs = __ldg(tab + (size_t)d * p.M);
                 const float x0 = v[d], x1 = v[d + half];
                 v[d] = x0 * cs.x - x1 * cs.y;
                 v[d + half] = x0 * cs.y + x1 * cs.x;
@@ -400,13 +401,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 constexpr int kPairBN = 256;                                   // N of the pair's tile; each CTA stages half of it
-struct PairCfg {
-    static constexpr int kBlockBytes = (BM + kPairBN / 2) * BK * 2;         // one k-block per CTA: 32 KB
-    static constexpr int kRingBlocks = 6;                                   // 192 KB of stages, whatever their size
+// PBN: the tile's N (256; 128 or 192 where narrower tiles fill the last wave better)
+template <int PBN> struct PairCfgT {
+    static constexpr int kBlockBytes = (BM + PBN / 2) * BK * 2;             // one k-block per CTA: 32 KB at 256
+    static constexpr int kRingBlocks = 6;                                   // 192 KB of stages at most, whatever their size
     static constexpr int kOutBytes = BM * 128;                              // a [128 rows x 32 fp32] box of results
     static constexpr int kSmemBytes = kRingBlocks * kBlockBytes + 1024 + 1024 + 2 * kOutBytes;
     static constexpr int kTmemCols = 512;
 };
+using PairCfg = PairCfgT<kPairBN>;
 
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
     uint32_t r;
@@ -440,13 +443,13 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int G>
+template <int G, int PBN = kPairBN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-    using C = PairCfg;
+    using C = PairCfgT<PBN>;
     constexpr int g = G > 0 ? G : 1;
-    constexpr int kStages = C::kRingBlocks / g, BNH = kPairBN / 2;
+    constexpr int kStages = C::kRingBlocks / g, BNH = PBN / 2;
     constexpr int kABytes = g * BM * BK * 2, kStageBytes = g * C::kBlockBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -463,7 +466,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles_n = (p.N + kPairBN - 1) / kPairBN;
+    const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles_n = (p.N + PBN - 1) / PBN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + BK - 1) / BK;
     const int num_groups = (num_kb + g - 1) / g;               // stages per tile; the last may hold fewer k-blocks
@@ -495,7 +498,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             bool ok = true;
             const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-                const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * kPairBN + rank * BNH;
+                const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * PBN + rank * BNH;
                 for (int gi = 0; gi < num_groups; ++gi, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -516,7 +519,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (the even CTA's)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * BM, kPairBN);
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * BM, PBN);
             uint32_t it = 0;
             bool ok = true;
             int local = 0;
@@ -525,7 +528,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const uint32_t aph = (local >> 1) & 1;
                 if (!(ok = mbar_wait(&acc_empty[a], aph ^ 1, abort, p.status))) break;
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + a * kPairBN;
+                const uint32_t d_tmem = tmem_base + a * PBN;
                 for (int gi = 0; gi < num_groups; ++gi, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -558,11 +561,11 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
             const int a = local & 1;
             const uint32_t aph = (local >> 1) & 1;
-            const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * kPairBN;
+            const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * PBN;
             if (!(ok = mbar_wait(&acc_full[a], aph, abort, p.status))) break;
             tc_fence_after_sync();
             const int m = m0 + row_in_tile;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kPairBN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * PBN;
             if (p.tma_out) {
                 // fp32 results: a chunk of 32 columns of all 128 rows goes to shared memory (the layout of a
                 // 128-byte-swizzled box) and from there to global memory with one TMA instruction, a store or
@@ -570,7 +573,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 // two buffers let a chunk be written while the previous one is read
                 const bool issuer = threadIdx.x == 64;
 #pragma unroll 1
-                for (int c = 0; c < kPairBN; c += 32) {
+                for (int c = 0; c < PBN; c += 32) {
                     if (n0 + c >= p.N) break;
                     uint8_t* buf = out_s + (out_chunk++ & 1) * C::kOutBytes;      // the buffers alternate across tiles too
                     uint32_t r[32];
@@ -595,13 +598,17 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         bulk_commit_group();
                     }
                 }
+            } else if (p.epilogue == EPI_QKV_ROPE) {
+                // whole heads per tile: rotated and rounded once, q to C, k and v into the cache
+                if (p.head_dim == 64) qkv_rope_row<PBN, 64>(p, t_row, m, n0);
+                else if constexpr (PBN % 128 == 0) qkv_rope_row<PBN, 128>(p, t_row, m, n0);
             } else {
 #pragma unroll 1
-                for (int c = 0; c < kPairBN; c += 32) {
+                for (int c = 0; c < PBN; c += 32) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(t_row + c, r);
                     tmem_ld_wait();
-                    store_row_chunk<kPairBN>(p, r, m, n0 + c);
+                    store_row_chunk<PBN>(p, r, m, n0 + c);
                 }
             }
             tc_fence_before_sync();
@@ -944,8 +951,9 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 }
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+constexpr int kStreamKThreads = 224;       // warps 0 and 6 load, 1 issues the MMAs, 2..5 are the epilogue
 template <int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kStreamKThreads, 1)
 gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                           const GemmParams p, const StreamKWork wk, const int kStages) {
     using C = StreamKCfg<NT>;
@@ -998,21 +1006,26 @@ gemm_sm100_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     const uint32_t tmem_base = *tmem_slot;
     forge::pdl_launch_dependents();
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
         if (lane == 0) {
+            // Two threads of different warps ask for the units in turn (warp 0 the even ones, warp 6 the odd ones):
+            // one thread's copies of 16 KB are taken one after the other and bring an SM less than its share of
+            // HBM when all SMs stream (measured on a [128256 x 4096] vocabulary, 8 rows: 188 us with one thread,
+            // 161 us = 6.5 TB/s with two; no difference where the matrix is small).
+            const int who = warp == 0 ? 0 : 1;
             // the weights do not depend on earlier kernels: the first ring of stages is requested before the wait
             const int n_units = u_end - u_begin;
             const int first = min(n_units, kStages);
-            for (int i = 0; i < first; ++i) {
+            for (int i = who; i < first; i += 2) {
                 const int u = unit_at(i);
                 mbar_arrive_expect_tx(&full[i], C::kStageBytes);
                 tma_load_2d(tiles + i * C::kStageBytes, &tmap_w, &full[i], (u % num_kb) * BK, (u / num_kb) * BM);
             }
             forge::pdl_wait();
-            for (int i = 0; i < first; ++i)
+            for (int i = who; i < first; i += 2)
                 tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_x, &full[i], (unit_at(i) % num_kb) * BK, 0);
             bool ok = true;
-            for (int i = first; i < n_units && ok; ++i) {
+            for (int i = first + ((first ^ who) & 1); i < n_units && ok; i += 2) {
                 const int s = i % kStages, u = unit_at(i);
                 if (!(ok = mbar_wait(&empty[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
                 mbar_arrive_expect_tx(&full[s], C::kStageBytes);
@@ -1201,9 +1214,11 @@ int resident_pairs() {
     return cached;
 }
 
-int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t stream) {
+template <int PBN>
+int launch_pair_width(const void* A, const void* W, const GemmParams& p, cudaStream_t stream) {
+    using C = PairCfgT<PBN>;
     const int pairs = resident_pairs();                 // also sets the kernels' shared-memory limit
-    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + kPairBN - 1) / kPairBN);
+    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + PBN - 1) / PBN);
     const int grid = 2 * (tiles < pairs ? tiles : pairs);
     const int num_kb = (p.K + BK - 1) / BK;
     const int group = p.K % BK != 0 ? 0 : (num_kb >= 2 ? 2 : 1);
@@ -1211,10 +1226,10 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
     const char* err = nullptr;
     if (group > 0) {
         if (!bf16_kblock_map(A, p.M, p.K, BM, group, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
-        if (!bf16_kblock_map(W, p.N, p.K, kPairBN / 2, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_kblock_map(W, p.N, p.K, PBN / 2, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
     } else {
         if (!bf16_tile_map(A, p.M, p.K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
-        if (!bf16_tile_map(W, p.N, p.K, kPairBN / 2, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_tile_map(W, p.N, p.K, PBN / 2, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
     }
     // fp32 results leave by TMA where a map of C can be made (16-byte aligned rows)
     GemmParams q = p;
@@ -1222,10 +1237,28 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
     q.tma_out = (p.epilogue == EPI_STORE_F32 || p.epilogue == EPI_ACCUM_F32) && p.N % 4 == 0 &&
                 (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && f32_tile_map(p.C, p.M, p.N, BM, &tc, &err);
     cudaError_t e;
-    if (group == 2) e = forge::launch(gemm_sm100_pair_kernel<2>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
-    else if (group == 1) e = forge::launch(gemm_sm100_pair_kernel<1>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
-    else e = forge::launch(gemm_sm100_pair_kernel<0>, dim3(grid), dim3(kThreads), PairCfg::kSmemBytes, stream, 2, ta, tw, tc, q);
+    if constexpr (PBN == kPairBN) {
+        if (group == 2) e = forge::launch(gemm_sm100_pair_kernel<2>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, 2, ta, tw, tc, q);
+        else if (group == 1) e = forge::launch(gemm_sm100_pair_kernel<1>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, 2, ta, tw, tc, q);
+        else e = forge::launch(gemm_sm100_pair_kernel<0>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, 2, ta, tw, tc, q);
+    } else {
+        // the narrower tiles exist for K in whole groups of two k-blocks only (the caller checks)
+        if (group != 2) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: tiles of %d columns need K %% 64 == 0 and K >= 128, got %d", PBN, p.K);
+        static forge::PerDeviceFlag configured_on;
+        bool& configured = configured_on.current();
+        if (!configured) {
+            cudaError_t a = cudaFuncSetAttribute(gemm_sm100_pair_kernel<2, PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+            if (a != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "gemm_sm100: cannot set %d bytes of shared memory: %s",
+                                                     C::kSmemBytes, cudaGetErrorString(a));
+            configured = true;
+        }
+        e = forge::launch(gemm_sm100_pair_kernel<2, PBN>, dim3(grid), dim3(kThreads), C::kSmemBytes, stream, 2, ta, tw, tc, q);
+    }
     return forge::check_launch("gemm_sm100 (two CTAs per tile)", e);
+}
+
+int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t stream) {
+    return launch_pair_width<kPairBN>(A, W, p, stream);
 }
 
 // k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps)
@@ -1299,7 +1332,7 @@ int launch_streamk(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParam
                    static_cast<int*>(g_workspace[dev].ptr), per_cta, max_parts};
     const int stages = per_cta < C::kStages ? per_cta : C::kStages;
     return forge::check_launch("gemm_sm100 (few rows, stream-K)",
-                               forge::launch(gemm_sm100_streamk_kernel<NT>, dim3(grid), dim3(kThreads),
+                               forge::launch(gemm_sm100_streamk_kernel<NT>, dim3(grid), dim3(kStreamKThreads),
                                              C::smem_bytes(stages), stream, 1, tw, tx, p, wk, stages));
 }
 
@@ -1467,12 +1500,12 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
 }
 
 // The fused projection of a prompt step: x [M, K] . [Wq; Wk; Wv]^T (+ bias), whose epilogue rotates q and k by the rows'
-// angles (rope_table [M, head_dim/2, 2] of (cos, sin); null: no rotation), writes q [M, NH*head_dim] in bf16 and puts k
+// angles (rope_table [head_dim/2, M, 2] of (cos, sin); null: no rotation), writes q [M, NH*head_dim] in bf16 and puts k
 // and v into the paged cache at slot_mapping (null or negative: not written).  Head sizes 64 and 128; for more than 128
 // rows (fewer go through forge_gemm_sm100 and the separate rotary kernel).
 extern "C" int forge_gemm_sm100_qkv_rope(const void* A, const void* W, const float* bias, void* q_out, void* kv_cache,
                                          const float* rope_table, const int32_t* slot_mapping, int* status, int M, int K,
-                                         int NH, int NKV, int head_dim, int page_size, cudaStream_t stream) {
+                                         int NH, int NKV, int head_dim, int page_size, int force_tile, cudaStream_t stream) {
     if (head_dim != 64 && head_dim != 128) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: head_dim %d (64 or 128)", head_dim);
     if (M <= BM) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: for more than %d rows, got %d", BM, M);
     if (K <= 0 || K % 8 != 0 || NH <= 0 || NKV <= 0 || page_size <= 0)
@@ -1484,22 +1517,38 @@ extern "C" int forge_gemm_sm100_qkv_rope(const void* A, const void* W, const flo
         if (g_num_sms <= 0) g_num_sms = 148;
     }
     const int N = (NH + 2 * NKV) * head_dim;
-    // tiles hold whole heads: 128 or 256 columns, whichever wastes less of the last wave (the cost model of forge_gemm_sm100)
+    // Tiles hold whole heads.  One CTA per tile of 128 or 256 columns, or a pair of CTAs on [256 x 128, 192 or 256]:
+    // whichever needs the fewest clocks for its rounds of tiles.  Clocks per k-step of a tile, measured over prompts of
+    // 512 to 4,096 rows: a single CTA is bound by shared-memory traffic at about 64 + width / 2 (133 and 188), a pair
+    // takes 123, 128 and 174 for 128, 192 and 256 columns (about 0.68 per column with a floor of 123).
+    // `force_tile` (tests and measurements): 0 = choose, 128 / 256 = one CTA, 1128 / 1192 / 1256 = a pair.
     const long tm = (M + BM - 1) / BM, ksteps = (K + UMMA_K - 1) / UMMA_K;
-    int bn = 128;
+    const long tm2 = (M + 2 * BM - 1) / (2 * BM), pairs = resident_pairs();
+    const bool pair_ok = K % BK == 0 && K >= 2 * BK;
+    int choice = 128;
     long best = -1;
-    for (int cand : {256, 128}) {
-        const long tiles = tm * ((N + cand - 1) / cand);
-        const long cost = ((tiles + g_num_sms - 1) / g_num_sms) * ksteps * (64 + cand / 2) + 36L * cand;
-        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    for (int cand : {256, 128, 1256, 1192, 1128}) {
+        const bool pair = cand > 1000;
+        const int width = pair ? cand - 1000 : cand;
+        if (pair && (!pair_ok || width % head_dim != 0)) continue;
+        if (force_tile != 0 && cand != force_tile) continue;
+        const long tiles = (pair ? tm2 : tm) * ((N + width - 1) / width);
+        const long waves = pair ? (tiles + pairs - 1) / pairs : (tiles + g_num_sms - 1) / g_num_sms;
+        const long per_kstep = pair ? (17L * width / 25 > 123 ? 17L * width / 25 : 123) : 64 + width / 2;
+        const long cost = waves * ksteps * per_kstep + 36L * width;
+        if (best < 0 || cost < best) { best = cost; choice = cand; }
     }
+    if (best < 0) return forge::fail(FORGE_ERR_ARG, "gemm_sm100_qkv_rope: tile %d is not available for these sizes", force_tile);
+    GemmParams p{q_out, bias, M, N, K, EPI_QKV_ROPE, status, 0, rope_table, slot_mapping, static_cast<__nv_bfloat16*>(kv_cache),
+                 NH, NKV, head_dim, page_size};
+    if (choice == 1256) return launch_pair_width<256>(A, W, p, stream);
+    if (choice == 1192) return launch_pair_width<192>(A, W, p, stream);
+    if (choice == 1128) return launch_pair_width<128>(A, W, p, stream);
     const char* err = nullptr;
     CUtensorMap ta, tw;
     if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: A: %s", err);
-    if (!bf16_tile_map(W, N, K, bn, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: W: %s", err);
-    GemmParams p{q_out, bias, M, N, K, EPI_QKV_ROPE, status, 0, rope_table, slot_mapping, static_cast<__nv_bfloat16*>(kv_cache),
-                 NH, NKV, head_dim, page_size};
-    return bn == 256 ? launch<256>(ta, tw, p, stream) : launch<128>(ta, tw, p, stream);
+    if (!bf16_tile_map(W, N, K, choice, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100_qkv_rope: W: %s", err);
+    return choice == 256 ? launch<256>(ta, tw, p, stream) : launch<128>(ta, tw, p, stream);
 }
 
 // (checks build) the bounds that this library's projection tests slots against

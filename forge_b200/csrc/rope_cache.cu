@@ -14,13 +14,15 @@
 namespace {
 
 // cos/sin of every (token, pair) of a step: the angles depend on the position and the pair only, so one small
-// kernel per step serves every head of every layer.  table[t, d] = (cos, sin) of positions[t] / theta^(2d/HD).
-__global__ void rope_table_kernel(const int32_t* __restrict__ positions, float2* __restrict__ table, int T, int HD, float theta) {
+// kernel per step serves every head of every layer.  table[t, d] = (cos, sin) of positions[t] / theta^(2d/HD); with
+// `by_pair` the table is laid out [d, t] instead, for a reader whose neighbouring threads hold neighbouring tokens.
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, float2* __restrict__ table, int T, int HD, float theta,
+                                  int by_pair) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, half = HD >> 1;
     if (i >= T * half) return;
-    const int t = i / half, d = i % half;
+    const int t = by_pair ? i % T : i / half, d = by_pair ? i / T : i % half;
     const float freq = 1.0f / powf(theta, (2.0f * (float)d) / (float)HD);
     float s, c;
     sincosf((float)positions[t] * freq, &s, &c);
@@ -133,13 +135,13 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const int32_t* __restric
 
 }  // namespace
 
-// table: float [T, HD/2, 2] (cos, sin) for the step's tokens.
-extern "C" int forge_rope_table(const int32_t* positions, float* table, int T, int HD, float theta, cudaStream_t stream) {
+// table: float [T, HD/2, 2] (cos, sin) for the step's tokens; by_pair != 0: [HD/2, T, 2].
+extern "C" int forge_rope_table(const int32_t* positions, float* table, int T, int HD, float theta, int by_pair, cudaStream_t stream) {
     if (T < 0 || HD <= 0 || (HD & 1)) return forge::fail(FORGE_ERR_ARG, "rope_table: bad sizes T=%d HD=%d", T, HD);
     if (T == 0) return FORGE_OK;
     const long n = (long)T * (HD / 2);
     return forge::check_launch("rope_table", forge::launch(rope_table_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0,
-                                                           stream, 1, positions, reinterpret_cast<float2*>(table), T, HD, theta));
+                                                           stream, 1, positions, reinterpret_cast<float2*>(table), T, HD, theta, by_pair));
 }
 
 // table: optional cos/sin table from forge_rope_table for the same positions, HD and theta (null: compute here).

@@ -35,7 +35,7 @@ _SIGNATURES = {
         "forge_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
         "forge_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "forge_rope_kv_write": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
-        "forge_rope_table": [_P, _P, _I, _I, _F, _P],
+        "forge_rope_table": [_P, _P, _I, _I, _F, _I, _P],
         "forge_silu_mul_interleaved": [_P, _P, _I, _I, _I, _P],
         "forge_gemm_simt": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "forge_paged_attention_simt": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
@@ -46,7 +46,7 @@ _SIGNATURES = {
     "gemm_sm100": {
         "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "forge_gemm_sm100_set_workspace": [_P, ctypes.c_longlong],
-        "forge_gemm_sm100_qkv_rope": [_P] * 8 + [_I] * 6 + [_P],
+        "forge_gemm_sm100_qkv_rope": [_P] * 8 + [_I] * 7 + [_P],
     },
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
@@ -414,14 +414,17 @@ def rmsnorm(x, weight, eps, out_dtype, rows=None, out=None):
     return out
 
 
-def rope_table(positions, head_dim, theta):
+def rope_table(positions, head_dim, theta, by_pair=False):
     """float32 [T, head_dim/2, 2]: (cos, sin) of position / theta^(2d/head_dim) for the step's tokens; computed once
-    per step and shared by every head of every layer with the same head size and base."""
+    per step and shared by every head of every layer with the same head size and base.  ``by_pair``: laid out
+    [head_dim/2, T, 2] instead, which is what the projection whose epilogue rotates reads (a thread per token there,
+    so neighbouring threads read neighbouring tokens of one pair)."""
     lib = library("core")
     T = positions.numel()
-    table = new_tensor((T, head_dim // 2, 2), torch.float32, positions.device, whole_step=True)
+    shape = (head_dim // 2, T, 2) if by_pair else (T, head_dim // 2, 2)
+    table = new_tensor(shape, torch.float32, positions.device, whole_step=True)
     _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
-                                     float(theta), _stream()), "rope_table")
+                                     float(theta), 1 if by_pair else 0, _stream()), "rope_table")
     return table
 
 
@@ -844,10 +847,12 @@ def gemm_sm100_qkv_rope_supports(rows, head_dim, k):
     return _TENSOR_CORE_GEMM and rows > 128 and head_dim in (64, 128) and k % 8 == 0
 
 
-def gemm_sm100_qkv_rope(x, w, bias, rope_table, slot_mapping, kv_cache, n_heads, n_kv_heads, head_dim, page_size, q_out=None):
+def gemm_sm100_qkv_rope(x, w, bias, rope_table, slot_mapping, kv_cache, n_heads, n_kv_heads, head_dim, page_size, q_out=None,
+                        tile=0):
     """bf16 x [M,K] . w [(NH+2NKV)*HD, K]^T (+ bias) on the tensor cores; the epilogue rotates q and k by ``rope_table``
-    (fp32 [M, HD/2, 2] of (cos, sin); None: no rotation), returns q bf16 [M, NH*HD] and writes k and v into ``kv_cache``
-    at ``slot_mapping`` (None: not written).  The fp32 product never reaches global memory."""
+    (fp32 [HD/2, M, 2] of (cos, sin), ``rope_table(..., by_pair=True)``; None: no rotation), returns q bf16 [M, NH*HD] and writes k and v into ``kv_cache``
+    at ``slot_mapping`` (None: not written).  The fp32 product never reaches global memory.  ``tile``: 0 lets the
+    library choose; 128 / 256 one CTA per tile of that width, 1128 / 1192 / 1256 a pair of CTAs on 256 rows of it."""
     lib = library("gemm_sm100")
     (M, K), (N, K2) = x.shape, w.shape
     if K != K2 or N != (n_heads + 2 * n_kv_heads) * head_dim:
@@ -860,7 +865,7 @@ def gemm_sm100_qkv_rope(x, w, bias, rope_table, slot_mapping, kv_cache, n_heads,
         _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _opt(bias, "bias", torch.float32),
         _need(q_out, "q_out", torch.bfloat16, 2), _opt(kv_cache, "kv_cache", torch.bfloat16), _opt(rope_table, "rope_table", torch.float32),
         _opt(slot_mapping, "slot_mapping", torch.int32), _need(_gemm_status(x.device), "status", torch.int32), M, K, n_heads,
-        n_kv_heads, head_dim, page_size, _stream()), "gemm_sm100_qkv_rope")
+        n_kv_heads, head_dim, page_size, tile, _stream()), "gemm_sm100_qkv_rope")
     return q_out
 
 

@@ -27,25 +27,26 @@ class RotaryEmbedding(Part):
             return None
         return {"theta": self.theta, "rotary": self.rotary}
 
-    def _table(self, positions, batch):
+    def _table(self, positions, batch, by_pair=False):
         """The step's cos/sin table, computed once per step (kept in the batch's ``attention_plan``), not once per
         layer.  A batch that a CUDA graph replays keeps no table: the table of the captured step would be replayed
-        with every later step's positions."""
+        with every later step's positions.  ``by_pair``: the layout [head_dim/2, tokens, 2] that the fused projection
+        reads."""
         if not self.rotary or batch is None or getattr(batch, "decode_only", False):
             return None
-        key = ("rope", self.head_dim, self.theta, positions.data_ptr())
+        key = ("rope", self.head_dim, self.theta, positions.data_ptr(), by_pair)
         table = batch.attention_plan.get(key)
         if table is None:
-            table = batch.attention_plan[key] = kernels.rope_table(positions, self.head_dim, self.theta)
+            table = batch.attention_plan[key] = kernels.rope_table(positions, self.head_dim, self.theta, by_pair=by_pair)
         return table
 
     def fused_projection(self, positions, batch):
         """For the q/k/v product whose epilogue encodes and stores by itself (prompt portions): {"table": the step's
-        (cos, sin) table or None for no rotation}, or None if this part does not offer it.  As with ``fused_decode``
-        only the stock classes do: that epilogue computes the half-split rotation of the whole head."""
+        (cos, sin) table by pair, or None for no rotation}, or None if this part does not offer it.  As with
+        ``fused_decode`` only the stock classes do: that epilogue computes the half-split rotation of the whole head."""
         if type(self) not in (RotaryEmbedding, NoPosition) or batch is None or getattr(batch, "decode_only", False):
             return None
-        return {"table": self._table(positions, batch)}
+        return {"table": self._table(positions, batch, by_pair=True)}
 
     def encode_and_store(self, qkv, positions, slot_mapping, kv_cache, num_heads, num_kv_heads, page_size, batch=None):
         """``batch`` (optional): the step's batch, which keeps the step's table of angles."""

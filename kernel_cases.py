@@ -74,7 +74,7 @@ def case(name):
     if name == "gemm_prefill_qkv_rope":      # 2048 tokens x [2560, 2048]; the epilogue rotates q, k and writes q (bf16) and the cache
         x, w = _bf16(2048, H), _bf16((NH + 2 * NKV) * HD, H, scale=0.02)
         pos = torch.arange(2048, dtype=torch.int32, device=DEV)
-        table, kv = rope_table(pos, HD, 1e4), _bf16(2048 // PS, 2, NKV, PS, HD)
+        table, kv = rope_table(pos, HD, 1e4, by_pair=True), _bf16(2048 // PS, 2, NKV, PS, HD)
         return (lambda: gemm_sm100_qkv_rope(x, w, None, table, pos, kv, NH, NKV, HD, PS)), \
             (x.numel() + w.numel()) * 2 + 2048 * w.shape[0] * 2, 2 * 2048 * w.numel()
     if name == "attention_prefill_mma":      # the same through the mma.sync kernel, for comparison

@@ -187,9 +187,17 @@ def test_projection_whose_epilogue_rotates_and_stores(M, K, nh, nkv, hd, ps, bia
     q_ref, cache_ref = R.rope_kv_write_ref(qkv, positions, slots, cache0, nh, nkv, hd, ps, 10000.0, rotary)
     dev = "cuda:0"
     cache = cache0.clone().to(dev)
-    table = k.rope_table(positions.to(dev), hd, 10000.0) if rotary else None
-    q = k.gemm_sm100_qkv_rope(x.to(dev), w.to(dev), None if b is None else b.to(dev), table, slots.to(dev), cache, nh, nkv, hd, ps)
-    k.check_kernel_status()
-    assert (q.float().cpu() - q_ref).abs().max() <= 2e-2 * q_ref.abs().max()
-    assert (cache.float().cpu() - cache_ref).abs().max() <= 2e-2 * cache_ref.abs().max()
-    assert torch.equal(cache.cpu()[cache_ref == cache0.float()], cache0[cache_ref == cache0.float()])
+    table = k.rope_table(positions.to(dev), hd, 10000.0, by_pair=True) if rotary else None
+    # the library's own choice, then every tile it has: one CTA on 128 or 256 columns, a pair of CTAs on 128, 192 or 256
+    for tile in (0, 128, 256, 1128, 1192, 1256):
+        cache = cache0.clone().to(dev)
+        args = (x.to(dev), w.to(dev), None if b is None else b.to(dev), table, slots.to(dev), cache, nh, nkv, hd, ps)
+        if tile == 1192 and hd == 128:
+            with pytest.raises(k.KernelError, match="not available"):      # 192 columns are no whole heads of 128
+                k.gemm_sm100_qkv_rope(*args, tile=tile)
+            continue
+        q = k.gemm_sm100_qkv_rope(*args, tile=tile)
+        k.check_kernel_status()
+        assert (q.float().cpu() - q_ref).abs().max() <= 2e-2 * q_ref.abs().max(), tile
+        assert (cache.float().cpu() - cache_ref).abs().max() <= 2e-2 * cache_ref.abs().max(), tile
+        assert torch.equal(cache.cpu()[cache_ref == cache0.float()], cache0[cache_ref == cache0.float()]), tile
