@@ -284,57 +284,88 @@ paged_attention_mma_kernel(const AttnParams p) {
     }
 }
 
-// One warp per (tile, kv head, row): combines the slices' partial results in a fixed order.
-__global__ void __launch_bounds__(128)
+// One CTA of 1 to 8 warps per (tile, kv head, row) and 32 columns of the head: combines the slices' partial results.
+// The slices are dealt to the CTA's threads (thread t takes slices t, t + threads, ...: with hundreds of slices, a
+// long context spread over the whole GPU, a single warp walking them one after the other took 40 us).  A thread asks
+// for its first slice's maximum, sum AND 32 columns at once, before the row's reference maximum is known (only the
+// weights need it), so the kernel is one trip to L2 and two meetings of the CTA.  Every thread adds its slices'
+// weighted results in index order, the lanes of a warp are summed by a butterfly and the warps in warp order: the
+// order of additions is fixed, so the result does not depend on timing.
+constexpr int kMergeWarps = 8;
+__global__ void __launch_bounds__(32 * kMergeWarps)
 attention_merge_kernel(const AttnParams p, int num_tiles) {
     forge::pdl_launch_dependents();
     forge::pdl_wait();
+    __shared__ float red_m[kMergeWarps], red_l[kMergeWarps], red_o[kMergeWarps][32];
     const int G = p.NH / p.NKV;
-    const int gw = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    const int PR = p.part_rows;
-    if (gw >= num_tiles * p.NKV * PR) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5, threads = blockDim.x;
+    const int PR = p.part_rows, S = p.num_splits;
+    const int gw = blockIdx.x, c0 = blockIdx.y * 32;             // gw < num_tiles * NKV * PR by the launch
     const int row = gw % PR, kvh = (gw / PR) % p.NKV, tile = gw / (PR * p.NKV);
     const int s = p.tile_req[tile], row0 = p.tile_row0[tile];
     const int qs0 = p.q_start[s], qlen = p.q_start[s + 1] - qs0;
-    if (row0 + row >= qlen * G) return;
-    const size_t slot0 = ((size_t)tile * p.NKV + kvh) * p.num_splits;
-    // pass 1: the slices' running maxima and sums, 32 slices at a time across the lanes
-    float M = -INFINITY;
-    for (int z = lane; z < p.num_splits; z += 32) M = fmaxf(M, p.part_ml[((slot0 + z) * PR + row) * 2]);
+    if (tile >= num_tiles || row0 + row >= qlen * G) return;     // the same for every thread of the CTA
+    const size_t slot0 = ((size_t)tile * p.NKV + kvh) * S;
+    const float* ml = p.part_ml + (slot0 * PR + row) * 2;        // slice z: ml[z * PR * 2], + 1
+    const float* po = p.part_o + (slot0 * PR + row) * HD + c0;   // slice z: po[z * PR * HD]
+    // columns c0 .. c0 + 31 of slice z (the head size is a multiple of 16: whole float4s); a slice without a visible
+    // key (maximum -inf) never wrote its partial result and counts as zeros
+    auto load_cols = [&](int z, float m_z, float4 (&v)[8]) {
+        const float4* src = reinterpret_cast<const float4*>(po + (size_t)z * PR * HD);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v[i] = (m_z != -INFINITY && c0 + 4 * i < HD) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    const int z_first = threadIdx.x;
+    float m_first = -INFINITY, l_first = 0.f;
+    float4 v_first[8];
+    if (z_first < S) {
+        m_first = ml[(size_t)z_first * PR * 2];
+        l_first = ml[(size_t)z_first * PR * 2 + 1];
+    }
+    load_cols(z_first < S ? z_first : 0, m_first, v_first);
+    // the row's reference: the largest of the slices' running maxima
+    float M = m_first;
+    for (int z = z_first + threads; z < S; z += threads) M = fmaxf(M, ml[(size_t)z * PR * 2]);
     M = forge::warp_max(M);
-    float L = 0.f;
-    float acc[(HD + 31) / 32];
+    if (lane == 0) red_m[warp] = M;
+    __syncthreads();
+    M = red_m[0];
+    for (int w = 1; w < warps; ++w) M = fmaxf(M, red_m[w]);
+    float acc[32];
+    const float w_first = m_first == -INFINITY ? 0.f : exp2f(m_first - M);
+    float L = w_first * l_first;
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
-    // pass 2: slices in index order (a fixed order of additions); the loads of different slices are independent
-    for (int z0 = 0; z0 < p.num_splits; z0 += 32) {
-        const int zl = z0 + lane;
-        float m_l = -INFINITY, l_l = 0.f;
-        if (zl < p.num_splits) {
-            m_l = p.part_ml[((slot0 + zl) * PR + row) * 2];
-            l_l = p.part_ml[((slot0 + zl) * PR + row) * 2 + 1];
-        }
-        const float w_l = m_l == -INFINITY ? 0.f : exp2f(m_l - M);      // a slice without a visible key weighs 0
-        const int nz = min(32, p.num_splits - z0);
-        for (int zz = 0; zz < nz; ++zz) {
-            const float w = __shfl_sync(0xffffffffu, w_l, zz);
-            L += w * __shfl_sync(0xffffffffu, l_l, zz);
-            if (w == 0.f) continue;
-            const float* po = p.part_o + ((slot0 + z0 + zz) * PR + row) * HD;
+    for (int i = 0; i < 8; ++i) {
+        acc[4 * i] = w_first * v_first[i].x; acc[4 * i + 1] = w_first * v_first[i].y;
+        acc[4 * i + 2] = w_first * v_first[i].z; acc[4 * i + 3] = w_first * v_first[i].w;
+    }
+    for (int z = z_first + threads; z < S; z += threads) {       // more slices than threads: the rest, in index order
+        const float m_z = ml[(size_t)z * PR * 2];
+        if (m_z == -INFINITY) continue;
+        const float w = exp2f(m_z - M);
+        L += w * ml[(size_t)z * PR * 2 + 1];
+        float4 v[8];
+        load_cols(z, m_z, v);
 #pragma unroll
-            for (int i = 0; i < (HD + 31) / 32; ++i) {
-                const int d = lane + 32 * i;
-                if (d < HD) acc[i] += w * po[d];
-            }
+        for (int i = 0; i < 8; ++i) {
+            acc[4 * i] += w * v[i].x; acc[4 * i + 1] += w * v[i].y; acc[4 * i + 2] += w * v[i].z; acc[4 * i + 3] += w * v[i].w;
         }
     }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
-    const int r = row0 + row;
-    __nv_bfloat16* o = p.out + (size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD;
+    L = forge::warp_sum(L);
+    if (lane == 0) red_l[warp] = L;
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < HD) o[d] = __float2bfloat16_rn(acc[i] * inv);
+    for (int i = 0; i < 32; ++i) {
+        const float t = forge::warp_sum(acc[i]);
+        if (lane == i) red_o[warp][i] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32 && c0 + threadIdx.x < HD) {
+        float Lsum = red_l[0], v = red_o[0][threadIdx.x];
+        for (int w = 1; w < warps; ++w) { Lsum += red_l[w]; v += red_o[w][threadIdx.x]; }
+        const float inv = Lsum > 0.f ? 1.0f / Lsum : 0.f;
+        const int r = row0 + row;
+        p.out[(size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD + c0 + threadIdx.x] = __float2bfloat16_rn(v * inv);
     }
 }
 
@@ -667,8 +698,10 @@ extern "C" int forge_paged_attention_mma(const void* q, const void* kv, void* ou
                            dim3(32 * ((max_rows + 15) / 16)), smem_big, stream, 1, p);
     int rc = forge::check_launch("paged_attention_mma", le);
     if (rc != FORGE_OK || num_splits == 1) return rc;
-    const long warps = (long)num_tiles * NKV * p.part_rows;
-    return forge::check_launch("attention_merge", forge::launch(attention_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, 1, p, num_tiles));
+    const long rows = (long)num_tiles * NKV * p.part_rows;
+    const int merge_warps = num_splits >= 32 * kMergeWarps ? kMergeWarps : (num_splits + 31) / 32;     // a thread per slice, up to eight warps
+    return forge::check_launch("attention_merge", forge::launch(attention_merge_kernel, dim3((unsigned)rows, (HD + 31) / 32),
+                                                                dim3(32 * merge_warps), 0, stream, 1, p, num_tiles));
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -67,6 +67,24 @@ def test_decode_tokens_with_sliced_keys(nh, nkv, hd, ps, splits):
     assert (auto - ref).abs().max() <= 1e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 4, 64, 16), (6, 2, 80, 16), (2, 1, 256, 64), (4, 4, 16, 16)])
+@pytest.mark.parametrize("splits", [40, 150, 300])
+def test_long_contexts_in_many_slices(nh, nkv, hd, ps, splits):
+    """Hundreds of slices per request (a long context spread over the whole GPU): the merge deals them to the threads
+    of a CTA, one to four warps; short requests leave most slices without a key; one far key carries the weight."""
+    from forge_b200 import kernels as k
+    reqs = [(5000, 1), (9000, 1), (100, 1), (0, 1)]
+    q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=6)
+    far = 4321
+    page = int(group.block_table[1, far // ps])
+    cache[page, 0, 0, far % ps, :] = (q[1, :hd].float() * 4.0).to(torch.bfloat16)
+    ref = R.paged_attention_ref(q, cache, group.block_table, tok_req, positions, nh, nkv, hd, ps)
+    got = k.paged_attention_mma(q, cache, group, batch, nh, nkv, hd, ps, num_splits=splits).float()
+    k.check_kernel_status()
+    err = (got - ref).abs().amax(dim=1)
+    assert float(err.max()) <= 1e-2 * float(ref.abs().max()), err.tolist()
+
+
 def test_far_key_and_page_edges():
     """One early key gets nearly all the weight of the last query; contexts end exactly on, one before and
     one after a page's edge and a key tile's edge."""
