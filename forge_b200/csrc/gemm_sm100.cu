@@ -703,7 +703,8 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     const uint32_t rank = cluster_ctarank();
     const int n0 = (blockIdx.x / ksplit) * BM;
     const int num_kb = (p.K + BK - 1) / BK;
-    const int kb_per = ((num_kb + ksplit - 1) / ksplit + g - 1) / g * g;      // whole groups per CTA
+    // a CTA's last group may reach into the next CTA's k-blocks: those bytes are loaded and not multiplied
+    const int kb_per = (num_kb + ksplit - 1) / ksplit;
     const int kb_begin = rank * kb_per, kb_end = min(kb_begin + kb_per, num_kb);
     const int my_kb = max(kb_end - kb_begin, 0);
     const int my_groups = (my_kb + g - 1) / g;
@@ -862,14 +863,14 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     cluster_sync_all();                       // every CTA's partial is in place and visible
 
     if (warp >= 2 && warp < 6 && !direct) {
-        // this CTA owns rows [rank * rows_per, +rows_per) of the tile: add the partials in rank order, four
+        // this CTA owns a share of the tile's rows: add the partials in rank order, four
         // adjacent rows (16 bytes of each peer's shared memory) per thread
-        const int rows_per = BM / ksplit;                  // 16, 32 or 64
-        const int groups = rows_per / 4;
+        // (the tile's 32 groups of four rows are dealt out as evenly as the cluster's size allows)
+        const int group0 = (int)rank * (BM / 4) / ksplit, groups = ((int)rank + 1) * (BM / 4) / ksplit - group0;
         const int t = threadIdx.x - 64;                    // 0..127
         const uint32_t partial_addr = smem_u32(partial);
         for (int idx = t; idx < p.M * groups; idx += 128) {
-            const int m = idx / groups, nl = rank * rows_per + 4 * (idx % groups);
+            const int m = idx / groups, nl = 4 * (group0 + idx % groups);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int q = 0; q < ksplit; ++q) {
                 const float4 v = ld_dsmem_f32x4(partial_addr + (m * BM + nl) * 4, q);
@@ -1261,11 +1262,18 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
     return launch_pair_width<kPairBN>(A, W, p, stream);
 }
 
-// k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps)
+// k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps).  The group
+// that loads the fewest k-blocks beyond the CTA's own (its last group is whole all the same), the larger one of equals;
+// at least two per instruction where there are two (one 16 KB box per instruction is bound by the instruction rate).
 int few_rows_group(int K, int kb_per, int max_group) {
     if (K % BK != 0) return 0;
-    const int g = kb_per < max_group ? kb_per : max_group;
-    return g < 1 ? 1 : g;
+    if (kb_per <= max_group) return kb_per < 1 ? 1 : kb_per;
+    int best = max_group, best_waste = (kb_per + max_group - 1) / max_group * max_group - kb_per;
+    for (int g = max_group - 1; g >= 2; --g) {
+        const int waste = (kb_per + g - 1) / g * g - kb_per;
+        if (waste < best_waste) { best = g; best_waste = waste; }
+    }
+    return best;
 }
 
 template <int NT>
@@ -1381,7 +1389,7 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
 // tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; 512 (M > 128) = a pair
-// of CTAs on a [256 x 256] tile (cta_group::2); -1, -2, -4, -8 (M <= 128 only) =
+// of CTAs on a [256 x 256] tile (cta_group::2); -1 .. -8 (M <= 128 only) =
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
@@ -1427,12 +1435,14 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         int ksplit = 1;
         if (tile_n < 0) {
             ksplit = -tile_n;
-            if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
-                return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1, 2, 4 or 8, got %d", ksplit);
+            if (ksplit < 1 || ksplit > 8)
+                return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1 to 8, got %d", ksplit);
         } else {
             // The widest cluster whose CTAs all run at once (a second wave doubles the time) and still have a
             // group of four k-blocks each.  An SM's tensor core takes W from shared memory at about 100 GB/s
             // (the M operand of an N = 16 MMA), so it takes some 64 streaming SMs to keep up with HBM.
+            // (clusters of 3, 5, 6 and 7 work too but measured no faster than the next power of two below them:
+            // [2560 x 2048] 4.5 us with 4 CTAs, 5.2 with 6; [2048 x 5632] 7.7 and 7.4; 7 fit too few at once)
             for (int ks = 2; ks <= 8; ks *= 2)
                 if (tiles_n * ks <= max_resident_ctas(ks) && num_kb / ks >= 4) ksplit = ks;
         }

@@ -116,10 +116,10 @@ def test_two_ctas_on_one_tile(M, N, K):
 
 @pytest.mark.parametrize("M", [1, 8, 16, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
-@pytest.mark.parametrize("cluster", [0, -1, -2, -4, -8, -100])
+@pytest.mark.parametrize("cluster", [0, -1, -2, -3, -4, -5, -6, -7, -8, -100])
 def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
     """The decode-shaped kernels (weights as the MMA's M operand) for every epilogue: K cut over a cluster of
-    1/2/4/8 CTAs with partial sums added through distributed shared memory, and (-100) units of work dealt
+    1 to 8 CTAs with partial sums added through distributed shared memory, and (-100) units of work dealt
     out evenly to persistent CTAs with partial sums added through a workspace."""
     k = _k()
     a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
