@@ -273,6 +273,10 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                 const int b = it & 1;
                 if (!(ok = mbar_wait<true>(&k_full[kst], kph, abort, p.status, 3))) break;
                 if (it >= 2 && !(ok = mbar_wait<true>(&s_free[b], ((it - 2) >> 1) & 1, abort, p.status, 11))) break;
+                // P V of tile it - 2 has read its P buffer before these scores exist: the rows, who wait for the
+                // scores, then need no probe of their own before they overwrite that buffer (a probe costs them
+                // some 200 clocks of their dependent chain; this thread has the time)
+                if (it >= 2 && !(ok = mbar_wait<true>(&o_done[b], ((it - 2) >> 1) & 1, abort, p.status, 10))) break;
                 tc_fence_after_sync();
                 const uint32_t ka = k_addr + kst * kKVBytes;
 #pragma unroll
@@ -354,8 +358,8 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                 }
                 tmem_st_wait();
             }
-            // this P buffer was read by P V of the tile before the previous one
-            if (it > 1 && !(ok = mbar_wait<true>(&o_done[b], ((it - 2) >> 1) & 1, abort, p.status, 10))) break;
+            // (this P buffer was read by P V of the tile before the previous one: the thread that issued this
+            // tile's Q K^T waited for that)
             // pass 2: weights (exp2 of -inf is 0), their sum, and P in the MMA's shared-memory layout
             // (16-byte chunk ^ row % 8)
             const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), nref2 = pack_f32x2(-ref, -ref);
