@@ -653,17 +653,18 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 // two accumulators (always in the same order).
 constexpr int kSkinnyThreads = 224;
 template <int NT> struct SkinnyCfg {                       // NT: token box (UMMA N) = 16, 32 or 64
-    static constexpr int kBlockBytes = BM * BK * 2 + NT * BK * 2;      // one k-block of W and of the tokens
+    // one k-block of W (`rows` weight rows of 128 bytes) and of the tokens
+    static constexpr int block_bytes(int rows) { return rows * BK * 2 + NT * BK * 2; }
     static constexpr int kPartialBytes = NT * BM * 4;
     static constexpr int kMaxGroup = NT <= 64 ? 4 : 2;      // 128 tokens: a k-block is 32 KB, two of them per stage
     static constexpr int kMaxStages = 12;
-    static constexpr int max_stages(int group) {
-        const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * kBlockBytes);
+    static constexpr int max_stages(int group, int rows) {
+        const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * block_bytes(rows));
         return fit > kMaxStages ? kMaxStages : fit;
     }
     static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;      // two accumulators, one per issuing thread
     // a CTA takes only as many stages as it has work for, so that CTAs of the next kernel fit beside it
-    static constexpr int smem_bytes(int stages, int group) { return stages * group * kBlockBytes + kPartialBytes + 1024 + 1024; }
+    static constexpr int smem_bytes(int stages, int group, int rows) { return stages * group * block_bytes(rows) + kPartialBytes + 1024 + 1024; }
 };
 
 __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
@@ -678,12 +679,18 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 template <int NT>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                         const GemmParams p, const int ksplit, const int kStages, const int group) {
+                         const GemmParams p, const int ksplit, const int kStages, const int group, const int tile_rows) {
     // group > 0: the maps are the 3D k-block views and a stage holds `group` k-blocks; group == 0: 2D maps,
-    // one k-block per stage
+    // one k-block per stage.
+    // tile_rows (a multiple of 8, at most 128): weight rows per CTA.  What bounds a product of few rows is how many
+    // bytes the GPU has in flight, i.e. how many SMs stream: a matrix of 88 tiles of 128 rows leaves 60 SMs idle,
+    // 141 tiles of 80 rows do not.  The MMA is M = 128 all the same: a tile's k-blocks lie tile_rows * 128 bytes
+    // apart in shared memory, the rows beyond tile_rows that the tensor core reads belong to whatever follows
+    // there, and the sums they produce (rows of the accumulator that no row of C corresponds to) are never read.
     using C = SkinnyCfg<NT>;
     const int g = group > 0 ? group : 1;
-    const int w_bytes = g * BM * BK * 2, x_bytes = g * NT * BK * 2;       // one stage of each operand
+    const int w_block = tile_rows * BK * 2;                                 // one k-block of the tile
+    const int w_bytes = g * w_block, x_bytes = g * NT * BK * 2;           // one stage of each operand
     const int x_region = kStages * x_bytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -701,7 +708,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
-    const int n0 = (blockIdx.x / ksplit) * BM;
+    const int n0 = (blockIdx.x / ksplit) * tile_rows;
     const int num_kb = (p.K + BK - 1) / BK;
     // a CTA's last group may reach into the next CTA's k-blocks: those bytes are loaded and not multiplied
     const int kb_per = (num_kb + ksplit - 1) / ksplit;
@@ -781,7 +788,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     if (j >= here) break;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(d_tmem, umma_desc_advance(w_desc, j * (BM * BK * 2) + k * UMMA_K * 2),
+                        umma_bf16(d_tmem, umma_desc_advance(w_desc, j * w_block + k * UMMA_K * 2),
                                   umma_desc_advance(x_desc, j * (NT * BK * 2) + k * UMMA_K * 2), idesc, !(fresh && k == 0));
                     fresh = false;
                 }
@@ -813,7 +820,8 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (direct) {
             // the whole reduction happened in this CTA: straight from tensor memory to C.  A thread holds
             // one weight row n for all tokens, so for each token a warp writes 32 consecutive columns.
-            const int n = n0 + n_local;
+            // rows of the accumulator beyond the tile's own are not rows of C
+            const int n = n_local < tile_rows ? n0 + n_local : p.N;
             const float b = (p.bias && n < p.N) ? p.bias[n] : 0.f;
             if (ok) {
 #pragma unroll
@@ -865,8 +873,8 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     if (warp >= 2 && warp < 6 && !direct) {
         // this CTA owns a share of the tile's rows: add the partials in rank order, four
         // adjacent rows (16 bytes of each peer's shared memory) per thread
-        // (the tile's 32 groups of four rows are dealt out as evenly as the cluster's size allows)
-        const int group0 = (int)rank * (BM / 4) / ksplit, groups = ((int)rank + 1) * (BM / 4) / ksplit - group0;
+        // (the tile's groups of four rows are dealt out as evenly as the cluster's size allows)
+        const int group0 = (int)rank * (tile_rows / 4) / ksplit, groups = ((int)rank + 1) * (tile_rows / 4) / ksplit - group0;
         const int t = threadIdx.x - 64;                    // 0..127
         const uint32_t partial_addr = smem_u32(partial);
         for (int idx = t; idx < p.M * groups; idx += 128) {
@@ -1277,7 +1285,7 @@ int few_rows_group(int K, int kb_per, int max_group) {
 }
 
 template <int NT>
-int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit, cudaStream_t stream) {
+int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit, int tile_rows, cudaStream_t stream) {
     using C = SkinnyCfg<NT>;
     static forge::PerDeviceFlag configured_on;
     bool& configured = configured_on.current();
@@ -1287,23 +1295,23 @@ int launch_skinny(const void* W, const void* A, const GemmParams& p, int ksplit,
                                                  kSmemLimit, cudaGetErrorString(e));
         configured = true;
     }
-    const int tiles_n = (p.N + BM - 1) / BM;
+    const int tiles_n = (p.N + tile_rows - 1) / tile_rows;
     const int num_kb = (p.K + BK - 1) / BK, kb_per = (num_kb + ksplit - 1) / ksplit;
     const int group = few_rows_group(p.K, kb_per, C::kMaxGroup), g = group > 0 ? group : 1;
     const int groups_per = (kb_per + g - 1) / g;
-    const int stages = groups_per < C::max_stages(g) ? groups_per : C::max_stages(g);
+    const int stages = groups_per < C::max_stages(g, tile_rows) ? groups_per : C::max_stages(g, tile_rows);
     CUtensorMap tw, tx;
     const char* err = nullptr;
     if (group > 0) {
-        if (!bf16_kblock_map(W, p.N, p.K, BM, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_kblock_map(W, p.N, p.K, tile_rows, group, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
         if (!bf16_kblock_map(A, p.M, p.K, NT, group, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     } else {
-        if (!bf16_tile_map(W, p.N, p.K, BM, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        if (!bf16_tile_map(W, p.N, p.K, tile_rows, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
         if (!bf16_tile_map(A, p.M, p.K, NT, &tx, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     }
     return forge::check_launch("gemm_sm100 (few rows)",
                                forge::launch(gemm_sm100_skinny_kernel<NT>, dim3(tiles_n * ksplit), dim3(kSkinnyThreads),
-                                             C::smem_bytes(stages, g), stream, ksplit, tw, tx, p, ksplit, stages, group));
+                                             C::smem_bytes(stages, g, tile_rows), stream, ksplit, tw, tx, p, ksplit, stages, group, tile_rows));
 }
 
 // workspace for the stream-K partial sums and flags, per device, handed over once by the caller
@@ -1432,29 +1440,55 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
                 default: return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: the evenly dealt kernel takes at most 64 rows, got %d", M);
             }
         }
-        int ksplit = 1;
+        // The CTAs' shape: weight rows per tile (128, or fewer so that more SMs stream) and how many CTAs of a
+        // cluster cut K between them.  tile_n = -(100 * rows + cluster) names both (tests and measurements),
+        // -1 .. -8 the cluster with tiles of 128 rows.
+        int ksplit = 1, tile_rows = BM;
         if (tile_n < 0) {
-            ksplit = -tile_n;
+            ksplit = (-tile_n) % 100;
+            if (-tile_n >= 100) tile_rows = (-tile_n) / 100;
             if (ksplit < 1 || ksplit > 8)
                 return forge::fail(FORGE_ERR_ARG, "gemm_sm100: cluster size must be 1 to 8, got %d", ksplit);
+            // The MMA reads 128 rows from a tile's base whatever the tile holds: (128 - rows) * 128 bytes beyond the
+            // last k-block of the last stage, which must stay inside the CTA's shared memory.  Behind the weight
+            // stages lie the tokens' stages and the partial sums (at least 8 KB): 64 rows or more are safe.
+            if (tile_rows < 64 || tile_rows > BM || tile_rows % 16 != 0)
+                return forge::fail(FORGE_ERR_ARG, "gemm_sm100: a tile's weight rows must be 64, 80, 96, 112 or 128, got %d", tile_rows);
         } else {
             // The widest cluster whose CTAs all run at once (a second wave doubles the time) and still have a
-            // group of four k-blocks each.  An SM's tensor core takes W from shared memory at about 100 GB/s
-            // (the M operand of an N = 16 MMA), so it takes some 64 streaming SMs to keep up with HBM.
+            // group of four k-blocks each.
             // (clusters of 3, 5, 6 and 7 work too but measured no faster than the next power of two below them:
             // [2560 x 2048] 4.5 us with 4 CTAs, 5.2 with 6; [2048 x 5632] 7.7 and 7.4; 7 fit too few at once)
             for (int ks = 2; ks <= 8; ks *= 2)
                 if (tiles_n * ks <= max_resident_ctas(ks) && num_kb / ks >= 4) ksplit = ks;
+            // More CTAs through tiles of fewer than 128 weight rows (the MMA rows that nobody reads are free here).
+            // Up to 32 tokens this LOSES inside a decode step although each product alone gains: a product that
+            // leaves SMs idle leaves them to the next product's CTAs, which start early and request their first
+            // weight stages while this one runs; measured at 8 tokens, all four projections on 128 to 141 SMs:
+            // 0.83 -> 0.95 ms per step.  At 33 to 64 tokens a product lasts long enough for the gain to stay:
+            // gate/up 18.2 -> 15.3 us, 47.8 -> 49.1 thousand tokens a second at batch 64.
+            if (nt == 64) {
+                long best = (long)tiles_n * ksplit;
+                for (int rows = BM - 16; rows >= 64; rows -= 16) {
+                    const int tiles = (N + rows - 1) / rows;
+                    for (int ks = 1; ks <= 8; ks *= 2) {
+                        if (ks > 1 && num_kb / ks < 4) continue;
+                        const long ctas = (long)tiles * ks;
+                        if (ctas > max_resident_ctas(ks) || ctas <= best) continue;
+                        best = ctas; ksplit = ks; tile_rows = rows;
+                    }
+                }
+            }
         }
         // 65..128 tokens with an unsplit tile per CTA (many row tiles, e.g. gate/up): the token-major kernel with
         // 128-wide tiles is the faster one there (22 against 28-33 us at [11264 x 2048])
         const bool token_major_instead = nt == 128 && tile_n == 0 && ksplit == 1;
         GemmParams p{C, bias, M, N, K, epilogue, status};
         if (!token_major_instead) switch (nt) {
-            case 16: return launch_skinny<16>(W, A, p, ksplit, stream);
-            case 32: return launch_skinny<32>(W, A, p, ksplit, stream);
-            case 64: return launch_skinny<64>(W, A, p, ksplit, stream);
-            default: return launch_skinny<128>(W, A, p, ksplit, stream);
+            case 16: return launch_skinny<16>(W, A, p, ksplit, tile_rows, stream);
+            case 32: return launch_skinny<32>(W, A, p, ksplit, tile_rows, stream);
+            case 64: return launch_skinny<64>(W, A, p, ksplit, tile_rows, stream);
+            default: return launch_skinny<128>(W, A, p, ksplit, tile_rows, stream);
         }
     }
     int bn = tile_n;

@@ -116,11 +116,12 @@ def test_two_ctas_on_one_tile(M, N, K):
 
 @pytest.mark.parametrize("M", [1, 8, 16, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (48, 8), (2560, 2048), (257, 200), (2048, 5632), (1000, 1032)])
-@pytest.mark.parametrize("cluster", [0, -1, -2, -3, -4, -5, -6, -7, -8, -100])
+@pytest.mark.parametrize("cluster", [0, -1, -2, -3, -4, -5, -6, -7, -8, -100, -8004, -6402, -9601, -11203, -6408, -6401])
 def test_few_rows_kernel_with_k_cut_across_a_cluster(M, N, K, cluster):
     """The decode-shaped kernels (weights as the MMA's M operand) for every epilogue: K cut over a cluster of
-    1 to 8 CTAs with partial sums added through distributed shared memory, and (-100) units of work dealt
-    out evenly to persistent CTAs with partial sums added through a workspace."""
+    1 to 8 CTAs with partial sums added through distributed shared memory, tiles of fewer than 128 weight rows
+    (-(100 * rows + cluster)), and (-100) units of work dealt out evenly to persistent CTAs with partial sums added
+    through a workspace."""
     k = _k()
     a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
     bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
@@ -154,6 +155,8 @@ def test_few_rows_kernel_is_deterministic():
 
 def test_refuses_what_it_cannot_do():
     k = _k()
+    with pytest.raises(k.KernelError, match="64, 80, 96, 112 or 128"):      # shorter tiles would let the MMA read past the CTA's shared memory
+        k.gemm_sm100(_rand(4, 64), _rand(128, 64), tile_n=-1601)
     with pytest.raises(k.KernelError, match="multiple of 8"):
         k.gemm_sm100(_rand(4, 12), _rand(8, 12))
     with pytest.raises(k.KernelError, match="even"):
