@@ -51,6 +51,7 @@ _SIGNATURES = {
     "attention_mma": {
         "forge_paged_attention_mma": [_P] * 10 + [_I] * 9 + [_F, _P],
         "forge_decode_attention_fused": [_P] * 6 + [_I] * 8 + [_F, _F, _I, _P],
+        "forge_decode_attention_stream": [_P] * 7 + [_I] * 9 + [_F, _F, _I, _I, _P],
     },
     "attention_sm100": {
         "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
@@ -71,7 +72,7 @@ _libs = {}
 # library the bounds, per library (one per source file that checks):
 _CHECK_ENTRIES = {"core": ["forge_checks_configure_rope", "forge_checks_configure_attention_simt"],
                   "gemm_sm100": ["forge_checks_configure_gemm_sm100"],
-                  "attention_mma": ["forge_checks_configure_attention_mma"],
+                  "attention_mma": ["forge_checks_configure_attention_mma", "forge_checks_configure_attention_decode_stream"],
                   "attention_sm100": ["forge_checks_configure_attention_sm100"]}
 _check_bounds = [None]          # (num_pages, page_size, num_tokens, status tensor, first_bad tensor) of the current step
 
@@ -678,7 +679,7 @@ def paged_attention_mma(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, he
     return out
 
 
-def decode_attention_fused_supports(dtype, head_dim, group, num_requests, n_kv_heads, max_context):
+def decode_attention_fused_supports(dtype, head_dim, group, num_requests, n_kv_heads, max_context, page_size=None):
     """One launch for rotary encoding + cache write + attention of a decode step: bfloat16, head sizes in steps
     of 16 up to 128, at most 16 query heads per kv head.  With few requests and long contexts the
     sliced kernel (keys spread over many CTAs) is the better choice."""
@@ -687,7 +688,44 @@ def decode_attention_fused_supports(dtype, head_dim, group, num_requests, n_kv_h
     # with few requests the kernel spreads a request's keys over a cluster of up to 4 CTAs; measured (22 layers, 4 kv
     # heads, 8 requests x 6,000 cached tokens) 1.10 ms per step against 1.26 for the sliced kernel + merge.  Beyond
     # 16k cached tokens with a handful of CTAs the sliced kernel's many CTAs are the better choice again.
+    if page_size is not None and decode_attention_stream_supports(head_dim, page_size, group):
+        # the kernel that streams the cache spreads a request over up to 8 CTAs and keeps a ring of tiles in flight:
+        # the sliced kernel only wins with at most 16 (request, kv head) pairs beyond 16k tokens (measured: 4 pairs x
+        # 32k tokens 25 against 18 us, 16 pairs 46 against 38; 32 pairs 50 against 63)
+        return not (num_requests * n_kv_heads <= 16 and max_context > 16384)
     return not (num_requests * n_kv_heads < 64 and max_context > 16384)
+
+
+# The decode attention that streams the cache through a TMA ring pays where a request has many tiles of 64 keys, or
+# where there are more (request, kv head) pairs than SMs; with few pairs and fewer than this many cached tokens (an
+# upper bound known on the host) the kernel with one buffer pair per warp, which asks for a short context's tiles
+# before its dependency wait, is the faster one inside a step (measured, 8 requests x 540 tokens: 0.826 against
+# 0.846 ms per step; 64 requests: 48.6 against 49.9 thousand tokens a second the other way round).
+STREAM_ATTENTION_MIN_CONTEXT = int(os.environ.get("FORGE_STREAM_ATTENTION_MIN_CONTEXT", "2048"))
+STREAM_ATTENTION_MANY_PAIRS = 148
+
+
+def decode_attention_stream_supports(head_dim, page_size, group):
+    return _TENSOR_CORE_ATTENTION and head_dim in (64, 128) and page_size in (16, 32, 64) and group <= 16
+
+
+def decode_attention_stream(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim, page_size,
+                            theta, rotary=True, window=0, scale=None, out=None, max_context=0, ksplit=0):
+    """The same step as ``decode_attention_fused`` with the keys and values brought by TMA into a ring of tiles
+    (csrc/attention_decode_stream.cu): head sizes 64 and 128, pages of 16, 32 or 64 tokens.  ``ksplit``: CTAs that
+    share a request's keys (0: chosen from ``max_context``)."""
+    lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
+    S = qkv.shape[0]
+    if out is None:
+        out = new_tensor((S, n_heads * head_dim), torch.bfloat16, qkv.device)
+    scale = head_dim ** -0.5 if scale is None else scale
+    _check(lib, lib.forge_decode_attention_stream(
+        _need(qkv, "qkv", torch.float32, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
+        _need(block_table, "block_table", torch.int32, 2), _need(positions, "positions", torch.int32),
+        _need(slot_mapping, "slot_mapping", torch.int32), _need(_gemm_status(qkv.device), "status", torch.int32), S, n_heads,
+        n_kv_heads, head_dim, page_size, block_table.shape[1], kv_cache.shape[0], int(window or 0), 1 if rotary else 0,
+        float(theta), float(scale), int(max_context or 0), int(ksplit), _stream()), "decode_attention_stream")
+    return out
 
 
 def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim, page_size,
@@ -696,6 +734,10 @@ def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, 
     the cache at ``slot_mapping`` and returns the attention output bf16 [S, NH*HD], all in one kernel.
     ``max_context``: an upper bound of any request's cached tokens + 1, if known: with few requests and many keys
     the kernel then spreads a request's keys over 2 or 4 CTAs."""
+    if ((max_context or 0) >= STREAM_ATTENTION_MIN_CONTEXT or qkv.shape[0] * n_kv_heads > STREAM_ATTENTION_MANY_PAIRS) and \
+            decode_attention_stream_supports(head_dim, page_size, n_heads // n_kv_heads):
+        return decode_attention_stream(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim,
+                                       page_size, theta, rotary=rotary, window=window, scale=scale, out=out, max_context=max_context)
     lib = library("attention_mma", {"FORGE_ATT_HD": head_dim})
     S = qkv.shape[0]
     if out is None:

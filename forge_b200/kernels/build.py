@@ -25,7 +25,8 @@ LIBRARIES = {
     # bf16 tcgen05 + TMA GEMM with fused epilogues
     "gemm_sm100": ["gemm_sm100.cu"],
     # bf16 tensor-core paged attention (mma.sync) for any head size, prompt portions and decode
-    "attention_mma": ["attention_mma.cu"],
+    # ... and the decode step's attention that streams a long context through a TMA ring (head sizes 64 and 128)
+    "attention_mma": ["attention_mma.cu", "attention_decode_stream.cu"],
     # bf16 tcgen05/TMEM paged attention for prompt portions, head sizes 64 and 128 (built per head size)
     "attention_sm100": ["attention_sm100.cu"],
     # all layers of a decode step in one persistent kernel (tcgen05 + TMA weight stream, attention inside)

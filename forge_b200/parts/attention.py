@@ -67,7 +67,8 @@ class GQAAttention(Part):
             return None
         max_ctx = getattr(batch, "max_context", None) or (max(batch.host_context_before) + 1)
         ok = kernels.decode_attention_fused_supports(self.rt.dtype, self.head_dim, self.num_heads // self.num_kv_heads,
-                                                     batch.num_requests, self.num_kv_heads, max_ctx)
+                                                     batch.num_requests, self.num_kv_heads, max_ctx,
+                                                     page_size=cache.page_size)
         return params if ok else None
 
     def forward(self, x, batch, cache, residual):

@@ -128,3 +128,40 @@ def test_decode_step_in_one_kernel(nh, nkv, hd, ps, window, rotary):
                                            rotary=rotary, window=window, max_context=max_context).float()
             assert (got - ref).abs().max() <= 1e-2 * ref.abs().max(), max_context
             assert (work.float() - cache_ref.float()).abs().max() <= 1e-2 * cache_ref.float().abs().max()   # k, v landed in their slots
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 4, 64, 64), (32, 4, 64, 16), (14, 2, 128, 64), (16, 2, 128, 32), (3, 1, 64, 32), (16, 1, 64, 64)])
+@pytest.mark.parametrize("window,rotary", [(0, True), (100, True), (0, False)])
+def test_decode_step_with_the_cache_streamed_through_a_ring(nh, nkv, hd, ps, window, rotary):
+    """The decode attention whose keys and values come by TMA into a ring of 64-key tiles, against the plain
+    rope-and-write followed by the plain attention: contexts on and around page and tile edges (the new token is the
+    first, the last, the only row of its tile), few and many requests (8 or 4 consumer warps), 1 to 8 CTAs per request,
+    more tiles than the ring holds, a window that cuts the first tile, and one far key that carries the weight."""
+    from forge_b200 import kernels as k
+    theta = 5e5
+    for ctxs in ([0, 15, 16, 31, 32, 33, 63, 64, 65, 127, 128, 300, 1000], [7] * 70 + [129, 640], [2500, 3100], [5000]):
+        reqs = [(c, 1) for c in ctxs]
+        q, cache, group, batch, tok_req, positions = make_case(nh, nkv, hd, ps, reqs, seed=4)
+        S = len(reqs)
+        qkv = torch.randn(S, (nh + 2 * nkv) * hd, generator=torch.Generator().manual_seed(9)).to(q.device) * 1.5
+        slots = torch.tensor([int(group.block_table[s, c // ps]) * ps + c % ps for s, c in enumerate(ctxs)],
+                             dtype=torch.int32, device=q.device)
+        q_ref, cache_ref = R.rope_kv_write_ref(qkv, positions, slots, cache, nh, nkv, hd, ps, theta, rotary)
+        if window == 0 and max(ctxs) >= 2500:
+            # one early key gets nearly all the weight of the last request's first head
+            far = 77
+            page = int(group.block_table[S - 1, far // ps])
+            cache_ref[page, 0, 0, far % ps, :] = q_ref[S - 1, :hd].float() * 4.0
+            cache[page, 0, 0, far % ps, :] = cache_ref[page, 0, 0, far % ps, :].to(torch.bfloat16)
+        cache_ref = cache_ref.to(torch.bfloat16)                  # the engine's cache holds bf16
+        ref = R.paged_attention_ref(q_ref.to(torch.bfloat16), cache_ref, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
+        for ksplit, max_context in ((0, 0), (0, max(ctxs) + 1), (1, 0), (2, 0), (4, 0), (8, 0)):
+            if ksplit > 1 and S * nkv * ksplit > 2048:
+                continue
+            work = cache.clone()
+            got = k.decode_attention_stream(qkv, work, group.block_table, positions, slots, nh, nkv, hd, ps, theta,
+                                            rotary=rotary, window=window, max_context=max_context, ksplit=ksplit).float()
+            k.check_kernel_status()
+            err = (got - ref).abs().amax(dim=1)
+            assert float(err.max()) <= 1e-2 * float(ref.abs().max()), (ksplit, max_context, err.tolist())
+            assert (work.float() - cache_ref.float()).abs().max() <= 1e-2 * cache_ref.float().abs().max()   # k, v landed in their slots
