@@ -734,7 +734,9 @@ def decode_attention_fused(qkv, kv_cache, block_table, positions, slot_mapping, 
     the cache at ``slot_mapping`` and returns the attention output bf16 [S, NH*HD], all in one kernel.
     ``max_context``: an upper bound of any request's cached tokens + 1, if known: with few requests and many keys
     the kernel then spreads a request's keys over 2 or 4 CTAs."""
-    if ((max_context or 0) >= STREAM_ATTENTION_MIN_CONTEXT or qkv.shape[0] * n_kv_heads > STREAM_ATTENTION_MANY_PAIRS) and \
+    pairs = qkv.shape[0] * n_kv_heads
+    # (beyond some 768 pairs with short contexts the per-warp kernel is ahead again: 256 requests x 1,024 tokens 60 against 67 us)
+    if ((max_context or 0) >= STREAM_ATTENTION_MIN_CONTEXT or STREAM_ATTENTION_MANY_PAIRS < pairs <= 768) and \
             decode_attention_stream_supports(head_dim, page_size, n_heads // n_kv_heads):
         return decode_attention_stream(qkv, kv_cache, block_table, positions, slot_mapping, n_heads, n_kv_heads, head_dim,
                                        page_size, theta, rotary=rotary, window=window, scale=scale, out=out, max_context=max_context)

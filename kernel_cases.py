@@ -65,6 +65,17 @@ def case(name):
         slots = (g.block_table[:, 1023 // PS] * PS + 1023 % PS).to(torch.int32).contiguous()
         return (lambda: decode_attention_fused(qkv, kv, g.block_table, pos, slots, NH, NKV, HD, PS, 1e4)), \
             64 * 1024 * 2 * NKV * HD * 2, 4 * 64 * 1024 * NH * HD
+    if name == "attention_decode_stream":    # 32 requests x 8192 cached tokens through the TMA ring: 268 MB of keys and values
+        from forge_b200.kernels import decode_attention_stream
+        ctx, S, ps = 8192, 32, 64
+        pages_per = ctx // ps + 1
+        table = torch.arange(S * pages_per, dtype=torch.int32, device=DEV).reshape(S, pages_per)
+        kv = _bf16(S * pages_per, 2, NKV, ps, HD)
+        qkv = torch.randn(S, (NH + 2 * NKV) * HD, device=DEV)
+        pos = torch.full((S,), ctx, dtype=torch.int32, device=DEV)
+        slots = (table[:, ctx // ps] * ps + ctx % ps).to(torch.int32)
+        return (lambda: decode_attention_stream(qkv, kv, table, pos, slots, NH, NKV, HD, ps, 1e4, max_context=ctx + 1)), \
+            S * ctx * 2 * NKV * HD * 2, 4 * S * ctx * NH * HD
     if name == "attention_prefill":          # one request, 2048 tokens, causal: 17.2 GFLOP
         q, kv, g, b = _attention_inputs([(0, 2048)])
         return (lambda: paged_attention(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
@@ -82,7 +93,7 @@ def case(name):
         return (lambda: paged_attention_mma(q, kv, g, b, NH, NKV, HD, PS)), 0, 2 * 2048 * 2048 * NH * HD
     raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
-                     "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_prefill "
+                     "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "
                      "attention_prefill_hd128 attention_prefill_mma")
 
 
