@@ -435,6 +435,8 @@ int launch_stream(const CUtensorMap& tkv, const StreamParams& p, int S, int NKV,
     bool& configured = configured_on.current();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_stream_kernel<NC, R, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e == cudaSuccess && CLUSTER)      // one or two requests with very long contexts: clusters of 16
+            e = cudaFuncSetAttribute(decode_attention_stream_kernel<NC, R, CLUSTER>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return forge::fail(FORGE_ERR_LAUNCH, "decode_attention_stream: %s", cudaGetErrorString(e));
         configured = true;
     }
@@ -446,7 +448,8 @@ int launch_stream(const CUtensorMap& tkv, const StreamParams& p, int S, int NKV,
 }  // namespace
 
 // As forge_decode_attention_fused, plus: num_pages (pages of the cache tensor), status (device int, bit 1 raised if a
-// wait ran out), ksplit (0: choose; 1, 2, 4, 8: CTAs that share a request's keys).
+// wait ran out), ksplit (0: choose; 1, 2, 4, 8, 16: CTAs that share a request's keys; 16 is a cluster size beyond the
+// portable 8, which the kernel is marked for).
 extern "C" int forge_decode_attention_stream(const float* qkv, void* kv, void* out, const int32_t* block_table,
                                              const int32_t* positions, const int32_t* slot_mapping, int* status, int S,
                                              int NH, int NKV, int head_dim, int page_size, int max_pages, int num_pages,
@@ -458,8 +461,8 @@ extern "C" int forge_decode_attention_stream(const float* qkv, void* kv, void* o
     if (page_size != 16 && page_size != 32 && page_size != 64)
         return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_stream: page size %d (16, 32 or 64)", page_size);
     if (NH / NKV > 16) return forge::fail(FORGE_ERR_UNSUPPORTED, "decode_attention_stream: %d query heads per kv head (at most 16)", NH / NKV);
-    if (ksplit != 0 && ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
-        return forge::fail(FORGE_ERR_ARG, "decode_attention_stream: %d CTAs per request (1, 2, 4 or 8)", ksplit);
+    if (ksplit != 0 && ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8 && ksplit != 16)
+        return forge::fail(FORGE_ERR_ARG, "decode_attention_stream: %d CTAs per request (1, 2, 4, 8 or 16)", ksplit);
     if (S == 0) return FORGE_OK;
     const char* err = nullptr;
     CUtensorMap tkv;
@@ -479,14 +482,15 @@ extern "C" int forge_decode_attention_stream(const float* qkv, void* kv, void* o
     } else if (few && max_context > 0) {
         // a cluster lives inside one GPC: fewer CTAs run at once in clusters of 4 or 8 than there are SMs, and a
         // second wave would double the time
-        static int resident[9] = {0};
+        static int resident[17] = {0};
         const long tiles = (max_context + TK - 1) / TK;
-        for (int ks = 2; ks <= 8; ks *= 2) {
+        for (int ks = 2; ks <= 16; ks *= 2) {
             if (resident[ks] == 0) {
                 cudaFuncSetAttribute(decode_attention_stream_kernel<kFew, kFew, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      StreamCfg<kFew, kFew>::kSmemBytes);
+                cudaFuncSetAttribute(decode_attention_stream_kernel<kFew, kFew, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
                 cudaLaunchConfig_t cfg = {};
-                cfg.gridDim = dim3(ks * 32);
+                cfg.gridDim = dim3(ks * 16);
                 cfg.blockDim = dim3(StreamCfg<kFew, kFew>::kThreads);
                 cfg.dynamicSmemBytes = StreamCfg<kFew, kFew>::kSmemBytes;
                 cudaLaunchAttribute at[1];
@@ -499,9 +503,9 @@ extern "C" int forge_decode_attention_stream(const float* qkv, void* kv, void* o
                 int n = 0;
                 if (cudaOccupancyMaxActiveClusters(&n, decode_attention_stream_kernel<kFew, kFew, true>, &cfg) != cudaSuccess || n <= 0) {
                     cudaGetLastError();
-                    n = (sms - sms / 8 * (ks > 2 ? (ks > 4 ? 2 : 1) : 0)) / ks;      // a guess on the safe side
+                    n = ks > 8 ? 0 : (sms - sms / 8 * (ks > 2 ? (ks > 4 ? 2 : 1) : 0)) / ks;      // a guess on the safe side; no clusters of 16
                 }
-                resident[ks] = n * ks;
+                resident[ks] = n > 0 ? n * ks : -1;
             }
             if ((long)S * NKV * ks <= resident[ks] && tiles >= (long)kFew * ks) p.ksplit = ks;
         }

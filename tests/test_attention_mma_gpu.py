@@ -135,7 +135,7 @@ def test_decode_step_in_one_kernel(nh, nkv, hd, ps, window, rotary):
 def test_decode_step_with_the_cache_streamed_through_a_ring(nh, nkv, hd, ps, window, rotary):
     """The decode attention whose keys and values come by TMA into a ring of 64-key tiles, against the plain
     rope-and-write followed by the plain attention: contexts on and around page and tile edges (the new token is the
-    first, the last, the only row of its tile), few and many requests (8 or 4 consumer warps), 1 to 8 CTAs per request,
+    first, the last, the only row of its tile), few and many requests (8 or 4 consumer warps), 1 to 16 CTAs per request,
     more tiles than the ring holds, a window that cuts the first tile, and one far key that carries the weight."""
     from forge_b200 import kernels as k
     theta = 5e5
@@ -155,8 +155,8 @@ def test_decode_step_with_the_cache_streamed_through_a_ring(nh, nkv, hd, ps, win
             cache[page, 0, 0, far % ps, :] = cache_ref[page, 0, 0, far % ps, :].to(torch.bfloat16)
         cache_ref = cache_ref.to(torch.bfloat16)                  # the engine's cache holds bf16
         ref = R.paged_attention_ref(q_ref.to(torch.bfloat16), cache_ref, group.block_table, tok_req, positions, nh, nkv, hd, ps, window)
-        for ksplit, max_context in ((0, 0), (0, max(ctxs) + 1), (1, 0), (2, 0), (4, 0), (8, 0)):
-            if ksplit > 1 and S * nkv * ksplit > 2048:
+        for ksplit, max_context in ((0, 0), (0, max(ctxs) + 1), (1, 0), (2, 0), (4, 0), (8, 0), (16, 0)):
+            if (ksplit > 1 and S * nkv * ksplit > 2048) or (ksplit == 16 and S > 4):
                 continue
             work = cache.clone()
             got = k.decode_attention_stream(qkv, work, group.block_table, positions, slots, nh, nkv, hd, ps, theta,
