@@ -5,11 +5,14 @@ they expect under the plan's prefixes, hands each part its tensors, and runs the
 ``plan.schedule``.  (The reference's counterpart is TransformerEngine + GenericEngine,
 src/inference/engines/transformer_engine.cpp:445-522, with the layer body at generic_engine.cpp:916-1085.)
 """
+import os
+
 import torch
 
+from .. import kernels
 from ..config.base import ConfigError, ModelPlan
 from ..parts import Runtime, build_block, build_part
-from ..parts.base import is_graph_safe
+from ..parts.base import is_graph_safe, replay_of
 from ..weights.loader import WeightError
 
 
@@ -29,6 +32,7 @@ class Model:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
         self.loaded = False
         self._fused = None
+        self._replay_ok, self._replay_tensors = False, []
 
     # ---------------------------------------------------------------------------------- tensors
     def _children(self):
@@ -62,6 +66,11 @@ class Model:
             else:
                 part.bind(mine)
         self.loaded = True
+        # layers whose launches may be repeated from one noted layer: from the second run of the schedule on, all of
+        # one key (the first run is always made by the parts themselves)
+        runs = [replay_of(self.blocks[i]) for i in self.plan.schedule]
+        self._replay_ok = len(runs) >= 3 and all(r is not None for r in runs[1:]) and len({r[0] for r in runs[1:]}) == 1
+        self._replay_tensors = [r[1] if r is not None else None for r in runs]
 
     def graph_safe(self):
         """True if every part that a step runs declares that a CUDA graph may capture it."""
@@ -127,6 +136,22 @@ class Model:
             return False
         return True
 
+    def _replay_applies(self, position_caches, ws):
+        """Whether the layers after the second may repeat the second's launches: every layer from the second on
+        declares it and has the same key (``parts.base.replay_of``), their caches are of one kind, the outputs come
+        from the step's workspace (so a layer's intermediates have the same addresses in every layer), and no timing
+        table is being taken (it wants an event per launch)."""
+        if ws is None or not self._replay_ok or kernels.profiler_enabled() or os.environ.get("FORGE_LAYER_REPLAY", "1") == "0":
+            return False
+        c1 = position_caches[1]
+        kind = (getattr(c1, "group", None), getattr(c1, "writable", None), getattr(c1, "page_size", None))
+        for c in position_caches[1:]:
+            kv = getattr(c, "kv", None)
+            if kv is None or (getattr(c, "group", None), getattr(c, "writable", None), getattr(c, "page_size", None)) != kind \
+                    or kv.shape != c1.kv.shape or kv.dtype != c1.kv.dtype:
+                return False
+        return True
+
     # ---------------------------------------------------------------------------------- forward
     def forward(self, batch, position_caches, workspace=None):
         """Runs the step's tokens through the schedule; ``position_caches[p]`` is the cache of the p-th run.
@@ -139,9 +164,23 @@ class Model:
             fused.run(residual, g.block_table, batch.positions, g.slot_mapping)
         else:
             ws = workspace
+            replay = None
             for pos, i in enumerate(self.plan.schedule):
+                if replay is not None:
+                    replay.run(self._replay_tensors[pos] + [position_caches[pos].kv])
+                    continue
+                # the second layer's launches are noted (the first also makes what the whole step shares: tile
+                # lists, the table of angles) and repeated for the layers after it
+                note = pos == 1 and self._replay_applies(position_caches, ws)
                 m = ws.mark() if ws is not None else 0
-                self.blocks[i].forward(residual, batch, position_caches[pos])
+                if note:
+                    overflow = ws.allocations
+                    with kernels.record_launches() as rec:
+                        self.blocks[i].forward(residual, batch, position_caches[pos])
+                    if ws.allocations == overflow:      # every output came from the workspace: the addresses repeat
+                        replay = kernels.LayerReplay(rec, self._replay_tensors[pos] + [position_caches[pos].kv])
+                else:
+                    self.blocks[i].forward(residual, batch, position_caches[pos])
                 if ws is not None:
                     ws.release(m)              # a layer's intermediates are dead: the residual stream carries on
         if batch.num_logits == 0:

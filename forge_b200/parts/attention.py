@@ -55,6 +55,19 @@ class GQAAttention(Part):
     def cache_spec(self):
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def replay_tensors(self):
+        from .base import replay_of
+        pos = replay_of(self.position)
+        if type(self) is not GQAAttention or pos is None:
+            return None
+        return self.qkv.replay_tensors() + self.o.replay_tensors() + pos[1]
+
+    def replay_key(self):
+        from .base import replay_of
+        pos = replay_of(self.position)
+        return None if pos is None else ("gqa", self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                                         self.qkv.replay_key(), self.o.replay_key(), pos[0])
+
     def _decode_in_one_kernel(self, batch, cache):
         """A step of one new token per request, with a position part that offers its encoding to the decode
         kernel (``fused_decode``): encoding, cache write and attention run as one launch.  Returns the

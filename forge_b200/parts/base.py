@@ -70,6 +70,21 @@ def registered_parts(category):
     return sorted(_REGISTRY[category])
 
 
+def replay_of(part):
+    """(key, tensors) if ``part`` declares that its launches in one layer differ from its launches in another layer of
+    the same shape only by the addresses of its own device tensors, else None.  A part declares it with
+    ``replay_tensors()`` (its device tensors in a fixed order, None where an optional one is absent) and ``replay_key()``
+    (everything else that shapes its launches: sizes, constants, types); the model then runs one such layer through
+    Python, notes the launches, and repeats them for the other layers with the addresses exchanged.  A part that keeps
+    host state per layer, or runs device work that is not one of ``forge_b200.kernels``' launches, must not declare it."""
+    tensors = getattr(part, "replay_tensors", None)
+    key = getattr(part, "replay_key", None)
+    if tensors is None or key is None:
+        return None
+    t, k = tensors(), key()
+    return None if t is None or k is None else (k, list(t))
+
+
 def is_graph_safe(part):
     """True if the part and every part inside it declare ``graph_safe``."""
     if not getattr(part, "graph_safe", False):

@@ -59,6 +59,19 @@ class PreNormBlock(Part):
                 "tensors": {"wqkv": m.qkv.weight, "wo": m.o.weight, "wgu": f.gate_up.weight, "wdown": f.down.weight,
                             "norm1": n1.weight, "norm2": n2.weight, "bias": m.qkv.bias}}
 
+    def _replay_parts(self):
+        from .base import replay_of
+        parts = [replay_of(p) for p in (self.norm_in, self.mixer, self.norm_post, self.feed_forward)]
+        return None if type(self) is not PreNormBlock or any(p is None for p in parts) else parts
+
+    def replay_tensors(self):
+        parts = self._replay_parts()
+        return None if parts is None else [t for _, tensors in parts for t in tensors]
+
+    def replay_key(self):
+        parts = self._replay_parts()
+        return None if parts is None else ("pre_norm",) + tuple(k for k, _ in parts)
+
     def forward(self, residual, batch, cache):
         x = self.norm_in.forward(residual)
         self.mixer.forward(x, batch, cache, residual)

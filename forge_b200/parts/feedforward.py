@@ -31,6 +31,12 @@ class SwiGLU(Part):
         self.gate_up = Linear(self._matrix(gu), None, self.rt)
         self.down = Linear(self._matrix(tensors[n["down"] + ".weight"]), None, self.rt)
 
+    def replay_tensors(self):
+        return self.gate_up.replay_tensors() + self.down.replay_tensors() if type(self) is SwiGLU else None
+
+    def replay_key(self):
+        return ("swiglu", self.gate_up.replay_key(), self.down.replay_key())
+
     def forward(self, x, residual):
         act = self.gate_up.forward(x, epilogue="swiglu")          # [T,I] in the activation type
         self.down.forward(act, accumulate_into=residual)

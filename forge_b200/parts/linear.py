@@ -17,6 +17,12 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.tensor_core = (not rt.full_precision) and kernels.gemm_sm100_supports(self.out_features, self.in_features)
 
+    def replay_tensors(self):
+        return [self.weight, self.bias]
+
+    def replay_key(self):
+        return ("linear", tuple(self.weight.shape), self.weight.dtype, self.bias is None, self.tensor_core)
+
     def forward(self, x, accumulate_into=None, epilogue="none"):
         """x [M,K] in rt.dtype.
         epilogue "none":   fp32 [M,N] (added into ``accumulate_into`` if given, which is then returned)

@@ -17,6 +17,12 @@ class RMSNorm(Part):
     def bind(self, tensors):
         self.weight = self._vector_f32(tensors[self.names["weight"]])
 
+    def replay_tensors(self):
+        return [self.weight] if type(self) is RMSNorm else None
+
+    def replay_key(self):
+        return ("rmsnorm", self.size, self.eps, self.rt.dtype)
+
     def forward(self, x, out_dtype=None, rows=None):
         """x: fp32 [T,size] (the residual stream); returns [T or len(rows), size] in ``out_dtype``."""
         return kernels.rmsnorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)

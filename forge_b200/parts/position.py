@@ -27,6 +27,12 @@ class RotaryEmbedding(Part):
             return None
         return {"theta": self.theta, "rotary": self.rotary}
 
+    def replay_tensors(self):
+        return [] if type(self) in (RotaryEmbedding, NoPosition) else None      # no tensors: the angles come from positions
+
+    def replay_key(self):
+        return (type(self).__name__, self.head_dim, self.theta, self.rotary)
+
     def _table(self, positions, batch, by_pair=False):
         """The step's cos/sin table, computed once per step (kept in the batch's ``attention_plan``), not once per
         layer.  A batch that a CUDA graph replays keeps no table: the table of the captured step would be replayed
