@@ -301,3 +301,38 @@ def test_command_line_benchmark(tiny):
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert "Prefill   32 tokens" in proc.stdout and "Prefill  512 tokens" in proc.stdout and "Decode   128 tokens" in proc.stdout
     assert "Benchmark complete" in proc.stdout
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_long_contexts_decode_through_the_streamed_attention(name, tmp_path, monkeypatch):
+    """Requests of more than 2,048 tokens beside a short one, decoded together through the CUDA graph: the graph's
+    context bucket (4,096) sends the step's attention to the kernel that streams the cache through a TMA ring, with
+    clusters of CTAs per request; every token must follow the plain implementation.  Head sizes 64 and 128."""
+    import forge_b200 as forge
+    from forge_b200 import kernels
+    from forge_b200.config import config_from_dict
+    from forge_b200.weights import write_random_model
+    from helpers import STDS
+    from plain.llama import PlainLlama
+    cfg = dict(TINY[name], max_position_embeddings=4096)
+    d = str(tmp_path / "long")
+    write_random_model(config_from_dict(cfg), d, seed=11, **STDS[name])
+    plain = PlainLlama(d)
+    V = cfg["vocab_size"]
+    prompts = [random_tokens(n, V, seed=60 + i) for i, n in enumerate([2100, 37, 2311])]
+    calls = [0]
+    orig = kernels.decode_attention_stream
+
+    def counted(*a, **k):
+        calls[0] += 1
+        return orig(*a, **k)
+    monkeypatch.setattr(kernels, "decode_attention_stream", counted)
+    model = forge.Model(d, dtype="bfloat16", max_num_seqs=4, cache_tokens=3 * 2432, max_tokens_per_step=1024)
+    sched = forge.RequestScheduler(model, max_num_seqs=4)
+    ids = [sched.submit(p, max_new_tokens=10, sampler_config=forge.SamplerConfig(do_sample=False)) for p in prompts]
+    done = {r.request_id: r for r in sched.run()}
+    assert calls[0] >= cfg["num_hidden_layers"], "the long contexts were meant to take the streamed attention"
+    for rid, p in zip(ids, prompts):
+        assert done[rid].finish_reason == "length" and len(done[rid].output_tokens) == 10
+        assert_greedy_follows_plain(plain.logits, p, done[rid].output_tokens, TOL["bfloat16"], f"request of {len(p)} tokens")
+    model.runner.check_status()
