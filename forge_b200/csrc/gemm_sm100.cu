@@ -626,6 +626,190 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     }
 }
 
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Some hundred rows, few tiles: K cut across a cluster.
+//
+// A product of 129 to about 1,000 rows onto a narrow matrix (the o and down projections of a prompt of 512 tokens:
+// [512 x 2048]) makes 64 tiles of 128 x 128, so fewer than half of the SMs work, and each of them has to take in its
+// whole share of both operands (1 MB a tile at K = 2048) at the 60 GB/s that an SM's copies deliver: 17 of the 20 us
+// such a product takes.  Here the 2 or 4 CTAs of a cluster share one tile and cut K between them, so twice or four
+// times the SMs take the operands in.  Each CTA parks its [128 x 128] fp32 partial in shared memory (the ring of
+// stages is free by then; 16-byte chunk j of row m at chunk j ^ (m % 32), which both the writers, a row per thread,
+// and the readers, a row per warp, touch without bank conflicts), the cluster synchronises, and every CTA then adds
+// up, in rank order (so the result does not depend on timing), the rows it owns, adds the bias and writes C: a
+// store, or one add per element into the residual stream.  fp32 results only (no bf16 or SwiGLU epilogue).
+constexpr int kSplitBN = 128;
+struct SplitKCfg {
+    static constexpr int kStageBytes = (BM + kSplitBN) * BK * 2;            // 32 KB
+    static constexpr int kStages = 4;
+    static constexpr int kPartialBytes = BM * kSplitBN * 4;                 // 64 KB
+    static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 1024;
+    static constexpr int kTmemCols = 128;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sm100_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                         const GemmParams p, const int ksplit) {
+    using C = SplitKCfg;
+    constexpr int kStages = C::kStages, BN = kSplitBN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    float* partial = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);          // [128 rows][32 chunks of 4], swizzled
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kPartialBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kStages;
+    uint64_t* acc_full = bars + 2 * kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tile = blockIdx.x / ksplit;
+    const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int kb_per = (num_kb + ksplit - 1) / ksplit;
+    const int kb_begin = rank * kb_per, kb_end = min(kb_begin + kb_per, num_kb);
+    const int my_kb = max(kb_end - kb_begin, 0);
+
+    if (threadIdx.x == 0) {
+        *abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        mbar_fence_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    forge::pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // the weights do not depend on earlier kernels: their first stages are requested before the wait
+            const int first = min(my_kb, kStages);
+            for (int i = 0; i < first; ++i) {
+                mbar_arrive_expect_tx(&full[i], C::kStageBytes);
+                tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_w, &full[i], (kb_begin + i) * BK, n0);
+            }
+            forge::pdl_wait();                    // the activations come from the previous kernel
+            for (int i = 0; i < first; ++i) tma_load_2d(tiles + i * C::kStageBytes, &tmap_a, &full[i], (kb_begin + i) * BK, m0);
+            bool ok = true;
+            for (int i = first; i < my_kb && ok; ++i) {
+                const int s = i % kStages;
+                if (!(ok = mbar_wait(&empty[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
+                mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                tma_load_2d(tiles + s * C::kStageBytes, &tmap_a, &full[s], (kb_begin + i) * BK, m0);
+                tma_load_2d(tiles + s * C::kStageBytes + BM * BK * 2, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < my_kb && ok; ++i) {
+                const int s = i % kStages;
+                if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
+                const uint64_t a_desc = umma_desc_k_sw128(a_addr), w_desc = umma_desc_k_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, umma_desc_advance(a_desc, k * UMMA_K * 2), umma_desc_advance(w_desc, k * UMMA_K * 2),
+                              idesc, k != 0 || i != 0);
+                umma_commit(&empty[s]);
+            }
+            if (ok && my_kb > 0) umma_commit(acc_full);
+        }
+    } else {
+        // warps 2..5: this CTA's partial sums out of tensor memory, a row per thread
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        forge::pdl_wait();                        // C and bias: written or still read by earlier kernels
+        bool ok = true;
+        if (my_kb > 0) ok = mbar_wait(acc_full, 0, abort, p.status);
+        tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        float4* prow = reinterpret_cast<float4*>(partial) + row * (BN / 4);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t r[32];
+            if (my_kb > 0 && ok) {
+                tmem_ld_32x32b_x32(t_row + c, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                prow[((c >> 2) + j) ^ (row & 31)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();                       // every CTA's partial is in place and visible
+
+    if (warp >= 2) {
+        // this CTA owns rows [rank * 128 / ksplit, (rank + 1) * 128 / ksplit) of the tile; a warp takes a row at a
+        // time, a lane 16 bytes of it
+        const int row_lo = rank * BM / ksplit, row_hi = (rank + 1) * BM / ksplit;
+        const uint32_t partial_addr = smem_u32(partial);
+        const int n = n0 + 4 * lane;
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p.bias) {
+            if (n + 3 < p.N) b = *reinterpret_cast<const float4*>(p.bias + n);
+            else { if (n < p.N) b.x = p.bias[n]; if (n + 1 < p.N) b.y = p.bias[n + 1]; if (n + 2 < p.N) b.z = p.bias[n + 2]; }
+        }
+        for (int row = row_lo + (warp - 2); row < row_hi; row += 4) {
+            const int m = m0 + row;
+            float4 acc = b;
+            const uint32_t at = partial_addr + (row * (BN / 4) + (lane ^ (row & 31))) * 16;
+            for (int q = 0; q < ksplit; ++q) {
+                const float4 v = ld_dsmem_f32x4(at, q);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            if (m >= p.M || n >= p.N) continue;
+            float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+            const bool accum = p.epilogue == EPI_ACCUM_F32;
+            if (n + 3 < p.N && (p.N & 3) == 0) {
+                if (accum) atomicAdd(reinterpret_cast<float4*>(dst), acc);       // one add per element: the order of CTAs does not matter
+                else *reinterpret_cast<float4*>(dst) = acc;
+            } else {
+                const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+                for (int i = 0; i < 4; ++i) {
+                    if (n + i >= p.N) break;
+                    if (accum) atomicAdd(dst + i, v[i]);
+                    else dst[i] = v[i];
+                }
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_all();                       // nobody leaves while a peer may still read its partial
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // Few rows (decode): the weight matrix is the MMA's M operand.
 //
@@ -666,15 +850,6 @@ template <int NT> struct SkinnyCfg {                       // NT: token box (UMM
     // a CTA takes only as many stages as it has work for, so that CTAs of the next kernel fit beside it
     static constexpr int smem_bytes(int stages, int group, int rows) { return stages * group * block_bytes(rows) + kPartialBytes + 1024 + 1024; }
 };
-
-__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t rank) {
-    uint32_t remote;
-    float4 v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
-    return v;
-}
 
 template <int NT>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
@@ -1270,6 +1445,45 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
     return launch_pair_width<kPairBN>(A, W, p, stream);
 }
 
+// How many CTAs of the split-K kernel run at once in clusters of `ks` (one CTA per SM).
+int splitk_resident_ctas(int ks) {
+    static int cached[5] = {0};
+    if (ks != 2 && ks != 4) return 0;
+    if (cached[ks] == 0) {
+        cudaFuncSetAttribute(gemm_sm100_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SplitKCfg::kSmemBytes);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ks * 32);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = SplitKCfg::kSmemBytes;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = ks;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_splitk_kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = (g_num_sms - (ks > 2 ? g_num_sms / 8 : 0)) / ks;      // a guess on the safe side
+        }
+        cached[ks] = n * ks;
+    }
+    return cached[ks];
+}
+
+int launch_splitk(const void* A, const void* W, const GemmParams& p, int ksplit, cudaStream_t stream) {
+    splitk_resident_ctas(2);                            // also sets the kernel's shared-memory limit
+    CUtensorMap ta, tw;
+    const char* err = nullptr;
+    if (!bf16_tile_map(A, p.M, p.K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+    if (!bf16_tile_map(W, p.N, p.K, kSplitBN, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + kSplitBN - 1) / kSplitBN);
+    return forge::check_launch("gemm_sm100 (K cut across a cluster)",
+                               forge::launch(gemm_sm100_splitk_kernel, dim3(tiles * ksplit), dim3(kThreads), SplitKCfg::kSmemBytes,
+                                             stream, ksplit, ta, tw, p, ksplit));
+}
+
 // k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps).  The group
 // that loads the fewest k-blocks beyond the CTA's own (its last group is whole all the same), the larger one of equals;
 // at least two per instruction where there are two (one 16 KB box per instruction is bound by the instruction rate).
@@ -1411,7 +1625,8 @@ extern "C" int forge_gemm_sm100_set_workspace(void* ptr, long long bytes) {
 // A [M,K] bf16, W [N,K] bf16 (both row-major, K % 8 == 0, 16-byte aligned), bias fp32 [N] or null.
 // epilogue: 0 C fp32 = ..., 1 C fp32 += ..., 2 C bf16 = ..., 3 C bf16 [M,N/2] = swiglu (N even).
 // tile_n: 0 = choose; 16, 32, 64, 128, 160, 192, 224, 256 = token-major tiles of that width; 512 (M > 128) = a pair
-// of CTAs on a [256 x 256] tile (cta_group::2); -1 .. -8 (M <= 128 only) =
+// of CTAs on a [256 x 256] tile (cta_group::2); 1002, 1004 (M > 128, fp32 results) = tiles of 128 x 128 with K cut across
+// a cluster of 2 or 4 CTAs; -1 .. -8 (M <= 128 only) =
 // the few-rows kernel with K cut across a cluster of that many CTAs; -100 (M <= 64 only) = the few-rows kernel
 // that deals units of work out evenly to persistent CTAs (the default once a workspace has been set).  status: device int, bit 1 raised if a wait ran out.
 extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias, void* C, int* status, int M, int N,
@@ -1505,6 +1720,24 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             case 32: return launch_skinny<32>(W, A, p, ksplit, tile_rows, stream);
             case 64: return launch_skinny<64>(W, A, p, ksplit, tile_rows, stream);
             default: return launch_skinny<128>(W, A, p, ksplit, tile_rows, stream);
+        }
+    }
+    // Some hundred rows onto a narrow matrix with an fp32 result (o and down projections of a short prompt): tiles of
+    // 128 x 128 with K cut across 2 or 4 CTAs while that fills no more than the SMs that run at once.  tile_n 1002 and
+    // 1004 name it (tests and measurements).
+    if (M > BM && (epilogue == EPI_STORE_F32 || epilogue == EPI_ACCUM_F32) && (tile_n == 0 || tile_n == 1002 || tile_n == 1004)) {
+        const long tiles = (long)((M + BM - 1) / BM) * ((N + kSplitBN - 1) / kSplitBN);
+        const int num_kb = (K + BK - 1) / BK;
+        int ks = 0;
+        if (tile_n > 1000) {
+            ks = tile_n - 1000;
+        } else {
+            for (int c : {2, 4})
+                if (tiles * c <= splitk_resident_ctas(c) && num_kb / c >= 8) ks = c;
+        }
+        if (ks > 0) {
+            GemmParams p{C, bias, M, N, K, epilogue, status};
+            return launch_splitk(A, W, p, ks, stream);
         }
     }
     int bn = tile_n;

@@ -88,6 +88,38 @@ def test_fp32_results_through_shared_memory_and_tma(M, N, K, tile_n):
     k.check_kernel_status()
 
 
+@pytest.mark.parametrize("tile_n", [0, 1002, 1004])
+@pytest.mark.parametrize("M,N,K", [(512, 2048, 2048), (129, 36, 64), (300, 1000, 136), (512, 2048, 5632), (700, 515, 1032),
+                                   (257, 130, 4104), (1100, 2052, 72)])
+def test_k_cut_across_a_cluster_for_some_hundred_rows(M, N, K, tile_n):
+    """Tiles of 128 x 128 whose K is shared by 2 or 4 CTAs, partial sums added through distributed shared memory in
+    rank order: fp32 store and the addition into the residual (each product counted once), bias, row, column and
+    reduction tails (a last k-block that is partly zeros, CTAs of a cluster with no k-block at all: K = 64 or 72 with 4
+    CTAs), and the same bits every time."""
+    k = _k()
+    a, w = _rand(M, K), _rand(N, K, seed=1, scale=0.3)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(2)).to(DEV)
+    ref = R.gemm_ref(a, w, bias)
+    tol = 1e-5 * ref.abs().max() * max(1.0, (K / 64) ** 0.5)
+    guard = torch.full((M + 2, N), 7.0, device=DEV)            # the rows around the result must stay as they are
+    got = k.gemm_sm100(a, w, bias=bias, tile_n=tile_n, out=guard[1:M + 1])
+    assert (got - ref).abs().max() <= tol
+    assert (guard[0] == 7.0).all() and (guard[M + 1] == 7.0).all()
+    for _ in range(3):
+        assert torch.equal(k.gemm_sm100(a, w, bias=bias, tile_n=tile_n), got)
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(3)).to(DEV)
+    acc = res.clone()
+    k.gemm_sm100(a, w, bias=bias, accumulate_into=acc, tile_n=tile_n)
+    assert (acc - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max()
+    first = acc.clone()
+    k.gemm_sm100(a, w, bias=bias, accumulate_into=acc, tile_n=tile_n)
+    assert (acc - (res + 2 * ref)).abs().max() <= 2 * tol + 1e-6 * res.abs().max()
+    again = res.clone()
+    k.gemm_sm100(a, w, bias=bias, accumulate_into=again, tile_n=tile_n)
+    assert torch.equal(again, first)                           # the additions do not depend on the CTAs' timing
+    k.check_kernel_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (130, 257, 200), (300, 515, 1032), (2048, 2560, 2048), (1000, 384, 96),
                                    (257, 130, 4104), (4608, 4608, 128)])
 def test_two_ctas_on_one_tile(M, N, K):
