@@ -1725,7 +1725,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
     // Some hundred rows onto a narrow matrix with an fp32 result (o and down projections of a short prompt): tiles of
     // 128 x 128 with K cut across 2 or 4 CTAs while that fills no more than the SMs that run at once.  tile_n 1002 and
     // 1004 name it (tests and measurements).
-    if (M > BM && (epilogue == EPI_STORE_F32 || epilogue == EPI_ACCUM_F32) && (tile_n == 0 || tile_n == 1002 || tile_n == 1004)) {
+    if ((M > BM || tile_n > 1000) && (epilogue == EPI_STORE_F32 || epilogue == EPI_ACCUM_F32) && (tile_n == 0 || tile_n == 1002 || tile_n == 1004)) {
         const long tiles = (long)((M + BM - 1) / BM) * ((N + kSplitBN - 1) / kSplitBN);
         const int num_kb = (K + BK - 1) / BK;
         int ks = 0;
