@@ -1770,10 +1770,13 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
             if (((pair_tiles + pairs - 1) / pairs) * ksteps * 150 + 36L * kPairBN < best) bn = 512;
         }
     }
-    if (bn == 512) {
+    if (bn == 512 || bn == 1192 || bn == 1128) {
         if (M <= BM) return forge::fail(FORGE_ERR_ARG, "gemm_sm100: the two-CTA tile is for more than %d rows, got %d", BM, M);
         GemmParams p{C, bias, M, N, K, epilogue, status};
-        return launch_pair(A, W, p, stream);
+        if (bn == 512) return launch_pair(A, W, p, stream);
+        if (K % BK != 0 || K < 2 * BK)
+            return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: two-CTA tiles of %d columns need K %% 64 == 0 and K >= 128, got %d", bn - 1000, K);
+        return bn == 1192 ? launch_pair_width<192>(A, W, p, stream) : launch_pair_width<128>(A, W, p, stream);
     }
     CUtensorMap ta, tw;
     if (!bf16_tile_map(A, M, K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
@@ -1788,7 +1791,7 @@ extern "C" int forge_gemm_sm100(const void* A, const void* W, const float* bias,
         case 64: return launch<64>(ta, tw, p, stream);
         case 32: return launch<32>(ta, tw, p, stream);
         case 16: return launch<16>(ta, tw, p, stream);
-        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224, 256 or 512 (two CTAs on 256 x 256), got %d", bn);
+        default: return forge::fail(FORGE_ERR_ARG, "gemm_sm100: tile_n must be 16, 32, 64, 128, 160, 192, 224, 256, or 512 / 1192 / 1128 (two CTAs on 256 x 256 / 192 / 128), got %d", bn);
     }
 }
 

@@ -141,6 +141,19 @@ def test_two_ctas_on_one_tile(M, N, K):
         got = k.gemm_sm100(a, w, bias=bias, epilogue="swiglu", tile_n=512)
         want = R.silu_mul_interleaved_ref(ref)
         assert got.shape == (M, N // 2) and (got.float() - want).abs().max() <= 8e-3 * want.abs().max() + 1e-6
+    # the same pair of CTAs on tiles of 192 and 128 columns (K in whole pairs of k-blocks only; other K are refused)
+    for tile_n in (1192, 1128):
+        if K % 64 != 0 or K < 128:
+            with pytest.raises(k.KernelError, match="K % 64"):
+                k.gemm_sm100(a, w, bias=bias, tile_n=tile_n)
+            continue
+        got = k.gemm_sm100(a, w, bias=bias, tile_n=tile_n)
+        assert (got - ref).abs().max() <= tol, tile_n
+        got = k.gemm_sm100(a, w, bias=bias, accumulate_into=res.clone(), tile_n=tile_n)
+        assert (got - (res + ref)).abs().max() <= tol + 1e-6 * res.abs().max(), tile_n
+        if N % 2 == 0:
+            got = k.gemm_sm100(a, w, bias=bias, epilogue="swiglu", tile_n=tile_n)
+            assert (got.float() - want).abs().max() <= 8e-3 * want.abs().max() + 1e-6, tile_n
     k.check_kernel_status()
     with pytest.raises(k.KernelError, match="two-CTA"):
         k.gemm_sm100(_rand(64, 64), _rand(128, 64), tile_n=512)
