@@ -840,7 +840,10 @@ template <int NT> struct SkinnyCfg {                       // NT: token box (UMM
     // one k-block of W (`rows` weight rows of 128 bytes) and of the tokens
     static constexpr int block_bytes(int rows) { return rows * BK * 2 + NT * BK * 2; }
     static constexpr int kPartialBytes = NT * BM * 4;
-    static constexpr int kMaxGroup = NT <= 64 ? 4 : 2;      // 128 tokens: a k-block is 32 KB, two of them per stage
+    // k-blocks per TMA instruction at most: four at 16 tokens (three stages of 72 KB); at 32 and 64 tokens a k-block is
+    // 20 / 24 KB and groups of four leave room for two stages only: up to three (in practice two, which divide the
+    // k-blocks evenly: five / four stages) measured 1.5 % faster per step; 128 tokens: a k-block is 32 KB, two per stage
+    static constexpr int kMaxGroup = NT <= 16 ? 4 : (NT <= 64 ? 3 : 2);
     static constexpr int kMaxStages = 12;
     static constexpr int max_stages(int group, int rows) {
         const int fit = (kSmemLimit - 2048 - kPartialBytes) / (group * block_bytes(rows));
@@ -958,7 +961,7 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 const uint64_t x_desc = umma_desc_k_sw128(smem_u32(x_tiles + s * x_bytes));
                 const int here = min(g, my_kb - i * g);            // k-blocks of this group inside my range
 #pragma unroll
-                for (int jj = 0; jj < C::kMaxGroup / 2; ++jj) {
+                for (int jj = 0; jj < (C::kMaxGroup + 1) / 2; ++jj) {
                     const int j = 2 * jj + who;
                     if (j >= here) break;
 #pragma unroll
