@@ -223,20 +223,42 @@ class ModelRunner:
             self.manager.release_out_of_window(e.req_id)
         return out
 
-    def decode_step_async(self, entries, from_previous=False):
-        """decode_step whose greedy tokens are not waited for: returns a handle whose ``tokens()`` blocks until
-        the step has run and gives them as a list.  ``from_previous``: take the input tokens from the previous
-        decode step's greedy tokens on the device (the entries' token ids are placeholders)."""
-        _, greedy = self.decode_step(entries, tokens_on_device=from_previous)
+    def decode_step_async(self, entries, from_previous=False, sampling=None):
+        """decode_step whose tokens are not waited for: returns a handle whose ``tokens()`` blocks until the step has
+        run and gives them as a list.  ``from_previous``: take the input tokens from the previous decode step's
+        tokens on the device (the entries' token ids are placeholders).  ``sampling``: None, the tokens are the
+        greedy ones of the graph; or one (temperature, top_k, top_p, u, greedy) per entry: rows that are not greedy
+        draw their token on the device with the uniform number u that the request's generator gave (the sampling
+        kernel of ``forge_b200.sampling``, so a request draws what it would draw with its logits on the host)."""
+        logits, greedy = self.decode_step(entries, tokens_on_device=from_previous)
         S = greedy.numel()
         ring = self._token_rings.get(S)
         if ring is None:
             # a handle is read at the latest after the NEXT step has been launched: four buffers are plenty
             ring = self._token_rings[S] = {"bufs": [torch.empty(S, dtype=torch.int32, pin_memory=True) for _ in range(4)],
-                                           "events": [torch.cuda.Event() for _ in range(4)], "pos": 0}
+                                           "events": [torch.cuda.Event() for _ in range(4)], "pos": 0,
+                                           "params": [torch.empty(4, S, dtype=torch.float32, pin_memory=True) for _ in range(4)],
+                                           "params_dev": torch.empty(4, S, dtype=torch.float32, device=self.device),
+                                           "drawn": [torch.empty(S, dtype=torch.int32, device=self.device) for _ in range(2)]}
         i = ring["pos"]
         ring["pos"] = (i + 1) % len(ring["bufs"])
-        ring["bufs"][i].copy_(greedy, non_blocking=True)
+        chosen = greedy
+        if sampling is not None and not all(g for _, _, _, _, g in sampling):
+            from .. import kernels
+            host = ring["params"][i]                    # free: its handle was read before this slot came round again
+            host[0] = torch.tensor([t for t, _, _, _, _ in sampling])
+            host[1] = torch.tensor([p for _, _, p, _, _ in sampling])
+            host[2] = torch.tensor([u for _, _, _, u, _ in sampling])
+            host[3].view(torch.int32).copy_(torch.tensor([k for _, k, _, _, _ in sampling], dtype=torch.int32))
+            dev = ring["params_dev"]
+            dev.copy_(host, non_blocking=True)
+            chosen = ring["drawn"][i % 2]
+            kernels.sample(logits, dev[0], dev[3].view(torch.int32), dev[1], dev[2], out=chosen)
+            if any(g for _, _, _, _, g in sampling):    # greedy rows keep the graph's argmax (lowest index wins a tie)
+                mask = torch.tensor([bool(g) for _, _, _, _, g in sampling]).to(self.device, non_blocking=True)
+                torch.where(mask, greedy, chosen, out=chosen)
+            self._last_greedy = chosen                  # what the next step takes its input tokens from
+        ring["bufs"][i].copy_(chosen, non_blocking=True)
         ring["events"][i].record()
         return PendingTokens(ring["bufs"][i], ring["events"][i])
 
@@ -268,7 +290,7 @@ class ModelRunner:
 
 
 class PendingTokens:
-    """Greedy tokens of a decode step on their way to pinned host memory."""
+    """The tokens of a decode step on their way to pinned host memory."""
 
     def __init__(self, host, event):
         self.host, self.event = host, event

@@ -14,9 +14,11 @@ requests Waiting -> Prefilling -> Decoding -> Finished | Failed with finish_reas
     the queue; a request that cannot make progress even alone fails with "error:out_of_pages" (the
     reference logs "cache overflow" and carries on, src/inference/kv_cache.cpp:629-633);
   * every request has its own sampler state;
-  * greedy decoding runs one step AHEAD of the host: while the same requests keep decoding, step k is launched
-    with its input tokens taken on the device from step k-1's argmax, and only then are step k-1's tokens read
-    and handed to their requests.  A request that turns out to have ended (eos, a stop token) has then computed
+  * decoding runs one step AHEAD of the host: while the same requests keep decoding, step k is launched with its
+    input tokens taken on the device from step k-1's tokens (the argmax of the graph, or the draw of the sampling
+    kernel with the uniform number that the request's generator gave at launch), and only then are step k-1's
+    tokens read and handed to their requests.  Requests with a repeat penalty wait for their tokens instead (the
+    penalty needs the history, which the host keeps).  A request that turns out to have ended (eos, a stop token) has then computed
     one token too many, which is dropped; anything else that would change the batch (a request about to reach
     its length, an admission, pages running short) first waits for the step in flight.
 """
@@ -258,7 +260,14 @@ class RequestScheduler:
         try:
             if ahead:
                 self.runner.validate(entries)
-                handle = self.runner.decode_step_async(entries, from_previous=self._inflight is not None)
+                sampling = None
+                if not all(self._greedy_only(r) for r in rows):
+                    # the uniform number of a row that samples comes from the request's own generator, now, in the
+                    # order in which the request's tokens are drawn; the draw itself happens on the device
+                    sampling = [(1.0, 1, 1.0, 0.5, True) if r.sampler.config.greedy else
+                                (float(r.sampler.config.temperature), int(r.sampler.config.top_k), float(r.sampler.config.top_p),
+                                 r.sampler.rng.uniform(), False) for r in rows]
+                handle = self.runner.decode_step_async(entries, from_previous=self._inflight is not None, sampling=sampling)
             elif decode_only:
                 self.runner.validate(entries)
                 logits, greedy = self.runner.decode_step(entries)
@@ -301,10 +310,17 @@ class RequestScheduler:
     def _greedy_only(r):
         return r.sampler.config.greedy and r.sampler.config.repeat_penalty == 1.0
 
+    @staticmethod
+    def _drawn_on_device(r):
+        """Greedy, or temperature / top-k / top-p sampling: the token can be chosen on the device from the logits and a
+        uniform number known beforehand.  A repeat penalty needs the request's history, which the host keeps."""
+        return r.sampler.config.repeat_penalty == 1.0
+
     def _plan_runs_ahead(self, plan):
-        """A step of single decoded tokens, all greedy, on a runner that can leave the tokens on the device."""
+        """A step of single decoded tokens whose choice needs nothing from the host but numbers known beforehand, on a
+        runner that can leave the tokens on the device."""
         return (getattr(self.runner, "cuda_graphs", False) and hasattr(self.runner, "decode_step_async")
-                and all(n == 1 and wants and r.status == RequestStatus.Decoding and self._greedy_only(r)
+                and all(n == 1 and wants and r.status == RequestStatus.Decoding and self._drawn_on_device(r)
                         for r, _, n, wants in plan))
 
     def _can_run_ahead(self):

@@ -87,7 +87,7 @@ def argmax_ref(logits):
 def sample_probabilities_ref(row, temperature, top_k, top_p):
     """The reference's pipeline (src/inference/sampler.cpp:197-316) in float64; returns kept probabilities."""
     p = torch.softmax(row.double() / temperature, dim=0)
-    if top_k > 0:
+    if 0 < top_k < p.numel():                       # k at least the vocabulary: nothing is cut
         kth = torch.topk(p, top_k).values[-1]
         p = torch.where(p >= kth, p, torch.zeros_like(p))
         p = p / p.sum()

@@ -161,12 +161,15 @@ def test_argmax_lowest_index_wins():
     assert got[0].item() == 17
 
 
+@pytest.mark.parametrize("V", [1531, 32000, 60000])      # keys in shared memory (a partial chunk; whole chunks of 32), keys in global memory
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 1.0), (0.8, 40, 1.0), (1.3, 0, 0.9),
-                                                      (0.7, 40, 0.9), (1.0, 1, 1.0)])
-def test_sample_picks_the_token_whose_interval_holds_u(temperature, top_k, top_p):
+                                                      (0.7, 40, 0.9), (1.0, 1, 1.0), (0.9, 3000, 0.95)])
+def test_sample_picks_the_token_whose_interval_holds_u(temperature, top_k, top_p, V):
+    """(0.9, 3000, 0.95): more kept entries than the kernel gathers, so top-p is found digit by digit as without top-k."""
     k = _k()
-    R_, V = 16, 1531
+    R_ = 16
     logits = _rand(R_, V, scale=3.0)
+    logits[3, 100:140] = logits[3].max() + 0.5             # ties at the top: all of them are kept
     us = torch.linspace(0.01, 0.99, R_)
     got = k.sample(logits, torch.full((R_,), temperature, device=DEV), torch.full((R_,), top_k, dtype=torch.int32, device=DEV),
                    torch.full((R_,), top_p, device=DEV), us.to(DEV))

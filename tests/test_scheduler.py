@@ -184,11 +184,13 @@ class FakeAheadRunner(FakeRunner):
         super().__init__(**kw)
         self.device_tokens = None
         self.from_previous = 0
+        self.sampling = []
 
     def validate(self, entries):
         assert len({e.req_id for e in entries}) == len(entries)
 
-    def decode_step_async(self, entries, from_previous=False):
+    def decode_step_async(self, entries, from_previous=False, sampling=None):
+        self.sampling.append(sampling)
         toks = [e.tokens[0] for e in entries]
         if from_previous:
             assert self.device_tokens is not None and len(self.device_tokens) == len(entries)
@@ -245,6 +247,35 @@ def test_running_ahead_gives_the_same_tokens_and_reasons():
     # was in one more step than it has tokens
     in_steps = sum(1 for step in r.steps for e in step if e[0] == 0)
     assert in_steps == len(ahead[0][0]) + 1
+
+
+def test_sampling_requests_run_ahead_too_with_their_own_uniform_numbers():
+    """Temperature / top-k / top-p need nothing from the host but a uniform number, which the request's generator
+    gives when the step is launched: such requests run ahead like greedy ones, each row with its own parameters (a
+    greedy row beside them keeps its argmax); a repeat penalty needs the history on the host and waits for its tokens."""
+    r = FakeAheadRunner(pages=32)
+    s = RequestScheduler(r, max_num_seqs=4, max_tokens_per_step=64, sample_fn=next_token)
+    a = s.submit(prompt_tokens=[10], max_new_tokens=8, sampler_config=SamplerConfig(temperature=0.8, top_k=40, top_p=0.9, seed=3))
+    b = s.submit(prompt_tokens=[20], max_new_tokens=8, sampler_config=GREEDY)
+    c = s.submit(prompt_tokens=[30], max_new_tokens=8, sampler_config=SamplerConfig(temperature=0.5, seed=4))
+    done = {x.request_id: x for x in s.run()}
+    assert all(len(done[i].output_tokens) == 8 for i in (a, b, c))
+    assert r.from_previous >= 4
+    given = [x for x in r.sampling if x is not None]
+    assert len(given) >= 5
+    want_a, want_c = XorShift64(3), XorShift64(4)
+    for step in given:
+        (ta, ka, pa, ua, ga), (tb, kb, pb, ub, gb), (tc, kc, pc, uc, gc) = step
+        assert (ta, ka, pa, ga) == (0.8, 40, 0.9, False) and ua == want_a.uniform()
+        assert gb and kb == 1
+        assert (tc, kc, pc, gc) == (0.5, 0, 1.0, False) and uc == want_c.uniform()
+    # with a repeat penalty in the batch nothing runs ahead
+    r2 = FakeAheadRunner(pages=32)
+    s2 = RequestScheduler(r2, max_num_seqs=4, max_tokens_per_step=64, sample_fn=next_token)
+    s2.submit(prompt_tokens=[10], max_new_tokens=6, sampler_config=SamplerConfig(temperature=0.8, repeat_penalty=1.1))
+    r2.decode_step = lambda entries: (r2.step(entries), None)
+    s2.run()
+    assert r2.sampling == [] and r2.from_previous == 0
 
 
 def test_running_ahead_waits_before_admissions_and_when_pages_run_short():
