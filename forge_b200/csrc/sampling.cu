@@ -106,6 +106,39 @@ constexpr int kMaxSmemKeys = 49152;
 constexpr int kListCap = 2048;
 #define KEY_AT(i) ((i) + ((i) >> 5))
 
+// The repeat penalty from a history that lives on the device: counts [slots, V] holds, per request slot, how often
+// each token was generated; a row's logits are penalised once per occurrence, as in repeat_penalty_kernel.  With the
+// history on the device a step's tokens can be drawn, and the next step launched, before the host has seen them.
+__global__ void history_penalty_kernel(float* __restrict__ logits, const int32_t* __restrict__ counts,
+                                       const int32_t* __restrict__ slot_of_row, const float* __restrict__ penalty, int V) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int r = blockIdx.y;
+    const float pen = penalty[r];
+    if (pen == 1.0f) return;
+    const int32_t* hist = counts + (size_t)slot_of_row[r] * V;
+    float* row = logits + (size_t)r * V;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
+        const int c = hist[i];
+        if (c > 0) {
+            float v = row[i];
+            for (int k = 0; k < c; ++k) v = v > 0.f ? v / pen : v * pen;
+            row[i] = v;
+        }
+    }
+}
+
+// counts[slot of row r][tokens[r]] += 1 for the rows whose requests have a penalty (one thread per row).
+__global__ void history_add_kernel(int32_t* __restrict__ counts, const int32_t* __restrict__ slot_of_row,
+                                   const int32_t* __restrict__ tokens, const float* __restrict__ penalty, int R, int V) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R || penalty[r] == 1.0f) return;
+    const int t = tokens[r];
+    if (t >= 0 && t < V) counts[(size_t)slot_of_row[r] * V + t] += 1;      // a slot belongs to one row of a step
+}
+
 template <bool SMEM>
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
@@ -378,6 +411,23 @@ extern "C" int forge_repeat_penalty(float* logits, const int32_t* tokens, const 
     if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "repeat_penalty: bad sizes R=%d V=%d", R, V);
     if (R == 0) return FORGE_OK;
     return forge::check_launch("repeat_penalty", forge::launch(repeat_penalty_kernel, dim3(R), dim3(256), 0, stream, 1, logits, tokens, counts, offsets, penalty, V));
+}
+
+// counts int32 [slots, V]; slot_of_row int32 [R]; penalty fp32 [R] (1 = none).
+extern "C" int forge_history_penalty(float* logits, const int32_t* counts, const int32_t* slot_of_row, const float* penalty,
+                                     int R, int V, cudaStream_t stream) {
+    if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "history_penalty: bad sizes R=%d V=%d", R, V);
+    if (R == 0) return FORGE_OK;
+    return forge::check_launch("history_penalty", forge::launch(history_penalty_kernel, dim3((V + 1023) / 1024, R), dim3(256), 0, stream, 1,
+                                                                logits, counts, slot_of_row, penalty, V));
+}
+
+extern "C" int forge_history_add(int32_t* counts, const int32_t* slot_of_row, const int32_t* tokens, const float* penalty,
+                                 int R, int V, cudaStream_t stream) {
+    if (R < 0 || V <= 0) return forge::fail(FORGE_ERR_ARG, "history_add: bad sizes R=%d V=%d", R, V);
+    if (R == 0) return FORGE_OK;
+    return forge::check_launch("history_add", forge::launch(history_add_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, 1,
+                                                            counts, slot_of_row, tokens, penalty, R, V));
 }
 
 // temperature[r] must be > 0 (the caller routes temperature <= 0 to forge_argmax).

@@ -223,13 +223,19 @@ class ModelRunner:
             self.manager.release_out_of_window(e.req_id)
         return out
 
-    def decode_step_async(self, entries, from_previous=False, sampling=None):
+    device_history = True      # repeat penalties can be applied from a history kept on the device (decode_step_async)
+
+    def decode_step_async(self, entries, from_previous=False, sampling=None, history=None):
         """decode_step whose tokens are not waited for: returns a handle whose ``tokens()`` blocks until the step has
         run and gives them as a list.  ``from_previous``: take the input tokens from the previous decode step's
         tokens on the device (the entries' token ids are placeholders).  ``sampling``: None, the tokens are the
-        greedy ones of the graph; or one (temperature, top_k, top_p, u, greedy) per entry: rows that are not greedy
-        draw their token on the device with the uniform number u that the request's generator gave (the sampling
-        kernel of ``forge_b200.sampling``, so a request draws what it would draw with its logits on the host)."""
+        greedy ones of the graph; or one (temperature, top_k, top_p, u, greedy, repeat_penalty) per entry: rows that
+        are not greedy draw their token on the device with the uniform number u that the request's generator gave (the
+        sampling kernel of ``forge_b200.sampling``, so a request draws what it would draw with its logits on the host).
+        Rows with a repeat penalty are penalised from a history of generated tokens that is kept on the device, one row
+        of counts per request slot, and the step adds its token to it; ``history`` (one Counter or None per entry)
+        replaces the slots' rows first: the caller gives it when the host's histories are complete, i.e. at the first
+        of a run of such steps."""
         logits, greedy = self.decode_step(entries, tokens_on_device=from_previous)
         S = greedy.numel()
         ring = self._token_rings.get(S)
@@ -237,30 +243,58 @@ class ModelRunner:
             # a handle is read at the latest after the NEXT step has been launched: four buffers are plenty
             ring = self._token_rings[S] = {"bufs": [torch.empty(S, dtype=torch.int32, pin_memory=True) for _ in range(4)],
                                            "events": [torch.cuda.Event() for _ in range(4)], "pos": 0,
-                                           "params": [torch.empty(4, S, dtype=torch.float32, pin_memory=True) for _ in range(4)],
-                                           "params_dev": torch.empty(4, S, dtype=torch.float32, device=self.device),
+                                           "params": [torch.empty(6, S, dtype=torch.float32, pin_memory=True) for _ in range(4)],
+                                           "params_dev": torch.empty(6, S, dtype=torch.float32, device=self.device),
                                            "drawn": [torch.empty(S, dtype=torch.int32, device=self.device) for _ in range(2)]}
         i = ring["pos"]
         ring["pos"] = (i + 1) % len(ring["bufs"])
         chosen = greedy
-        if sampling is not None and not all(g for _, _, _, _, g in sampling):
+        penalised = sampling is not None and any(pen != 1.0 for *_, pen in sampling)
+        if sampling is not None and (penalised or not all(g for _, _, _, _, g, _ in sampling)):
             from .. import kernels
             host = ring["params"][i]                    # free: its handle was read before this slot came round again
-            host[0] = torch.tensor([t for t, _, _, _, _ in sampling])
-            host[1] = torch.tensor([p for _, _, p, _, _ in sampling])
-            host[2] = torch.tensor([u for _, _, _, u, _ in sampling])
-            host[3].view(torch.int32).copy_(torch.tensor([k for _, k, _, _, _ in sampling], dtype=torch.int32))
+            host[0] = torch.tensor([t for t, *_ in sampling])
+            host[1] = torch.tensor([p for _, _, p, *_ in sampling])
+            host[2] = torch.tensor([u for _, _, _, u, *_ in sampling])
+            host[3].view(torch.int32).copy_(torch.tensor([k for _, k, *_ in sampling], dtype=torch.int32))
+            host[4] = torch.tensor([pen for *_, pen in sampling])
+            host[5].view(torch.int32).copy_(torch.tensor([self.manager.slot(e.req_id) for e in entries], dtype=torch.int32))
             dev = ring["params_dev"]
             dev.copy_(host, non_blocking=True)
+            slots_dev = dev[5].view(torch.int32)
+            if penalised:
+                counts = self._history_counts(logits.shape[1])
+                if history is not None:
+                    for e, h in zip(entries, history):
+                        if h is not None:
+                            row = counts[self.manager.slot(e.req_id)]
+                            row.zero_()
+                            if h:
+                                row[torch.tensor(list(h.keys()), device=self.device)] = \
+                                    torch.tensor(list(h.values()), dtype=torch.int32, device=self.device)
+                kernels.history_penalty(logits, counts, slots_dev, dev[4])
+                greedy = kernels.argmax(logits)         # of the penalised logits
+            all_greedy = all(g for _, _, _, _, g, _ in sampling)
             chosen = ring["drawn"][i % 2]
-            kernels.sample(logits, dev[0], dev[3].view(torch.int32), dev[1], dev[2], out=chosen)
-            if any(g for _, _, _, _, g in sampling):    # greedy rows keep the graph's argmax (lowest index wins a tie)
-                mask = torch.tensor([bool(g) for _, _, _, _, g in sampling]).to(self.device, non_blocking=True)
-                torch.where(mask, greedy, chosen, out=chosen)
+            if all_greedy:
+                chosen.copy_(greedy)
+            else:
+                kernels.sample(logits, dev[0], dev[3].view(torch.int32), dev[1], dev[2], out=chosen)
+                if any(g for _, _, _, _, g, _ in sampling):      # greedy rows keep the argmax (lowest index wins a tie)
+                    mask = torch.tensor([bool(g) for _, _, _, _, g, _ in sampling]).to(self.device, non_blocking=True)
+                    torch.where(mask, greedy, chosen, out=chosen)
+            if penalised:
+                kernels.history_add(counts, slots_dev, chosen, dev[4])
             self._last_greedy = chosen                  # what the next step takes its input tokens from
         ring["bufs"][i].copy_(chosen, non_blocking=True)
         ring["events"][i].record()
         return PendingTokens(ring["bufs"][i], ring["events"][i])
+
+    def _history_counts(self, vocab):
+        """int32 [request slots, vocabulary]: how often each request has generated each token (made at first use)."""
+        if getattr(self, "_history", None) is None:
+            self._history = torch.zeros(self.manager.max_requests, vocab, dtype=torch.int32, device=self.device)
+        return self._history
 
     def check_status(self):
         """Reads the device error word (synchronises); raises if a kernel flagged a problem."""

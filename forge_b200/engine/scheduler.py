@@ -17,8 +17,8 @@ requests Waiting -> Prefilling -> Decoding -> Finished | Failed with finish_reas
   * decoding runs one step AHEAD of the host: while the same requests keep decoding, step k is launched with its
     input tokens taken on the device from step k-1's tokens (the argmax of the graph, or the draw of the sampling
     kernel with the uniform number that the request's generator gave at launch), and only then are step k-1's
-    tokens read and handed to their requests.  Requests with a repeat penalty wait for their tokens instead (the
-    penalty needs the history, which the host keeps).  A request that turns out to have ended (eos, a stop token) has then computed
+    tokens read and handed to their requests.  A repeat penalty is applied from a history of generated tokens
+    that the runner keeps on the device (uploaded from the host's at the first of a run of such steps).  A request that turns out to have ended (eos, a stop token) has then computed
     one token too many, which is dropped; anything else that would change the batch (a request about to reach
     its length, an admission, pages running short) first waits for the step in flight.
 """
@@ -260,14 +260,21 @@ class RequestScheduler:
         try:
             if ahead:
                 self.runner.validate(entries)
-                sampling = None
+                sampling = history = None
                 if not all(self._greedy_only(r) for r in rows):
                     # the uniform number of a row that samples comes from the request's own generator, now, in the
                     # order in which the request's tokens are drawn; the draw itself happens on the device
-                    sampling = [(1.0, 1, 1.0, 0.5, True) if r.sampler.config.greedy else
+                    sampling = [(1.0, 1, 1.0, 0.5, True, float(r.sampler.config.repeat_penalty)) if r.sampler.config.greedy else
                                 (float(r.sampler.config.temperature), int(r.sampler.config.top_k), float(r.sampler.config.top_p),
-                                 r.sampler.rng.uniform(), False) for r in rows]
-                handle = self.runner.decode_step_async(entries, from_previous=self._inflight is not None, sampling=sampling)
+                                 r.sampler.rng.uniform(), False, float(r.sampler.config.repeat_penalty)) for r in rows]
+                    if self._inflight is None and any(r.sampler.config.repeat_penalty != 1.0 for r in rows):
+                        # the first of a run of steps: the host's histories are complete and go to the device, which
+                        # keeps them up to date itself from here on
+                        history = [r.sampler.history if r.sampler.config.repeat_penalty != 1.0 else None for r in rows]
+                if history is not None:
+                    handle = self.runner.decode_step_async(entries, from_previous=False, sampling=sampling, history=history)
+                else:
+                    handle = self.runner.decode_step_async(entries, from_previous=self._inflight is not None, sampling=sampling)
             elif decode_only:
                 self.runner.validate(entries)
                 logits, greedy = self.runner.decode_step(entries)
@@ -310,11 +317,11 @@ class RequestScheduler:
     def _greedy_only(r):
         return r.sampler.config.greedy and r.sampler.config.repeat_penalty == 1.0
 
-    @staticmethod
-    def _drawn_on_device(r):
+    def _drawn_on_device(self, r):
         """Greedy, or temperature / top-k / top-p sampling: the token can be chosen on the device from the logits and a
-        uniform number known beforehand.  A repeat penalty needs the request's history, which the host keeps."""
-        return r.sampler.config.repeat_penalty == 1.0
+        uniform number known beforehand.  A repeat penalty needs the request's history: only a runner that keeps
+        one on the device (``device_history``) can apply it without the host."""
+        return r.sampler.config.repeat_penalty == 1.0 or getattr(self.runner, "device_history", False)
 
     def _plan_runs_ahead(self, plan):
         """A step of single decoded tokens whose choice needs nothing from the host but numbers known beforehand, on a

@@ -42,6 +42,8 @@ _SIGNATURES = {
         "forge_argmax": [_P, _P, _I, _I, _P],
         "forge_repeat_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
         "forge_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "forge_history_penalty": [_P, _P, _P, _P, _I, _I, _P],
+        "forge_history_add": [_P, _P, _P, _P, _I, _I, _P],
     },
     "gemm_sm100": {
         "forge_gemm_sm100": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -598,6 +600,26 @@ def repeat_penalty(logits, tokens, counts, offsets, penalty):
                                          _need(counts, "counts", torch.int32), _need(offsets, "offsets", torch.int32),
                                          _need(penalty, "penalty", torch.float32), R, V, _stream()), "repeat_penalty")
     return logits
+
+
+def history_penalty(logits, counts, slot_of_row, penalty):
+    """The repeat penalty with the history on the device: ``counts`` int32 [slots, V] (how often each token was
+    generated, per request slot), ``slot_of_row`` int32 [R], ``penalty`` fp32 [R] (1 = none).  In place."""
+    lib = library("core")
+    R, V = logits.shape
+    _check(lib, lib.forge_history_penalty(_need(logits, "logits", torch.float32, 2), _need(counts, "counts", torch.int32, 2),
+                                          _need(slot_of_row, "slot_of_row", torch.int32), _need(penalty, "penalty", torch.float32),
+                                          R, V, _stream()), "history_penalty")
+    return logits
+
+
+def history_add(counts, slot_of_row, tokens, penalty):
+    """counts[slot_of_row[r], tokens[r]] += 1 for the rows with a penalty."""
+    lib = library("core")
+    R, V = tokens.numel(), counts.shape[1]
+    _check(lib, lib.forge_history_add(_need(counts, "counts", torch.int32, 2), _need(slot_of_row, "slot_of_row", torch.int32),
+                                      _need(tokens, "tokens", torch.int32), _need(penalty, "penalty", torch.float32), R, V,
+                                      _stream()), "history_add")
 
 
 def sample(logits, temperature, top_k, top_p, u, out=None):

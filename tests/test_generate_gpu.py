@@ -336,3 +336,37 @@ def test_long_contexts_decode_through_the_streamed_attention(name, tmp_path, mon
         assert done[rid].finish_reason == "length" and len(done[rid].output_tokens) == 10
         assert_greedy_follows_plain(plain.logits, p, done[rid].output_tokens, TOL["bfloat16"], f"request of {len(p)} tokens")
     model.runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeat_penalty_from_the_history_on_the_device(tiny, dtype):
+    """Requests with a repeat penalty decode one step ahead of the host, penalised from a history that the runner keeps
+    on the device: they generate exactly what they generate when every step waits for its tokens and the host applies
+    the penalty (the same logits, the same arithmetic, the same uniform numbers).  Greedy with a penalty, sampling with
+    one, and a request without, in one batch; few pages, so requests are preempted and their histories go to the
+    device again."""
+    import forge_b200 as forge
+    name, d, plain = tiny
+    V = TINY[name]["vocab_size"]
+    prompts = [random_tokens(n, V, seed=70 + i) for i, n in enumerate([12, 30, 7, 21, 16])]
+    configs = [forge.SamplerConfig(temperature=0.9, top_k=50, repeat_penalty=1.3, seed=5),
+               forge.SamplerConfig(do_sample=False, repeat_penalty=1.2),
+               forge.SamplerConfig(temperature=0.7, seed=6),
+               forge.SamplerConfig(temperature=1.1, top_p=0.9, repeat_penalty=1.15, seed=7),
+               forge.SamplerConfig(do_sample=False)]
+    outs = []
+    for on_device in (True, False):
+        model = forge.Model(d, dtype=dtype, max_num_seqs=4, cache_tokens=224, max_tokens_per_step=32, block_size=16)
+        model.runner.device_history = on_device
+        sched = forge.RequestScheduler(model, max_num_seqs=4)
+        ids = [sched.submit(p, max_new_tokens=40, sampler_config=c) for p, c in zip(prompts, configs)]
+        done = {r.request_id: r for r in sched.run()}
+        outs.append([done[i].output_tokens for i in ids])
+        assert all(done[i].finish_reason == "length" for i in ids)
+        if on_device:
+            assert sched.num_preemptions >= 1, "the cache was meant to be too small"
+            assert getattr(model.runner, "_history", None) is not None, "the penalised requests were meant to run ahead"
+        model.runner.check_status()
+    assert outs[0] == outs[1]
+    # the penalty did something: the greedy request with a penalty repeats itself less than greedy alone would
+    assert len(set(outs[0][1])) >= len(set(outs[0][4])) or len(set(outs[0][1])) > 20

@@ -265,17 +265,36 @@ def test_sampling_requests_run_ahead_too_with_their_own_uniform_numbers():
     assert len(given) >= 5
     want_a, want_c = XorShift64(3), XorShift64(4)
     for step in given:
-        (ta, ka, pa, ua, ga), (tb, kb, pb, ub, gb), (tc, kc, pc, uc, gc) = step
-        assert (ta, ka, pa, ga) == (0.8, 40, 0.9, False) and ua == want_a.uniform()
+        (ta, ka, pa, ua, ga, na), (tb, kb, pb, ub, gb, nb), (tc, kc, pc, uc, gc, nc) = step
+        assert (ta, ka, pa, ga, na) == (0.8, 40, 0.9, False, 1.0) and ua == want_a.uniform()
         assert gb and kb == 1
-        assert (tc, kc, pc, gc) == (0.5, 0, 1.0, False) and uc == want_c.uniform()
-    # with a repeat penalty in the batch nothing runs ahead
+        assert (tc, kc, pc, gc, nc) == (0.5, 0, 1.0, False, 1.0) and uc == want_c.uniform()
+    # with a repeat penalty in the batch nothing runs ahead on a runner that keeps no history on the device
     r2 = FakeAheadRunner(pages=32)
     s2 = RequestScheduler(r2, max_num_seqs=4, max_tokens_per_step=64, sample_fn=next_token)
     s2.submit(prompt_tokens=[10], max_new_tokens=6, sampler_config=SamplerConfig(temperature=0.8, repeat_penalty=1.1))
     r2.decode_step = lambda entries: (r2.step(entries), None)
     s2.run()
     assert r2.sampling == [] and r2.from_previous == 0
+    # and on one that does, it runs ahead: the histories go along with the first step of a run, and only then
+    r3 = FakeAheadRunner(pages=32)
+    r3.device_history = True
+    r3.histories = []
+    plain_async = r3.decode_step_async
+
+    def with_history(entries, from_previous=False, sampling=None, history=None):
+        r3.histories.append(None if history is None else [None if h is None else dict(h) for h in history])
+        return plain_async(entries, from_previous=from_previous, sampling=sampling)
+    r3.decode_step_async = with_history
+    s3 = RequestScheduler(r3, max_num_seqs=4, max_tokens_per_step=64, sample_fn=next_token)
+    s3.submit(prompt_tokens=[10], max_new_tokens=7, sampler_config=SamplerConfig(temperature=0.8, repeat_penalty=1.1))
+    s3.submit(prompt_tokens=[50], max_new_tokens=7, sampler_config=GREEDY)
+    done3 = s3.run()
+    assert all(len(x.output_tokens) == 7 for x in done3) and r3.from_previous >= 3
+    given3 = [h for h in r3.histories if h is not None]
+    assert len(given3) >= 1 and given3[0][1] is None and isinstance(given3[0][0], dict)      # the penalised row's history only
+    assert r3.histories[1] is None                                                              # the run's later steps bring none
+    assert all(step[0][5] == 1.1 and step[1][5] == 1.0 for step in r3.sampling if step is not None)
 
 
 def test_running_ahead_waits_before_admissions_and_when_pages_run_short():
