@@ -303,8 +303,8 @@ def test_command_line_benchmark(tiny):
     assert "Benchmark complete" in proc.stdout
 
 
-@pytest.mark.parametrize("name", ["C", "D"])
-def test_long_contexts_decode_through_the_streamed_attention(name, tmp_path, monkeypatch):
+@pytest.mark.parametrize("name,checks", [("C", False), ("D", False), ("C", True)])
+def test_long_contexts_decode_through_the_streamed_attention(name, checks, tmp_path, monkeypatch):
     """Requests of more than 2,048 tokens beside a short one, decoded together through the CUDA graph: the graph's
     context bucket (4,096) sends the step's attention to the kernel that streams the cache through a TMA ring, with
     clusters of CTAs per request; every token must follow the plain implementation.  Head sizes 64 and 128."""
@@ -314,6 +314,8 @@ def test_long_contexts_decode_through_the_streamed_attention(name, tmp_path, mon
     from forge_b200.weights import write_random_model
     from helpers import STDS
     from plain.llama import PlainLlama
+    if checks:                                   # the same under the build that tests every page id and slot before use
+        monkeypatch.setenv("FORGE_CHECKS", "1")
     cfg = dict(TINY[name], max_position_embeddings=4096)
     d = str(tmp_path / "long")
     write_random_model(config_from_dict(cfg), d, seed=11, **STDS[name])
@@ -336,6 +338,9 @@ def test_long_contexts_decode_through_the_streamed_attention(name, tmp_path, mon
         assert done[rid].finish_reason == "length" and len(done[rid].output_tokens) == 10
         assert_greedy_follows_plain(plain.logits, p, done[rid].output_tokens, TOL["bfloat16"], f"request of {len(p)} tokens")
     model.runner.check_status()
+    if checks:
+        assert model.runner.first_bad is not None and int(model.runner.status.item()) == 0
+        assert model.runner.first_bad.tolist() == [0, 0, 0]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
