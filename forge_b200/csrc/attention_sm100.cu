@@ -19,6 +19,10 @@
 // its registers to the second (setmaxnreg).  With head size 64 two such CTAs fit an SM (99 KB of shared memory,
 // 256 TMEM columns each); with 128 one does (163 KB).  Tiles are listed longest first and the kv heads of a tile are neighbouring CTAs, so the
 // long tiles of all heads start in the first wave.
+// A step with fewer tiles than the GPU has places for CTAs (a short portion on a long context) may list a tile several
+// times, each entry with a share of the tile's key tiles (``tile_cut``): such a CTA leaves its sums unnormalised in
+// fp32 with the row's reference exponent and sum, and a second kernel adds a tile's shares up in the order of the
+// shares.
 //   s_j = (q . k_j) * scale for keys max(0, p - window + 1) <= j <= p of the row's position p;
 //   o = sum_j softmax(s)_j v_j        (formulas of src/operators/cuda/cuda_flash_attn.cu:154-248)
 // Needs G <= 128, 64 % page_size == 0 and page_size >= 8; everything else is served by attention_mma.cu.
@@ -58,6 +62,9 @@ struct AttnTcParams {
     const int32_t* block_table;   // [S, max_pages]
     const int32_t* tile_req;      // [tiles]
     const int32_t* tile_row0;     // [tiles] first row (token * G + head) of the tile within its request
+    const int32_t* tile_cut;      // [tiles][3] or null: this entry's share of the tile's keys (share, shares, first slot)
+    float* part_o;                // [slots][NKV][128][HD] unnormalised sums of the entries that share a tile
+    float* part_ml;               // [slots][NKV][128][2] reference exponent (exp2 domain) and sum of weights
     const int32_t* q_start;       // [S+1]
     const int32_t* ctx_before;    // [S]
     int NH, NKV, page_size, max_pages, window;
@@ -178,7 +185,16 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const int pos_lo = ctx + row0 / G, pos_hi = ctx + (row0 + rows_here - 1) / G;
     const int kv_hi = pos_hi + 1;
     const int kv_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int t_begin = kv_lo / BKV, t_end = (kv_hi + BKV - 1) / BKV;
+    // this entry's share of the tile's key tiles (all of them unless the step cut the tile's keys)
+    int share = 0, shares = 1, slot = 0;
+    if (p.tile_cut != nullptr) {
+        share = p.tile_cut[3 * tile];
+        shares = p.tile_cut[3 * tile + 1];
+        slot = p.tile_cut[3 * tile + 2] + share;
+    }
+    const int t_first = kv_lo / BKV, n_all = (kv_hi + BKV - 1) / BKV - t_first;
+    const int t_begin = t_first + (int)((long long)n_all * share / shares);
+    const int t_end = t_first + (int)((long long)n_all * (share + 1) / shares);
     const int n_iter = t_end - t_begin;
 
     // the softmax rows keep a row's 64 scores in registers; the other warpgroup runs single threads and gives
@@ -394,7 +410,26 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         }
         if (ok && n_iter > 0) ok = mbar_wait<true>(&o_done[(n_iter - 1) & 1], ((n_iter - 1) >> 1) & 1, abort, p.status, 8);
         tc_fence_after_sync();
-        if (ok && n_iter > 0) {
+        if (shares > 1) {
+            // one share of the tile's keys: the sums as they are, with the reference they were taken against
+            // (a share without a visible key, or one that gave up waiting, counts as nothing)
+            const bool have = __all_sync(0xffffffffu, ok) && n_iter > 0;
+            const size_t prow = ((size_t)slot * p.NKV + kvh) * BQ + r_local;
+            p.part_ml[prow * 2] = have ? m : -INFINITY;
+            p.part_ml[prow * 2 + 1] = have ? l : 0.f;
+            if (have) {
+                float* dst = p.part_o + prow * HD;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld_32x32b_x32(t_out + c, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(ov[i], ov[i + 1], ov[i + 2], ov[i + 3]);
+                }
+            }
+        } else if (ok && n_iter > 0) {
             // every lane takes part in the TMEM loads (they are warp-wide instructions); only valid rows store
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD;
@@ -427,12 +462,57 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     }
 }
 
+// Adds up the shares of the tiles whose keys were cut: a thread per (row, four neighbouring columns), 256 / (HD / 4)
+// rows per CTA.  The shares are walked in their order, so the sum does not depend on timing.
+//   M = max_z m_z;  o = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z
+constexpr int kMergeThreads = 256, kMaxShares = 32;
+constexpr int kMergeRows = kMergeThreads / (HD / 4);             // rows per CTA
+__global__ void __launch_bounds__(kMergeThreads)
+attention_sm100_merge_kernel(const AttnTcParams p, const int32_t* __restrict__ merge_list) {
+    forge::pdl_launch_dependents();
+    forge::pdl_wait();
+    const int mt = blockIdx.x / p.NKV, kvh = blockIdx.x % p.NKV;
+    const int G = p.NH / p.NKV;
+    const int s_req = merge_list[4 * mt], row0 = merge_list[4 * mt + 1], slot0 = merge_list[4 * mt + 2];
+    const int shares = min(merge_list[4 * mt + 3], kMaxShares);
+    const int qs0 = p.q_start[s_req], qlen = p.q_start[s_req + 1] - qs0;
+    const int rows_here = min((BQ / G) * G, qlen * G - row0);
+    const int r_local = blockIdx.y * kMergeRows + threadIdx.x / (HD / 4), c = (threadIdx.x % (HD / 4)) * 4;
+    if (r_local >= rows_here) return;
+    const size_t prow0 = ((size_t)slot0 * p.NKV + kvh) * BQ + r_local, pstep = (size_t)p.NKV * BQ;     // share z: prow0 + z * pstep
+    float M = -INFINITY;
+    for (int z = 0; z < shares; ++z) M = fmaxf(M, p.part_ml[(prow0 + z * pstep) * 2]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int z = 0; z < shares; ++z) {
+        const size_t prow = prow0 + z * pstep;
+        const float m_z = p.part_ml[prow * 2], l_z = p.part_ml[prow * 2 + 1];
+        // a share without a visible key never wrote its sums
+        const float w = m_z == -INFINITY ? 0.f : exp2f(m_z - M);
+        const float4 v = w != 0.f ? *reinterpret_cast<const float4*>(p.part_o + prow * HD + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        L += w * l_z;
+        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    const int r = row0 + r_local;
+    __nv_bfloat16* dst = p.out + (size_t)(qs0 + r / G) * p.NH * HD + (size_t)(kvh * G + r % G) * HD + c;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+}
+
 }  // namespace
 
 // q [T, NH*HD] bf16, kv cache [pages, 2, NKV, page_size, HD] bf16, out [T, NH*HD] bf16.  tile_req / tile_row0
 // list tiles of (128 / G) * G query rows (rows = tokens * G); q_start / ctx_before as for forge_paged_attention_mma.
+// tile_cut (or null) [num_tiles][3]: entry i works on share tile_cut[i][0] of tile_cut[i][1] equal shares of its tile's
+// key tiles and, with more than one share, leaves its sums in slot tile_cut[i][2] + share of part_o [slots][NKV][128][HD]
+// and part_ml [slots][NKV][128][2]; merge_list [num_merge][4] = (request, first row, first slot, shares) names the
+// tiles to add up afterwards (at most 32 shares each).
 extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* out, const int32_t* block_table,
-                                           const int32_t* tile_req, const int32_t* tile_row0, const int32_t* q_start,
+                                           const int32_t* tile_req, const int32_t* tile_row0, const int32_t* tile_cut,
+                                           void* part_o, void* part_ml, const int32_t* merge_list, int num_merge,
+                                           const int32_t* q_start,
                                            const int32_t* ctx_before, int* status, int num_tiles, int T, int num_pages,
                                            int NH, int NKV, int head_dim, int page_size, int max_pages, int window,
                                            float scale, cudaStream_t stream) {
@@ -444,6 +524,8 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
     if (!(scale > 0.f)) return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: scale %g must be positive", (double)scale);
     if (num_tiles < 0 || T <= 0 || num_pages <= 0 || max_pages <= 0)
         return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: bad sizes tiles=%d T=%d pages=%d", num_tiles, T, num_pages);
+    if (num_merge < 0 || (num_merge > 0 && (!tile_cut || !part_o || !part_ml || !merge_list)))
+        return forge::fail(FORGE_ERR_ARG, "paged_attention_sm100: %d tiles to add up need tile_cut, part_o, part_ml and merge_list", num_merge);
     if (num_tiles == 0) return FORGE_OK;
     const int G = NH / NKV;
     const char* err = nullptr;
@@ -466,11 +548,15 @@ extern "C" int forge_paged_attention_sm100(const void* q, const void* kv, void* 
                                attr.numRegs, (kRegsFew + kRegsMany + 1) / 2);
         configured = true;
     }
-    AttnTcParams p{(__nv_bfloat16*)out, block_table, tile_req, tile_row0, q_start, ctx_before, NH, NKV, page_size,
-                   max_pages, window, scale * 1.4426950408889634f, status};
-    return forge::check_launch("paged_attention_sm100",
-                               forge::launch(paged_attention_sm100_kernel, dim3((unsigned)num_tiles * NKV), dim3(kThreads), kSmemBytes,
-                                             stream, 1, tq, tkv, p));
+    AttnTcParams p{(__nv_bfloat16*)out, block_table, tile_req, tile_row0, tile_cut, (float*)part_o, (float*)part_ml,
+                   q_start, ctx_before, NH, NKV, page_size, max_pages, window, scale * 1.4426950408889634f, status};
+    int rc = forge::check_launch("paged_attention_sm100",
+                                 forge::launch(paged_attention_sm100_kernel, dim3((unsigned)num_tiles * NKV), dim3(kThreads), kSmemBytes,
+                                               stream, 1, tq, tkv, p));
+    if (rc != FORGE_OK || num_merge == 0) return rc;
+    return forge::check_launch("attention_sm100_merge",
+                               forge::launch(attention_sm100_merge_kernel, dim3((unsigned)num_merge * NKV, BQ / kMergeRows), dim3(kMergeThreads), 0,
+                                             stream, 1, p, merge_list));
 }
 
 extern "C" const char* forge_last_error() { return forge::error_buffer(); }

@@ -56,7 +56,7 @@ _SIGNATURES = {
         "forge_decode_attention_stream": [_P] * 7 + [_I] * 9 + [_F, _F, _I, _I, _P],
     },
     "attention_sm100": {
-        "forge_paged_attention_sm100": [_P] * 9 + [_I] * 9 + [_F, _P],
+        "forge_paged_attention_sm100": [_P] * 10 + [_I] + [_P] * 3 + [_I] * 9 + [_F, _P],
     },
     "decode_layers": {
         "forge_decode_layers_desc_bytes": [],
@@ -690,10 +690,16 @@ def attention_plan(batch, group, device, only_below=None):
     return plan
 
 
-def attention_plan_tc(batch, group, device):
+TC_MIN_SHARE = 8     # key tiles (of 64 keys) that a share of a tile's keys holds at least
+TC_MAX_SHARES = 32
+
+
+def attention_plan_tc(batch, group, device, n_kv_heads=1, head_dim=64, window=0, shares=None):
     """Tiles of (128 // group) whole tokens, that is up to 128 rows, for the requests that bring at least TC_MIN_ROWS
-    rows, heaviest (most keys) first."""
-    key = ("tc", group)
+    rows, heaviest (most keys) first.  When the step has at most half as many (tile, kv head) pairs as the GPU has
+    places for the kernel's CTAs, the keys of the long tiles are cut into shares, in proportion to their length, so that the places
+    are taken (a short portion on a long context); ``shares`` forces a number for every tile (tests)."""
+    key = ("tc", group, n_kv_heads, head_dim, window, shares)
     plan = batch.attention_plan.get(key)
     if plan is not None:
         return plan
@@ -703,11 +709,41 @@ def attention_plan_tc(batch, group, device):
         rows = (qs[s + 1] - qs[s]) * group
         if rows < TC_MIN_ROWS:
             continue
+        ctx = batch.host_context_before[s]
         for r0 in range(0, rows, tile_rows):
-            tiles.append((batch.host_context_before[s] + min(rows, r0 + tile_rows) // group, s, r0))
-    tiles.sort(reverse=True)
-    plan = {"tile_req": new_ints([t[1] for t in tiles], device), "tile_row0": new_ints([t[2] for t in tiles], device),
-            "num_tiles": len(tiles)}
+            kv_hi = ctx + (min(rows, r0 + tile_rows) - 1) // group + 1
+            kv_lo = max(0, ctx + r0 // group - window + 1) if window else 0
+            tiles.append((-(-kv_hi // KV_TILE) - kv_lo // KV_TILE, s, r0))
+    places = _sm_count(device) * (2 if head_dim <= 64 else 1)
+    total = max(1, sum(t[0] for t in tiles) * n_kv_heads)
+
+    def worth(n, scale):        # n / (total / places): how many places this tile's keys are worth
+        return max(1, min(n // TC_MIN_SHARE, n * places * scale // (10 * total), TC_MAX_SHARES))
+    if shares is not None:
+        cut = [max(1, min(int(shares), t[0], TC_MAX_SHARES)) for t in tiles]
+    else:
+        cut = [1] * len(tiles)
+        # (with more than half of the places taken already there is nothing to gain that pays for the second kernel)
+        for scale in range(10, 4, -1) if 2 * len(tiles) * n_kv_heads <= places else ():
+            # short tiles count as one whole place each: shrink the others' worth until all fit
+            trial = [worth(t[0], scale) for t in tiles]
+            if sum(trial) * n_kv_heads <= places:
+                cut = trial
+                break
+    entries, merges, slots = [], [], 0
+    for (n, s, r0), z in zip(tiles, cut):
+        if z > 1:
+            merges.append((s, r0, slots, z))
+        entries += [(n / z, s, r0, i, z, slots if z > 1 else 0) for i in range(z)]
+        slots += z if z > 1 else 0
+    entries.sort(key=lambda e: (-e[0], e[1], e[2], e[3]))
+    plan = {"tile_req": new_ints([e[1] for e in entries], device), "tile_row0": new_ints([e[2] for e in entries], device),
+            "num_tiles": len(entries), "num_merge": len(merges), "tile_cut": None, "merge_list": None, "part_o": None, "part_ml": None}
+    if merges:
+        plan["tile_cut"] = new_ints([v for e in entries for v in e[3:6]], device)
+        plan["merge_list"] = new_ints([v for m in merges for v in m], device)
+        plan["part_o"] = new_tensor((slots * n_kv_heads * TC_ROWS * head_dim,), torch.float32, device, whole_step=True)
+        plan["part_ml"] = new_tensor((slots * n_kv_heads * TC_ROWS * 2,), torch.float32, device, whole_step=True)
     batch.attention_plan[key] = plan
     return plan
 
@@ -718,11 +754,12 @@ def attention_sm100_supports(head_dim, group, page_size):
 
 
 def paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, head_dim, page_size, window=0,
-                          scale=None, out=None):
+                          scale=None, out=None, shares=None):
     """tcgen05/TMEM attention for the requests of the step that bring many rows (prompt portions).  Writes
-    only those requests' rows of ``out``.  Returns (out, number of tiles run)."""
+    only those requests' rows of ``out``.  Returns (out, number of tiles run: a tile whose keys are cut into
+    shares counts once per share)."""
     lib = library("attention_sm100", {"FORGE_ATT_HD": head_dim})
-    plan = attention_plan_tc(batch, n_heads // n_kv_heads, q.device)
+    plan = attention_plan_tc(batch, n_heads // n_kv_heads, q.device, n_kv_heads, head_dim, int(window or 0), shares)
     if out is None:
         out = new_tensor(q.shape, q.dtype, q.device)
     if plan["num_tiles"] == 0:
@@ -731,10 +768,14 @@ def paged_attention_sm100(q, kv_cache, group_batch, batch, n_heads, n_kv_heads, 
     _check(lib, lib.forge_paged_attention_sm100(
         _need(q, "q", torch.bfloat16, 2), _need(kv_cache, "kv_cache", torch.bfloat16), _need(out, "out", torch.bfloat16),
         _need(group_batch.block_table, "block_table", torch.int32, 2), _need(plan["tile_req"], "tile_req"),
-        _need(plan["tile_row0"], "tile_row0"), _need(batch.q_start, "q_start", torch.int32),
+        _need(plan["tile_row0"], "tile_row0"), _opt(plan["tile_cut"], "tile_cut"), _opt(plan["part_o"], "part_o"),
+        _opt(plan["part_ml"], "part_ml"), _opt(plan["merge_list"], "merge_list"), plan["num_merge"],
+        _need(batch.q_start, "q_start", torch.int32),
         _need(batch.context_before, "context_before", torch.int32), _need(_gemm_status(q.device), "status", torch.int32),
         plan["num_tiles"], q.shape[0], kv_cache.shape[0], n_heads, n_kv_heads, head_dim, page_size,
         group_batch.block_table.shape[1], int(window or 0), float(scale), _stream()), "paged_attention_sm100")
+    if plan["num_merge"]:
+        count_launches(1)      # the kernel that adds the shares up
     return out, plan["num_tiles"]
 
 
