@@ -82,6 +82,9 @@ def case(name):
     if name == "attention_prefill_hd128":    # the Llama-3-8B heads: 32 / 8 kv heads of 128, one request of 2048 tokens: 34.4 GFLOP
         q, kv, g, b = _attention_inputs([(0, 2048)], 32, 8, 128)
         return (lambda: paged_attention(q, kv, g, b, 32, 8, 128, PS)), 0, 2 * 2048 * 2048 * 32 * 128
+    if name == "attention_prefill_shared_keys":     # 256 new tokens on 20,000 cached: 16 tiles x 4 kv heads, each tile's keys shared out among 4 CTAs
+        q, kv, g, b = _attention_inputs([(20000, 256)])
+        return (lambda: paged_attention(q, kv, g, b, NH, NKV, HD, PS)), 20256 * 2 * NKV * HD * 2, 4 * 256 * 20128 * NH * HD
     if name == "gemm_prefill_qkv_rope":      # 2048 tokens x [2560, 2048]; the epilogue rotates q, k and writes q (bf16) and the cache
         x, w = _bf16(2048, H), _bf16((NH + 2 * NKV) * HD, H, scale=0.02)
         pos = torch.arange(2048, dtype=torch.int32, device=DEV)
@@ -94,7 +97,7 @@ def case(name):
     raise SystemExit(f"unknown case {name!r}; known: gemm_decode_gateup gemm_decode_down gemm_decode_lmhead gemm_prefill_qkv "
                      "gemm_prefill_gateup "
                      "gemm_prefill_qkv_rope gemm_prefill_down attention_decode attention_decode_fused attention_decode_stream attention_prefill "
-                     "attention_prefill_hd128 attention_prefill_mma")
+                     "attention_prefill_hd128 attention_prefill_mma attention_prefill_shared_keys")
 
 
 def main(argv):
