@@ -6,7 +6,7 @@ top-p 0.9, repeat penalty 1.1, n-predict 256, -1 meaning 256; temperature 0 mean
 The reference tokenizes -p with the tokenizer stored in its GGUF file; a safetensors folder has none, so
 here -p takes token ids ("1,15,27" or "1 15 27"), as does --prompt-file.  Options that select what this
 engine does not have (-ngl, -t, -b, --kv-cache-dtype, --mmproj, --image, -i, --system-prompt) are refused
-with a message.  Ours only: --dtype, --random-weights CONFIG.json, --page-size, --max-tokens-per-step.
+with a message.  Ours only: --dtype, --random-weights CONFIG.json, --page-size, --kv-pages, --max-tokens-per-step.
 """
 import argparse
 import json
@@ -40,10 +40,12 @@ def build_parser():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
     ap.add_argument("--random-weights", metavar="CONFIG.json", help="make a random model from this config")
     ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page (8, 16, 32 or 64)")
-    ap.add_argument("--max-tokens-per-step", type=int, default=2048)
+    ap.add_argument("--kv-pages", type=int, default=None, help="pages of the cache (default: sized from the free device memory)")
+    ap.add_argument("--max-tokens-per-step", type=int, default=2048, help="longer prompts are run in portions of this many tokens")
     for flag in ("-ngl", "--n-gpu-layers", "-t", "--threads", "-b", "--batch-size", "--kv-cache-dtype", "--mmproj",
                  "--image", "--system-prompt"):
-        ap.add_argument(flag, dest="unsupported_" + flag.strip("-").replace("-", "_"), default=None)
+        ap.add_argument(flag, dest="unsupported_" + flag.strip("-").replace("-", "_"), default=None, metavar="X",
+                        help="(the reference's option; not part of this engine, refused)")
     ap.add_argument("-i", "--interactive", action="store_true")
     ap.add_argument("--bench", action="store_true", help="prefill of 32/128/512 tokens and 128 decode steps, timed")
     return ap
@@ -112,8 +114,12 @@ def main(argv=None):
         for k, v in cfg.to_dict().items():
             print(f"  {k}: {v}")
         return 0
+    if a.kv_pages is not None and a.kv_pages < 1:
+        raise SystemExit("Error: --kv-pages must be at least 1")
+    cache_tokens = a.kv_pages * a.page_size if a.kv_pages else None
     if a.bench:
-        model = Model(model_dir, dtype=a.dtype, block_size=a.page_size, max_num_seqs=1, max_tokens_per_step=a.max_tokens_per_step)
+        model = Model(model_dir, dtype=a.dtype, block_size=a.page_size, max_num_seqs=1, max_tokens_per_step=a.max_tokens_per_step,
+                      cache_tokens=cache_tokens)
         run_benchmark(model, a.verbose)
         return 0
     if a.prompt is None and a.prompt_file is None:
@@ -121,7 +127,7 @@ def main(argv=None):
     prompt = parse_ids(a.prompt if a.prompt is not None else open(a.prompt_file).read())
     n_predict = 256 if a.n_predict == -1 else a.n_predict
     model = Model(model_dir, dtype=a.dtype, block_size=a.page_size, max_num_seqs=1,
-                  max_tokens_per_step=a.max_tokens_per_step)
+                  max_tokens_per_step=a.max_tokens_per_step, cache_tokens=cache_tokens)
     times = []
     if a.verbose:                      # per-kernel timing table at the end (decode steps are launched one by one meanwhile)
         from . import kernels

@@ -133,7 +133,8 @@ def test_command_line(tiny):
     prompt = random_tokens(6, TINY[name]["vocab_size"], seed=9)
     want = plain.generate_greedy(prompt, 5)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "forge-cli"), "-m", d, "-p",
-                           " ".join(map(str, prompt)), "-n", "5", "--temp", "0", "--repeat-penalty", "1.0", "--no-stream", "--dtype", "float32"],
+                           " ".join(map(str, prompt)), "-n", "5", "--temp", "0", "--repeat-penalty", "1.0", "--no-stream", "--dtype", "float32",
+                           "--page-size", "8", "--kv-pages", "2"],
                           capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stderr[-2000:]
     first = proc.stdout.strip().splitlines()[0]
