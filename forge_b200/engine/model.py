@@ -32,7 +32,7 @@ class Model:
                 raise ConfigError(f"layer {i}: cache_from {spec.cache_from} is not a layer")
         self.loaded = False
         self._fused = None
-        self._replay_ok, self._replay_tensors = False, []
+        self._replay_ok, self._replay_from, self._replay_tensors = False, 0, []
 
     # ---------------------------------------------------------------------------------- tensors
     def _children(self):
@@ -66,10 +66,15 @@ class Model:
             else:
                 part.bind(mine)
         self.loaded = True
-        # layers whose launches may be repeated from one noted layer: from the second run of the schedule on, all of
-        # one key (the first run is always made by the parts themselves)
+        # layers whose launches may be repeated from one noted layer: all runs of the schedule from the first on, or
+        # (a model whose first layer is of another kind) from the second on, declare it with one key
         runs = [replay_of(self.blocks[i]) for i in self.plan.schedule]
-        self._replay_ok = len(runs) >= 3 and all(r is not None for r in runs[1:]) and len({r[0] for r in runs[1:]}) == 1
+        self._replay_ok = False
+        for first in (0, 1):
+            rest = runs[first:]
+            if len(rest) >= 2 and all(r is not None for r in rest) and len({r[0] for r in rest}) == 1:
+                self._replay_ok, self._replay_from = True, first
+                break
         self._replay_tensors = [r[1] if r is not None else None for r in runs]
 
     def graph_safe(self):
@@ -137,15 +142,15 @@ class Model:
         return True
 
     def _replay_applies(self, position_caches, ws):
-        """Whether the layers after the second may repeat the second's launches: every layer from the second on
-        declares it and has the same key (``parts.base.replay_of``), their caches are of one kind, the outputs come
-        from the step's workspace (so a layer's intermediates have the same addresses in every layer), and no timing
-        table is being taken (it wants an event per launch)."""
+        """Whether the layers after the noted one may repeat its launches: every layer from the noted one on declares
+        it and has the same key (``parts.base.replay_of``), their caches are of one kind, the outputs come from the
+        step's workspace (so a layer's intermediates have the same addresses in every layer), and no timing table is
+        being taken (it wants an event per launch)."""
         if ws is None or not self._replay_ok or kernels.profiler_enabled() or os.environ.get("FORGE_LAYER_REPLAY", "1") == "0":
             return False
-        c1 = position_caches[1]
+        c1 = position_caches[self._replay_from]
         kind = (getattr(c1, "group", None), getattr(c1, "writable", None), getattr(c1, "page_size", None))
-        for c in position_caches[1:]:
+        for c in position_caches[self._replay_from:]:
             kv = getattr(c, "kv", None)
             if kv is None or (getattr(c, "group", None), getattr(c, "writable", None), getattr(c, "page_size", None)) != kind \
                     or kv.shape != c1.kv.shape or kv.dtype != c1.kv.dtype:
@@ -169,9 +174,10 @@ class Model:
                 if replay is not None:
                     replay.run(self._replay_tensors[pos] + [position_caches[pos].kv])
                     continue
-                # the second layer's launches are noted (the first also makes what the whole step shares: tile
-                # lists, the table of angles) and repeated for the layers after it
-                note = pos == 1 and self._replay_applies(position_caches, ws)
+                # one layer's launches are noted and repeated for the layers after it (what the whole step shares,
+                # tile lists and the table of angles, is made inside the first layer: those launches are marked
+                # and stay out of the notes)
+                note = pos == self._replay_from and self._replay_applies(position_caches, ws)
                 m = ws.mark() if ws is not None else 0
                 if note:
                     overflow = ws.allocations

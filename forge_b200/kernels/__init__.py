@@ -146,7 +146,26 @@ _launches = [0]
 # about 17 us against 3 to 10 us of device time at few tokens: a prompt of 128 tokens took 2.7 ms for 0.9 ms of device
 # work.  So a model whose layers declare it (parts.base.replay_of) runs ONE layer through Python with the calls into
 # the libraries noted, and repeats the noted calls for the other layers with the layer's own addresses in place.
+# Launches that make what the whole step shares happen inside the layer that first needs it; they are marked
+# (once_per_step) and left out of the notes.
 _recording = [None]
+_once = [0, 0]          # depth of open ``once_per_step`` blocks; launches counted inside them while a recording is open
+
+
+class _OncePerStep:
+    def __enter__(self):
+        _once[0] += 1
+
+    def __exit__(self, *exc):
+        _once[0] -= 1
+        return False
+
+
+def once_per_step():
+    """``with once_per_step():`` around launches that make something the whole step shares (a table of angles, a
+    workspace handed to a library): a recording that is open leaves them out, and they are not repeated with the
+    layer they happened to be made in."""
+    return _OncePerStep()
 
 
 class _Entry:
@@ -159,7 +178,7 @@ class _Entry:
 
     def __call__(self, *args):
         rec = _recording[0]
-        if rec is not None:
+        if rec is not None and not _once[0]:
             rec.append((self, args))
         return self.fn(*args)
 
@@ -168,11 +187,12 @@ class _Recording:
     def __enter__(self):
         self.calls, self.launches0 = [], _launches[0]
         _recording[0] = self.calls
+        _once[1] = 0
         return self
 
     def __exit__(self, *exc):
         _recording[0] = None
-        self.launches = _launches[0] - self.launches0
+        self.launches = _launches[0] - self.launches0 - _once[1]
         return False
 
 
@@ -229,6 +249,8 @@ def count_launches(n):
 
 def _check(lib, rc, what):
     _launches[0] += 1
+    if _once[0]:
+        _once[1] += 1
     if rc != 0:
         raise KernelError(f"{what}: {lib.forge_last_error().decode(errors='replace')} (code {rc})")
     if _profile["on"]:
@@ -504,8 +526,9 @@ def rope_table(positions, head_dim, theta, by_pair=False):
     T = positions.numel()
     shape = (head_dim // 2, T, 2) if by_pair else (T, head_dim // 2, 2)
     table = new_tensor(shape, torch.float32, positions.device, whole_step=True)
-    _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
-                                     float(theta), 1 if by_pair else 0, _stream()), "rope_table")
+    with once_per_step():
+        _check(lib, lib.forge_rope_table(_need(positions, "positions", torch.int32), _need(table, "table"), T, head_dim,
+                                         float(theta), 1 if by_pair else 0, _stream()), "rope_table")
     return table
 
 
@@ -1064,7 +1087,7 @@ def _gemm_workspace(lib, device):
     key = str(device)
     if key not in _workspaces:
         ws = torch.zeros(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
-        with torch.cuda.device(device):
+        with torch.cuda.device(device), once_per_step():
             rc = lib.forge_gemm_sm100_set_workspace(ws.data_ptr(), GEMM_WORKSPACE_BYTES)
         if rc != 0:
             raise KernelError(f"gemm_sm100: {lib.forge_last_error().decode(errors='replace')}")

@@ -84,3 +84,18 @@ def test_parts_declare_it_only_for_exactly_the_stock_classes():
     m.weight = torch.ones(8)
     assert replay_of(m) is None
     assert replay_of(object()) is None
+
+
+def test_launches_marked_once_per_step_are_left_out():
+    """What the whole step shares is made inside the first layer that needs it: those launches are made, but
+    neither noted nor counted for the layers that repeat the notes."""
+    log = []
+    entry = make_entry(log, pointer_args=(0,))
+    w = torch.zeros(8)
+    with kernels.record_launches() as rec:
+        with kernels.once_per_step():
+            kernels._check(FakeLib(), entry(w.data_ptr(), 1), "table")        # runs, is not noted
+        kernels._check(FakeLib(), entry(w.data_ptr(), 2), "product")
+    assert [a[1] for a in log] == [1, 2]
+    assert len(rec.calls) == 1 and rec.calls[0][1][1] == 2 and rec.launches == 1
+    assert kernels._once[0] == 0

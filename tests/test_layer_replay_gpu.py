@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 
 # the tiny configurations A (small heads, every kernel's general form), C (the serving kernels of head size 64) and D
-# (heads of 128, bias) with six layers: one run by the parts, one noted, four repeated
+# (heads of 128, bias) with six layers: one run by the parts and noted, five repeated
 DEEP = {name: dict(TINY[name], num_hidden_layers=6) for name in ("A", "C", "D")}
 LENGTHS = {"A": [70, 129, 33, 200], "C": [300, 20, 131, 260], "D": [210, 9, 95, 150]}
 
@@ -58,8 +58,8 @@ def test_deep_models_equal_plain_and_themselves_without_replay(deep, dtype, sche
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_launches_are_counted_and_really_repeated(deep, dtype, monkeypatch):
-    """A prompt step makes the same number of launches with and without repetition, and with it only two of the six
-    layers go through the parts (seen by counting the calls of one part)."""
+    """A prompt step makes the same number of launches with and without repetition, and with it only one of the six
+    layers goes through the parts (seen by counting the calls of one part)."""
     from forge_b200 import kernels
     from forge_b200.engine import StepEntry
     from forge_b200.parts.norm import RMSNorm
@@ -84,7 +84,7 @@ def test_launches_are_counted_and_really_repeated(deep, dtype, monkeypatch):
         runner.release("a")
         counts[mode] = (kernels.launch_count() - before, calls[0], logits.clone())
     assert counts["1"][0] == counts["0"][0]
-    assert counts["0"][1] == 2 * 6 + 1 and counts["1"][1] == 2 * 2 + 1      # two norms a layer, and the final one
+    assert counts["0"][1] == 2 * 6 + 1 and counts["1"][1] == 2 * 1 + 1      # two norms a layer, and the final one
     assert torch.equal(counts["1"][2], counts["0"][2])
 
 
@@ -148,3 +148,53 @@ def test_layers_with_parts_that_do_not_declare_it_are_run_by_their_parts(tmp_pat
             assert CountingNorm.seen == 2 * 6
     finally:
         unregister_part("norm", "counting_rmsnorm")
+
+
+def test_a_first_layer_of_another_kind_is_run_by_its_parts_and_the_second_is_noted(tmp_path, monkeypatch):
+    """Only the first layer has the norm that does not declare it: that layer always runs by its parts, the second is
+    noted and the four after it repeat its launches; the same bits as with every layer run by its parts."""
+    from forge_b200.config import config_from_dict
+    from forge_b200.config.base import PartSpec
+    from forge_b200.engine import ModelRunner, StepEntry
+    from forge_b200.parts import register_part, unregister_part
+    from forge_b200.parts.norm import RMSNorm
+    from forge_b200.weights import write_random_model
+
+    class FirstNorm(RMSNorm):
+        seen = 0
+
+        def forward(self, x, out_dtype=None, rows=None):
+            FirstNorm.seen += 1
+            return super().forward(x, out_dtype, rows)
+
+    register_part("norm", "first_rmsnorm", FirstNorm)
+    try:
+        cfg = config_from_dict(DEEP["C"])
+        d = str(tmp_path / "m")
+        write_random_model(cfg, d, seed=6, **STDS["C"])
+        orig_plan = type(cfg).plan
+
+        def plan(self):
+            p = orig_plan(self)
+            for key, spec in list(p.layers[0].norms.items()):
+                p.layers[0].norms[key] = PartSpec("first_rmsnorm", spec.params)
+            return p
+        toks = random_tokens(150, DEEP["C"]["vocab_size"], seed=2)
+        outs = {}
+        for mode in ("1", "0"):
+            monkeypatch.setenv("FORGE_LAYER_REPLAY", mode)
+            type(cfg).plan = plan
+            try:
+                runner = ModelRunner(d, dtype="bfloat16", page_size=16, cache_tokens=256, max_requests=2)
+            finally:
+                type(cfg).plan = orig_plan
+            assert runner.model._replay_ok and runner.model._replay_from == 1
+            for _ in range(2):              # the second step finds its workspace sized
+                FirstNorm.seen = 0
+                runner.admit("a")
+                outs[mode] = runner.step([StepEntry("a", toks, list(range(150)))]).clone()
+                runner.release("a")
+                assert FirstNorm.seen == 2
+        assert torch.equal(outs["1"], outs["0"])
+    finally:
+        unregister_part("norm", "first_rmsnorm")
