@@ -647,25 +647,34 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t local_addr, uint32_t r
 // and the readers, a row per warp, touch without bank conflicts), the cluster synchronises, and every CTA then adds
 // up, in rank order (so the result does not depend on timing), the rows it owns, adds the bias and writes C: a
 // store, or one add per element into the residual stream.  fp32 results only (no bf16 or SwiGLU epilogue).
+// G: k-blocks per TMA instruction and ring slot (the matrix seen as {64 columns, rows, K / 64 k-blocks}); G = 1 is the
+// form for a K that is no multiple of 64 (plain 2-D maps).  Measured on the o-projection of 512 rows inside a prompt
+// step: 14.7 us with one k-block per instruction, 13.9 with two, 11.2 with the reduction asking for four rows' shares
+// before it uses the first.  Tiles of [128 x 256] cut four ways (a third fewer bytes per SM) were slower at every size
+// tried (512 rows: o 13.5, down 21.5 against 19.6 us): a CTA's time here is a chain of short phases, not its bytes.
 constexpr int kSplitBN = 128;
+template <int G>
 struct SplitKCfg {
-    static constexpr int kStageBytes = (BM + kSplitBN) * BK * 2;            // 32 KB
-    static constexpr int kStages = 4;
-    static constexpr int kPartialBytes = BM * kSplitBN * 4;                 // 64 KB
-    static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 1024;
-    static constexpr int kTmemCols = 128;
+    static constexpr int kStageBytes = G * (BM + kSplitBN) * BK * 2;        // 32 KB per k-block
+    static constexpr int kStages = 6 / G;                                   // a ring of 192 KB
+    static constexpr int kPartialBytes = BM * kSplitBN * 4;                 // 64 KB, parked in the ring once its slots are free
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+    static constexpr int kTmemCols = kSplitBN;
+    static_assert(kPartialBytes <= kStages * kStageBytes, "the partial sums take the ring's place");
 };
 
+template <int G>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sm100_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                          const GemmParams p, const int ksplit) {
-    using C = SplitKCfg;
+    using C = SplitKCfg<G>;
     constexpr int kStages = C::kStages, BN = kSplitBN;
+    constexpr int kTileA = BM * BK * 2, kTileW = BN * BK * 2;                            // one k-block of either operand
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tiles = smem;
-    float* partial = reinterpret_cast<float*>(smem + kStages * C::kStageBytes);          // [128 rows][32 chunks of 4], swizzled
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kPartialBytes);
+    uint8_t* tiles = smem;                                                               // slot: G tiles of A, then G tiles of W
+    float* partial = reinterpret_cast<float*>(smem);       // [128 rows][BN / 4 chunks of 4], swizzled; written when the last product has read the ring
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes);
     uint64_t* full = bars;
     uint64_t* empty = bars + kStages;
     uint64_t* acc_full = bars + 2 * kStages;
@@ -700,39 +709,57 @@ gemm_sm100_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t tmem_base = *tmem_slot;
     forge::pdl_launch_dependents();
 
+    const int my_groups = (my_kb + G - 1) / G;          // ring slots this CTA fills (the last may hold fewer k-blocks)
+    // one operand's G k-blocks of slot `i`: one instruction (a box beyond this CTA's share or beyond K brings the
+    // neighbour's k-blocks or zeros, which no product reads)
+    auto load_a = [&](int i, uint64_t* bar) {
+        uint8_t* dst = tiles + (i % kStages) * C::kStageBytes;
+        if constexpr (G == 1) tma_load_2d(dst, &tmap_a, bar, (kb_begin + i) * BK, m0);
+        else tma_load_3d(dst, &tmap_a, bar, 0, m0, kb_begin + i * G);
+    };
+    auto load_w = [&](int i, uint64_t* bar) {
+        uint8_t* dst = tiles + (i % kStages) * C::kStageBytes + G * kTileA;
+        if constexpr (G == 1) tma_load_2d(dst, &tmap_w, bar, (kb_begin + i) * BK, n0);
+        else tma_load_3d(dst, &tmap_w, bar, 0, n0, kb_begin + i * G);
+    };
     if (warp == 0) {
         if (lane == 0) {
             // the weights do not depend on earlier kernels: their first stages are requested before the wait
-            const int first = min(my_kb, kStages);
+            const int first = min(my_groups, kStages);
             for (int i = 0; i < first; ++i) {
                 mbar_arrive_expect_tx(&full[i], C::kStageBytes);
-                tma_load_2d(tiles + i * C::kStageBytes + BM * BK * 2, &tmap_w, &full[i], (kb_begin + i) * BK, n0);
+                load_w(i, &full[i]);
             }
             forge::pdl_wait();                    // the activations come from the previous kernel
-            for (int i = 0; i < first; ++i) tma_load_2d(tiles + i * C::kStageBytes, &tmap_a, &full[i], (kb_begin + i) * BK, m0);
+            for (int i = 0; i < first; ++i) load_a(i, &full[i]);
             bool ok = true;
-            for (int i = first; i < my_kb && ok; ++i) {
+            for (int i = first; i < my_groups && ok; ++i) {
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&empty[s], ((i / kStages) - 1) & 1, abort, p.status))) break;
                 mbar_arrive_expect_tx(&full[s], C::kStageBytes);
-                tma_load_2d(tiles + s * C::kStageBytes, &tmap_a, &full[s], (kb_begin + i) * BK, m0);
-                tma_load_2d(tiles + s * C::kStageBytes + BM * BK * 2, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
+                load_a(i, &full[s]);
+                load_w(i, &full[s]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
             bool ok = true;
-            for (int i = 0; i < my_kb && ok; ++i) {
+            for (int i = 0; i < my_groups && ok; ++i) {
                 const int s = i % kStages;
                 if (!(ok = mbar_wait(&full[s], (i / kStages) & 1, abort, p.status))) break;
                 tc_fence_after_sync();
-                const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-                const uint64_t a_desc = umma_desc_k_sw128(a_addr), w_desc = umma_desc_k_sw128(a_addr + BM * BK * 2);
+                const uint32_t slot = smem_u32(tiles + s * C::kStageBytes);
+                const int n_here = min(G, my_kb - i * G);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem_base, umma_desc_advance(a_desc, k * UMMA_K * 2), umma_desc_advance(w_desc, k * UMMA_K * 2),
-                              idesc, k != 0 || i != 0);
+                for (int g = 0; g < G; ++g) {
+                    if (g >= n_here) break;
+                    const uint64_t a_desc = umma_desc_k_sw128(slot + g * kTileA), w_desc = umma_desc_k_sw128(slot + G * kTileA + g * kTileW);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(tmem_base, umma_desc_advance(a_desc, k * UMMA_K * 2), umma_desc_advance(w_desc, k * UMMA_K * 2),
+                                  idesc, k != 0 || g != 0 || i != 0);
+                }
                 umma_commit(&empty[s]);
             }
             if (ok && my_kb > 0) umma_commit(acc_full);
@@ -769,35 +796,62 @@ gemm_sm100_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
     if (warp >= 2) {
         // this CTA owns rows [rank * 128 / ksplit, (rank + 1) * 128 / ksplit) of the tile; a warp takes a row at a
-        // time, a lane 16 bytes of it
+        // time, a lane 16 bytes of each 128 columns of it
         const int row_lo = rank * BM / ksplit, row_hi = (rank + 1) * BM / ksplit;
         const uint32_t partial_addr = smem_u32(partial);
-        const int n = n0 + 4 * lane;
-        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.bias) {
-            if (n + 3 < p.N) b = *reinterpret_cast<const float4*>(p.bias + n);
-            else { if (n < p.N) b.x = p.bias[n]; if (n + 1 < p.N) b.y = p.bias[n + 1]; if (n + 2 < p.N) b.z = p.bias[n + 2]; }
-        }
-        for (int row = row_lo + (warp - 2); row < row_hi; row += 4) {
-            const int m = m0 + row;
-            float4 acc = b;
-            const uint32_t at = partial_addr + (row * (BN / 4) + (lane ^ (row & 31))) * 16;
-            for (int q = 0; q < ksplit; ++q) {
-                const float4 v = ld_dsmem_f32x4(at, q);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        constexpr int kHalves = BN / 128;
+        float4 b[kHalves];
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+            const int n = n0 + 128 * h + 4 * lane;
+            b[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.bias) {
+                if (n + 3 < p.N) b[h] = *reinterpret_cast<const float4*>(p.bias + n);
+                else { if (n < p.N) b[h].x = p.bias[n]; if (n + 1 < p.N) b[h].y = p.bias[n + 1]; if (n + 2 < p.N) b[h].z = p.bias[n + 2]; }
             }
-            if (m >= p.M || n >= p.N) continue;
-            float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
-            const bool accum = p.epilogue == EPI_ACCUM_F32;
-            if (n + 3 < p.N && (p.N & 3) == 0) {
-                if (accum) atomicAdd(reinterpret_cast<float4*>(dst), acc);       // one add per element: the order of CTAs does not matter
-                else *reinterpret_cast<float4*>(dst) = acc;
-            } else {
-                const float v[4] = {acc.x, acc.y, acc.z, acc.w};
-                for (int i = 0; i < 4; ++i) {
-                    if (n + i >= p.N) break;
-                    if (accum) atomicAdd(dst + i, v[i]);
-                    else dst[i] = v[i];
+        }
+        // several rows' shares are asked for before the first is used: a load from a peer's shared memory takes some
+        // hundred clocks, and one row after the other was a chain of them
+        constexpr int kAhead = 4 / kHalves;
+        const bool accum = p.epilogue == EPI_ACCUM_F32;
+        for (int first = row_lo + (warp - 2); first < row_hi; first += 4 * kAhead) {
+            float4 v[kAhead][kHalves][4];
+#pragma unroll
+            for (int j = 0; j < kAhead; ++j) {
+                const int row = first + 4 * j;
+                if (row >= row_hi) break;
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) {
+                    const uint32_t at = partial_addr + (row * (BN / 4) + 32 * h + (lane ^ (row & 31))) * 16;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (q < ksplit) v[j][h][q] = ld_dsmem_f32x4(at, q);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kAhead; ++j) {
+                const int row = first + 4 * j, m = m0 + row;
+                if (row >= row_hi) break;
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) {
+                    const int n = n0 + 128 * h + 4 * lane;
+                    float4 acc = b[h];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (q < ksplit) { acc.x += v[j][h][q].x; acc.y += v[j][h][q].y; acc.z += v[j][h][q].z; acc.w += v[j][h][q].w; }
+                    if (m >= p.M || n >= p.N) continue;
+                    float* dst = reinterpret_cast<float*>(p.C) + (size_t)m * p.N + n;
+                    if (n + 3 < p.N && (p.N & 3) == 0) {
+                        if (accum) atomicAdd(reinterpret_cast<float4*>(dst), acc);       // one add per element: the order of CTAs does not matter
+                        else *reinterpret_cast<float4*>(dst) = acc;
+                    } else {
+                        const float e[4] = {acc.x, acc.y, acc.z, acc.w};
+                        for (int i = 0; i < 4; ++i) {
+                            if (n + i >= p.N) break;
+                            if (accum) atomicAdd(dst + i, e[i]);
+                            else dst[i] = e[i];
+                        }
+                    }
                 }
             }
         }
@@ -1448,16 +1502,20 @@ int launch_pair(const void* A, const void* W, const GemmParams& p, cudaStream_t 
     return launch_pair_width<kPairBN>(A, W, p, stream);
 }
 
-// How many CTAs of the split-K kernel run at once in clusters of `ks` (one CTA per SM).
+// How many CTAs of the split-K kernel run at once in clusters of `ks` (one CTA per SM; both forms of the kernel take
+// the same shared memory).
+constexpr int kSplitKSmem = SplitKCfg<2>::kSmemBytes;
+static_assert(SplitKCfg<1>::kSmemBytes == kSplitKSmem, "one occupancy figure serves both forms");
 int splitk_resident_ctas(int ks) {
     static int cached[5] = {0};
     if (ks != 2 && ks != 4) return 0;
     if (cached[ks] == 0) {
-        cudaFuncSetAttribute(gemm_sm100_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SplitKCfg::kSmemBytes);
+        cudaFuncSetAttribute(gemm_sm100_splitk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitKSmem);
+        cudaFuncSetAttribute(gemm_sm100_splitk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitKSmem);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ks * 32);
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = SplitKCfg::kSmemBytes;
+        cfg.dynamicSmemBytes = kSplitKSmem;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = ks;
@@ -1466,7 +1524,7 @@ int splitk_resident_ctas(int ks) {
         cfg.attrs = at;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_splitk_kernel, &cfg) != cudaSuccess || n <= 0) {
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_splitk_kernel<2>, &cfg) != cudaSuccess || n <= 0) {
             cudaGetLastError();
             n = (g_num_sms - (ks > 2 ? g_num_sms / 8 : 0)) / ks;      // a guess on the safe side
         }
@@ -1476,15 +1534,22 @@ int splitk_resident_ctas(int ks) {
 }
 
 int launch_splitk(const void* A, const void* W, const GemmParams& p, int ksplit, cudaStream_t stream) {
-    splitk_resident_ctas(2);                            // also sets the kernel's shared-memory limit
+    splitk_resident_ctas(2);                            // also sets the kernels' shared-memory limit
     CUtensorMap ta, tw;
     const char* err = nullptr;
+    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + kSplitBN - 1) / kSplitBN);
+    if (p.K % BK == 0) {                                // whole k-blocks: two of them per instruction
+        if (!bf16_kblock_map(A, p.M, p.K, BM, 2, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
+        if (!bf16_kblock_map(W, p.N, p.K, kSplitBN, 2, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
+        return forge::check_launch("gemm_sm100 (K cut across a cluster)",
+                                   forge::launch(gemm_sm100_splitk_kernel<2>, dim3(tiles * ksplit), dim3(kThreads),
+                                                 kSplitKSmem, stream, ksplit, ta, tw, p, ksplit));
+    }
     if (!bf16_tile_map(A, p.M, p.K, BM, &ta, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: A: %s", err);
     if (!bf16_tile_map(W, p.N, p.K, kSplitBN, &tw, &err)) return forge::fail(FORGE_ERR_UNSUPPORTED, "gemm_sm100: W: %s", err);
-    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + kSplitBN - 1) / kSplitBN);
     return forge::check_launch("gemm_sm100 (K cut across a cluster)",
-                               forge::launch(gemm_sm100_splitk_kernel, dim3(tiles * ksplit), dim3(kThreads), SplitKCfg::kSmemBytes,
-                                             stream, ksplit, ta, tw, p, ksplit));
+                               forge::launch(gemm_sm100_splitk_kernel<1>, dim3(tiles * ksplit), dim3(kThreads),
+                                             kSplitKSmem, stream, ksplit, ta, tw, p, ksplit));
 }
 
 // k-blocks per TMA instruction for a CTA that has kb_per of them; 0 = K is no multiple of 64 (2D maps).  The group

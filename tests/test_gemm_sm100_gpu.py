@@ -90,10 +90,10 @@ def test_fp32_results_through_shared_memory_and_tma(M, N, K, tile_n):
 
 @pytest.mark.parametrize("tile_n", [0, 1002, 1004])
 @pytest.mark.parametrize("M,N,K", [(512, 2048, 2048), (129, 36, 64), (300, 1000, 136), (512, 2048, 5632), (700, 515, 1032),
-                                   (257, 130, 4104), (1100, 2052, 72)])
+                                   (257, 130, 4104), (1100, 2052, 72), (1024, 2048, 2048), (384, 300, 192)])
 def test_k_cut_across_a_cluster_for_some_hundred_rows(M, N, K, tile_n):
-    """Tiles of 128 x 128 whose K is shared by 2 or 4 CTAs, partial sums added through distributed shared memory in
-    rank order: fp32 store and the addition into the residual (each product counted once), bias, row, column and
+    """Tiles of 128 x 128 whose K is shared by 2 or 4 CTAs, two k-blocks per copy where K is a multiple of 64, partial
+    sums added through distributed shared memory in rank order: fp32 store and the addition into the residual (each product counted once), bias, row, column and
     reduction tails (a last k-block that is partly zeros, CTAs of a cluster with no k-block at all: K = 64 or 72 with 4
     CTAs), and the same bits every time."""
     k = _k()
