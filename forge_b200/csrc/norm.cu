@@ -24,7 +24,8 @@ template <> struct Pack4<__nv_bfloat16> {
 };
 
 // One CTA per row.  With H a multiple of 4 a thread reads float4s (the first kKeep of them stay in registers
-// for the second pass) and writes four outputs at a time; any other H goes element by element.
+// for the second pass, beside the weights they meet there) and writes four outputs at a time; any other H goes
+// element by element.
 template <typename TOut>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
@@ -32,6 +33,16 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* _
     __shared__ float red[32];
     constexpr int kKeep = 4;
     forge::pdl_launch_dependents();
+    // the norm's weights do not depend on the kernel before: a thread's first kKeep float4s of them are read ahead of
+    // the dependency wait instead of after the row's reduction, where the load's latency stood in the open
+    float4 gain[kKeep];
+    if ((H & 3) == 0) {
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int c = threadIdx.x + i * kNormThreads;
+            gain[i] = c < (H >> 2) ? reinterpret_cast<const float4*>(w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     forge::pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -58,7 +69,7 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* _
         for (int i = 0; i < kKeep; ++i) {
             const int c = threadIdx.x + i * kNormThreads;
             if (c < n4) {
-                const float4 g = w4[c];
+                const float4 g = gain[i];
                 Pack4<TOut>::store(o + 4 * c, keep[i].x * inv * g.x, keep[i].y * inv * g.y, keep[i].z * inv * g.z, keep[i].w * inv * g.w);
             }
         }
