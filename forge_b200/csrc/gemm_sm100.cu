@@ -229,21 +229,36 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     forge::pdl_launch_dependents();
-    forge::pdl_wait();                 // A, bias and C may come from (or still be read by) earlier kernels
+    // A, bias and C may come from (or still be read by) earlier kernels: the thread that copies and the warps that
+    // write wait for them below.  W does not: the first tile's first k-blocks of it are asked for before the wait.
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;       // k-blocks issued so far, over all tiles
             bool ok = true;
+            uint32_t ahead = 0;    // stages whose W is on its way already
+            if ((int)blockIdx.x < num_tiles) {
+                const int n0 = ((int)blockIdx.x / tiles_m) * BN;
+                ahead = num_kb < kStages ? num_kb : kStages;
+                for (uint32_t s = 0; s < ahead; ++s) {
+                    mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                    tma_load_2d(tiles + s * C::kStageBytes + BM * BK * 2, &tmap_w, &full[s], s * BK, n0);
+                }
+            }
+            forge::pdl_wait();
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStages;
+                    uint8_t* a_dst = tiles + s * C::kStageBytes;
+                    if (it < ahead) {              // the first tile's k-block `it`: only A is still to come
+                        tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, m0);
+                        continue;
+                    }
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort, p.status))) break;
                     mbar_arrive_expect_tx(&full[s], C::kStageBytes);
-                    uint8_t* a_dst = tiles + s * C::kStageBytes;
                     tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, m0);
                     tma_load_2d(a_dst + BM * BK * 2, &tmap_w, &full[s], kb * BK, n0);
                 }
@@ -291,6 +306,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;              // TMEM lanes this warp may read: 32*quarter .. +31
         const int row_in_tile = quarter * 32 + lane;
+        forge::pdl_wait();                         // bias and C: written or still read by earlier kernels
         bool ok = true;
         int local = 0, out_chunk = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
@@ -489,7 +505,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     forge::pdl_launch_dependents();
-    forge::pdl_wait();                     // A, bias and C may come from (or still be read by) earlier kernels
+    // A, bias and C may come from (or still be read by) earlier kernels: the threads that copy and the warps that
+    // write wait for them below.  W does not: the first tile's first stages of it are asked for before the wait.
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one per CTA)
@@ -497,15 +514,33 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             uint32_t it = 0;
             bool ok = true;
             const uint32_t full0 = map_to_cta(smem_u32(&full[0]), 0);
+            uint32_t ahead = 0;                // stages whose W is on its way already
+            if (pair < num_tiles) {
+                const int n0 = (pair / tiles_m) * PBN + rank * BNH;
+                ahead = num_groups < kStages ? num_groups : kStages;
+                for (uint32_t s = 0; s < ahead; ++s) {
+                    if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);
+                    const uint32_t bar = full0 + s * 8;
+                    uint8_t* w_dst = tiles + s * kStageBytes + kABytes;
+                    if constexpr (G > 0) tma_load_3d_pair(w_dst, &tmap_w, bar, 0, n0, (int)s * g);
+                    else tma_load_2d_pair(w_dst, &tmap_w, bar, (int)s * BK, n0);
+                }
+            }
+            forge::pdl_wait();
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 const int m0 = (tile % tiles_m) * 2 * BM + rank * BM, n0 = (tile / tiles_m) * PBN + rank * BNH;
                 for (int gi = 0; gi < num_groups; ++gi, ++it) {
                     const int s = it % kStages;
+                    const uint32_t bar = full0 + s * 8;
+                    uint8_t* a_dst = tiles + s * kStageBytes;
+                    if (it < ahead) {              // the first tile's stage `it`: only A is still to come
+                        if constexpr (G > 0) tma_load_3d_pair(a_dst, &tmap_a, bar, 0, m0, gi * g);
+                        else tma_load_2d_pair(a_dst, &tmap_a, bar, gi * BK, m0);
+                        continue;
+                    }
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort, p.status))) break;
                     if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);   // k-blocks past K arrive as zeros
-                    const uint32_t bar = full0 + s * 8;
-                    uint8_t* a_dst = tiles + s * kStageBytes;
                     if constexpr (G > 0) {
                         tma_load_3d_pair(a_dst, &tmap_a, bar, 0, m0, gi * g);
                         tma_load_3d_pair(a_dst + kABytes, &tmap_w, bar, 0, n0, gi * g);
@@ -556,6 +591,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+        forge::pdl_wait();                         // bias, C and what the epilogue reads beside them: earlier kernels' to finish with
         bool ok = true;
         int local = 0, out_chunk = 0;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
