@@ -176,8 +176,9 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     forge::pdl_launch_dependents();
-    forge::pdl_wait();
 
+    // (the step's tile lists, request boundaries and block tables were written before its first kernel started: they
+    // are read ahead of the dependency wait, which orders this kernel after the one that makes q and this step's keys)
     const int s_req = p.tile_req[tile], row0 = p.tile_row0[tile];
     const int qs0 = p.q_start[s_req], qlen = p.q_start[s_req + 1] - qs0, ctx = p.ctx_before[s_req];
     const int tile_rows = (BQ / G) * G;                             // rows of a full tile: whole tokens only
@@ -196,6 +197,7 @@ paged_attention_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const int t_begin = t_first + (int)((long long)n_all * share / shares);
     const int t_end = t_first + (int)((long long)n_all * (share + 1) / shares);
     const int n_iter = t_end - t_begin;
+    forge::pdl_wait();
 
     // the softmax rows keep a row's 64 scores in registers; the other warpgroup runs single threads and gives
     // its registers up for that
