@@ -68,7 +68,7 @@ def test_short_portions_on_long_contexts_are_cut_to_fill_the_places(on_cpu, reqs
     plan = plan_of(reqs, group, nkv, hd)
     places = 148 * (2 if hd <= 64 else 1)
     assert plan["num_merge"] > 0
-    assert plan["num_tiles"] * nkv <= places, "the shares must not need a second round of CTAs"
+    assert plan["num_tiles"] * nkv <= places, "the shares must not need a second wave of CTAs"
     uncut = plan_of(reqs, group, nkv, hd, shares=1)
     assert plan["num_tiles"] > uncut["num_tiles"]
     check_consistent(plan, nkv, hd)
