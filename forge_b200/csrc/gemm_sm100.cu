@@ -984,12 +984,25 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     const int my_kb = max(kb_end - kb_begin, 0);
     const int my_groups = (my_kb + g - 1) / g;
 
+    // a group that sticks out over the end of K is filled with zeros there and counts in full
+    const int stage_tx = w_bytes + x_bytes;
+    auto load_w = [&](int i, int s) {
+        if (group > 0) tma_load_3d(w_tiles + s * w_bytes, &tmap_w, &full[s], 0, n0, kb_begin + i * g);
+        else tma_load_2d(w_tiles + s * w_bytes, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
+    };
+    const int first = min(my_groups, kStages);           // the stages that are filled without waiting for a free one
     if (threadIdx.x == 0) {
         *abort = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&reuse[s], 2); }
         mbar_init(acc_full, 2);
         mbar_fence_init();
-        prefetch_tensormap(&tmap_w);
+        // The weights depend on nothing that runs before this kernel: this thread, which is the one that copies, asks
+        // for their first stages as soon as the barriers they report to exist, ahead of the CTA's other set-up and of
+        // the dependency wait.
+        for (int i = 0; i < first; ++i) {
+            mbar_arrive_expect_tx(&full[i], stage_tx);
+            load_w(i, i);
+        }
         prefetch_tensormap(&tmap_x);
     }
     if (warp == 1) {
@@ -1009,22 +1022,11 @@ gemm_sm100_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            // a group that sticks out over the end of K is filled with zeros there and counts in full
-            const int stage_tx = w_bytes + x_bytes;
-            auto load_w = [&](int i, int s) {
-                if (group > 0) tma_load_3d(w_tiles + s * w_bytes, &tmap_w, &full[s], 0, n0, kb_begin + i * g);
-                else tma_load_2d(w_tiles + s * w_bytes, &tmap_w, &full[s], (kb_begin + i) * BK, n0);
-            };
             auto load_x = [&](int i, int s) {
                 if (group > 0) tma_load_3d(x_tiles + s * x_bytes, &tmap_x, &full[s], 0, 0, kb_begin + i * g);
                 else tma_load_2d(x_tiles + s * x_bytes, &tmap_x, &full[s], (kb_begin + i) * BK, 0);
             };
-            // the weights do not depend on earlier kernels: their first stages are requested before the wait
-            const int first = min(my_groups, kStages);
-            for (int i = 0; i < first; ++i) {
-                mbar_arrive_expect_tx(&full[i], stage_tx);
-                load_w(i, i);
-            }
+            // (the weights of the first stages were asked for during the set-up)
             forge::pdl_wait();                    // the activations come from the previous kernel
             for (int i = 0; i < first; ++i) load_x(i, i);
             bool ok = true;
